@@ -1,0 +1,166 @@
+// extern "C" entry points for the GEMMs and the fused linear layer, plus library metadata.
+// Argument checking happens here, before any launch; the kernels live in gemv_decode.cu
+// (M <= 16, HBM-bound) and gemm_tc.cu (tcgen05 tensor cores).
+#include "duq_common.cuh"
+
+namespace duq4 {
+int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
+int gemm_tc_launch(bool int4, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
+int tc_status_read(cudaStream_t st, int32_t *out);
+int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
+                            void *z1, void *s2, void *z2, cudaStream_t st);
+
+constexpr uint32_t kSmallM = 16;  // at or below this many tokens the layer is weight-bandwidth bound
+
+static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParams *p) {
+    *p = EpiParams{};
+    if (!e) {
+        p->mode = DUQ4_MODE_NONE;
+        p->ldo = N;
+        return DUQ4_OK;
+    }
+    if (e->mode < DUQ4_MODE_NONE || e->mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
+    p->mode = e->mode;
+    p->col_offset = e->col_offset;
+    p->s_row = (const __half *)e->scale_row;
+    p->z_row = (const __half *)e->zeros_row;
+    p->s_col1 = (const __half *)e->scale_col_1;
+    p->z_col1 = (const __half *)e->zeros_col_1;
+    p->s_col2 = (const __half *)e->scale_col_2;
+    p->z_col2 = (const __half *)e->zeros_col_2;
+    p->bias = (const __half *)e->bias;
+    p->ldo = e->ldo ? e->ldo : N;
+    if (p->ldo < N) return DUQ4_ERR_SHAPE;
+    if (e->mode == DUQ4_MODE_NONE) return DUQ4_OK;
+    const bool asym = e->mode == DUQ4_MODE_ASYM || e->mode == DUQ4_MODE_ASYM_DUAL;
+    const bool dual = e->mode == DUQ4_MODE_SYM_DUAL || e->mode == DUQ4_MODE_ASYM_DUAL;
+    if (need_row && (!p->s_row || (asym && !p->z_row))) return DUQ4_ERR_NULL;
+    if (!p->s_col1 || (asym && !p->z_col1)) return DUQ4_ERR_NULL;
+    if (dual && (!p->s_col2 || (e->mode == DUQ4_MODE_ASYM_DUAL && !p->z_col2))) return DUQ4_ERR_NULL;
+    if (!asym) p->z_row = nullptr;
+    return DUQ4_OK;
+}
+
+static int linear_dispatch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                           const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+    if (!A || !W) return DUQ4_ERR_NULL;
+    if (p.mode != DUQ4_MODE_NONE && !out) return DUQ4_ERR_NULL;
+    if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
+    if (M == 0 || N == 0 || batch == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (M <= kSmallM) return gemv_w4a4_launch(A, W, M, N, K, batch, p, out, acc_out, st);
+    return gemm_tc_launch(true, A, W, M, N, K, batch, p, out, acc_out, st);
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace duq4
+
+using namespace duq4;
+
+extern "C" {
+
+const char *duq4_version(void) { return "duq4-b200 0.1 (sm_100a)"; }
+
+const char *duq4_error_string(int status) {
+    switch (status) {
+        case DUQ4_OK: return "ok";
+        case DUQ4_ERR_NULL: return "a required pointer is NULL";
+        case DUQ4_ERR_SHAPE: return "unsupported shape (zero, not a required multiple, or too large)";
+        case DUQ4_ERR_MODE: return "unknown quantizer/epilogue mode";
+        case DUQ4_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+        case DUQ4_ERR_ALIGN: return "pointer not 16-byte aligned";
+        case DUQ4_ERR_DEVICE: return "device or driver does not provide what the kernel needs";
+        case DUQ4_ERR_TIMEOUT: return "a bounded device-side wait expired";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown duq4 status";
+    }
+}
+
+int duq4_dual_quant_col_k(void) { return DUQ4_QUANT_COL_K; }
+
+int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
+    EpiParams p{};
+    p.mode = DUQ4_MODE_NONE;
+    p.ldo = N;
+    return linear_dispatch(A, B, M, N, K, 1, p, nullptr, C, (cudaStream_t)stream);
+}
+
+int duq4_matmul_8bit(const int8_t *A, const int8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
+    if (!A || !B || !C) return DUQ4_ERR_NULL;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 16 != 0) return DUQ4_ERR_SHAPE;
+    EpiParams p{};
+    p.mode = DUQ4_MODE_NONE;
+    p.ldo = N;
+    return gemm_tc_launch(false, A, B, M, N, K, 1, p, nullptr, C, (cudaStream_t)stream);
+}
+
+int duq4_batch_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C,
+                           uint32_t batch_count, void *stream) {
+    EpiParams p{};
+    p.mode = DUQ4_MODE_NONE;
+    p.ldo = N;
+    return linear_dispatch(A, B, M, N, K, batch_count, p, nullptr, C, (cudaStream_t)stream);
+}
+
+int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, const duq4_epilogue *epi,
+                     void *out, int32_t *acc_out, void *stream) {
+    EpiParams p;
+    int rc = check_epi(epi, N, true, &p);
+    if (rc) return rc;
+    return linear_dispatch(A, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
+}
+
+int duq4_linear_w4a4_batched(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch_count,
+                             const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream) {
+    EpiParams p;
+    int rc = check_epi(epi, N, true, &p);
+    if (rc) return rc;
+    if (p.ldo != N) return DUQ4_ERR_SHAPE;  // batched outputs are dense [batch, M, N]
+    p.row_vec_stride = M;
+    p.col_vec_stride = N;
+    return linear_dispatch(A, W, M, N, K, batch_count, p, out, acc_out, (cudaStream_t)stream);
+}
+
+size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K) {
+    // codes [M, K/2] then four fp16 vectors [M] (scale_1, zeros_1, scale_2, zeros_2), each 256-byte aligned
+    return align_up((size_t)M * (K / 2), 256) + 4 * align_up((size_t)M * 2, 256);
+}
+
+int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                               float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
+                               size_t workspace_bytes, void *stream) {
+    if (!x || !W || !out || !epi) return DUQ4_ERR_NULL;
+    if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0 ||
+        workspace_bytes < duq4_linear_from_fp16_workspace_bytes(M, K))
+        return DUQ4_ERR_WORKSPACE;
+    EpiParams p;
+    int rc = check_epi(epi, N, false, &p);
+    if (rc) return rc;
+    if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
+    uint8_t *ws = (uint8_t *)workspace;
+    uint8_t *codes = ws;
+    size_t off = align_up((size_t)M * (K / 2), 256), vec = align_up((size_t)M * 2, 256);
+    void *s1 = ws + off, *z1 = ws + off + vec, *s2 = ws + off + 2 * vec, *z2 = ws + off + 3 * vec;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, codes, s1, z1, s2, z2, st);
+    if (rc) return rc;
+    const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
+    const bool act_asym = act_mode == DUQ4_MODE_ASYM || act_mode == DUQ4_MODE_ASYM_DUAL;
+    if (epi_asym && !act_asym) return DUQ4_ERR_MODE;  // an asymmetric epilogue needs per-token zero-points
+    p.s_row = (const __half *)s1;
+    p.z_row = epi_asym ? (const __half *)z1 : nullptr;
+    return linear_dispatch(codes, W, M, N, K, 1, p, out, nullptr, st);
+}
+
+int duq4_last_device_status(void *stream, int32_t *status_out) {
+    if (!status_out) return DUQ4_ERR_NULL;
+    return tc_status_read((cudaStream_t)stream, status_out);
+}
+
+}  // extern "C"

@@ -1,0 +1,110 @@
+// Shared device/host helpers for libduq4 (sm_100a only).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/duq4.h"
+
+namespace duq4 {
+
+// Clamp bounds of the reference (include/common.h:53-57 there). The symmetric upper bound
+// is written `(7 - 1e-8)` in the reference and truncates to 6; codes must match it.
+constexpr int kQminSym = -8;
+constexpr int kQmaxSym = 6;
+constexpr int kQminAsym = 0;
+constexpr int kQmaxAsym = 15;
+constexpr int kQmaxAsym8 = 126;  // src/kernels/quant.cu:241-242 of the reference
+constexpr uint32_t kColK = DUQ4_QUANT_COL_K;
+
+__host__ __device__ inline uint32_t cdiv(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+inline int launch_status() {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    return (int)e;
+}
+
+__device__ __forceinline__ int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }
+
+// One symmetric code: clamp(rn(x / s), -8, 6). __hdiv is the same intrinsic the reference
+// kernel calls, so codes agree bit for bit with it.
+__device__ __forceinline__ int code_sym(__half x, __half s) {
+    return clampi(__half2int_rn(__hdiv(x, s)), kQminSym, kQmaxSym);
+}
+// Asymmetric, single scale: rn(x/s) + rn(z).
+__device__ __forceinline__ int code_asym(__half x, __half s, int zi) {
+    return clampi(__half2int_rn(__hdiv(x, s)) + zi, kQminAsym, kQmaxAsym);
+}
+// Asymmetric, dual scheme: rn(x/s + z), the add rounded to fp16 first.
+__device__ __forceinline__ int code_asym_dual(__half x, __half s, __half z) {
+    return clampi(__half2int_rn(__hadd_rn(__hdiv(x, s), z)), kQminAsym, kQmaxAsym);
+}
+
+// Epilogue parameters as the kernels see them.
+struct EpiParams {
+    int mode;
+    uint32_t col_offset;
+    const __half *s_row, *z_row, *s_col1, *z_col1, *s_col2, *z_col2, *bias;
+    uint32_t ldo;
+    // batched launches: element strides between consecutive problems
+    uint32_t row_vec_stride, col_vec_stride;
+};
+
+// Epilogue operands of problem `b` of a batched launch.
+__host__ __device__ inline EpiParams epi_for_batch(EpiParams p, uint32_t b) {
+    size_t ro = (size_t)b * p.row_vec_stride, co = (size_t)b * p.col_vec_stride;
+    if (p.s_row) p.s_row += ro;
+    if (p.z_row) p.z_row += ro;
+    if (p.s_col1) p.s_col1 += co;
+    if (p.z_col1) p.z_col1 += co;
+    if (p.s_col2) p.s_col2 += co;
+    if (p.z_col2) p.z_col2 += co;
+    if (p.bias) p.bias += co;
+    return p;
+}
+
+// Column-side operands of one output column, resolved once per column.
+struct ColTerms {
+    __half s, z, b;
+    bool has_bias;
+};
+
+__device__ __forceinline__ ColTerms load_col_terms(const EpiParams &p, uint32_t c) {
+    ColTerms t;
+    t.z = __ushort_as_half(0);
+    t.b = __ushort_as_half(0);
+    t.s = __ushort_as_half(0);
+    uint32_t gc = c + p.col_offset;
+    switch (p.mode) {
+        case DUQ4_MODE_SYM: t.s = p.s_col1[c]; break;
+        case DUQ4_MODE_SYM_DUAL: t.s = gc < kColK ? p.s_col1[c] : p.s_col2[c]; break;
+        case DUQ4_MODE_ASYM: t.s = p.s_col1[c]; t.z = p.z_col1[c]; break;
+        case DUQ4_MODE_ASYM_DUAL:
+            t.s = gc == 0 ? p.s_col1[c] : p.s_col2[c];
+            t.z = gc == 0 ? p.z_col1[c] : p.z_col2[c];
+            break;
+        default: break;
+    }
+    t.has_bias = p.bias != nullptr;
+    if (t.has_bias) t.b = p.bias[c];
+    return t;
+}
+
+// The reference dequant arithmetic, one rounding per fp16 operation, explicit .rn forms so
+// that no multiply is contracted into an fma with the bias add:
+//   sym : (s_row * s_col) * half(acc)
+//   asym: (s_row * s_col) * ((half(acc) - z_row) - z_col)
+__device__ __forceinline__ __half dequant_one(int mode, int acc, __half sr, __half zr, const ColTerms &t) {
+    __half e = __int2half_rn(acc);
+    __half ss = __hmul_rn(sr, t.s);
+    __half v;
+    if (mode == DUQ4_MODE_ASYM || mode == DUQ4_MODE_ASYM_DUAL)
+        v = __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), t.z));
+    else
+        v = __hmul_rn(ss, e);
+    if (t.has_bias) v = __hadd_rn(v, t.b);
+    return v;
+}
+
+}  // namespace duq4

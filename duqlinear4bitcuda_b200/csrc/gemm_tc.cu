@@ -1,0 +1,574 @@
+// Tensor-core integer GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T with the dequant epilogue.
+//
+// Replaces the reference's CUTLASS Sm80 GEMMs (src/kernels/gemm.cu:8-43 int4, :46-81 int8,
+// :83-117 batched) and, when an epilogue mode is given, the dequant launch and bias add
+// that follow them in the module forwards (qlinear4bit/nn/linear.py:42-56 etc.).
+//
+// Blackwell has no 4-bit integer MMA, so the int4 path is:
+//   TMA (cp.async.bulk.tensor, no multicast) : packed int4 tiles  -> shared memory
+//   unpack warps                             : nibble -> int8 (value 16*s4), written in the
+//                                              K-major 128B-swizzled layout UMMA expects
+//   one thread                               : tcgen05.mma.kind::i8, int32 accumulators in TMEM
+//   epilogue warps                           : tcgen05.ld -> (>>8) -> fp16 dequant -> global
+// Both operands carry the factor 16, so accumulators are exactly 256x the true sums and the
+// epilogue shifts them back (|sum| <= 64*K*256 < 2^31 for K < 131072, checked by the host).
+// Inside a 128-element K block the unpack permutes K (low nibbles of a 16-byte packed chunk
+// form one 16-byte int8 chunk, high nibbles the next); A and B share the permutation.
+// The int8 path (matmul_8bit) lets TMA write the swizzled tiles directly and skips the unpack.
+//
+// Persistent kernel: one CTA per SM walks tiles in M-fastest order (CTAs running together
+// share B tiles and all of A through L2). TMEM holds two accumulator buffers so the
+// epilogue of tile i overlaps the main loop of tile i+1. Every mbarrier wait is bounded
+// (1 s of %globaltimer); on expiry the CTA raises a status word and leaves in order.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "duq_common.cuh"
+
+namespace duq4 {
+
+__device__ int g_tc_status = 0;  // 0 = ok, else code of the wait that expired
+
+namespace tc {
+
+constexpr int BM = 128;          // rows of A per tile = TMEM lanes
+constexpr int BK = 128;          // K elements per pipeline stage (= one 128-byte swizzle row of int8)
+constexpr int kUnpackWarps = 4;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps);
+constexpr uint64_t kWaitLimitNs = 1000000000ull;
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when the CTA is aborting (this or another wait expired).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            uint64_t now = globaltimer();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand descriptor: rows of 128 bytes, 8-row groups 1024 bytes
+// apart (stride byte offset), version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;               // leading byte offset (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024u >> 4) << 32;    // stride byte offset
+    d |= (uint64_t)1 << 46;               // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;               // SWIZZLE_128B
+    return d;
+}
+// kind::i8 instruction descriptor: D = s32, A = B = signed int8, both K-major, no saturation.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return w & 0xF0F0F0F0u; }
+
+template <bool INT4, int BN>
+struct Cfg {
+    static constexpr int kPackedStage = INT4 ? (BM + BN) * (BK / 2) : 0;
+    static constexpr int kUnpackedStage = (BM + BN) * BK;
+    static constexpr int NPK = INT4 ? 4 : 1;
+    static constexpr int NUP = INT4 ? (BN == 256 ? 2 : 4) : (BN == 256 ? 4 : 6);
+    static constexpr int kColTerms = kEpiWarps * 3 * BN * 2;  // per epilogue warp: (scale, zero, bias) x BN halves
+    static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + 256 /*barriers*/;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
+};
+
+struct Args {
+    uint32_t M, N, K, batch;  // K in elements
+    uint32_t tiles_m, tiles_n;
+    EpiParams epi;
+    __half *out;
+    int32_t *acc_out;
+};
+
+template <bool INT4, int BN>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                              const __grid_constant__ CUtensorMap tmB, const Args a) {
+    using C = Cfg<INT4, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gbase = smem_raw + (base - raw);
+    const uint32_t up0 = base;                                   // unpacked stages (1024-aligned each)
+    const uint32_t pk0 = up0 + C::NUP * C::kUnpackedStage;       // packed stages
+    const uint32_t ct_off = C::NUP * C::kUnpackedStage + C::NPK * C::kPackedStage;
+    __half *colterms = reinterpret_cast<__half *>(gbase + ct_off);
+    const uint32_t bar0 = base + ct_off + C::kColTerms;
+    // barrier map (8 bytes each)
+    auto pk_full = [&](int s) { return bar0 + 8u * s; };
+    auto pk_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+    auto up_full = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto up_empty = [&](int s) { return bar0 + 8u * (14 + s); };
+    auto acc_full = [&](int s) { return bar0 + 8u * (20 + s); };
+    auto acc_empty = [&](int s) { return bar0 + 8u * (22 + s); };
+    const uint32_t drain_bar = bar0 + 8u * 24;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t num_tiles = a.tiles_m * a.tiles_n * a.batch;
+    const uint32_t ksteps = (a.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(pk_full(s), 1);
+            mbar_init(pk_empty(s), kUnpackWarps);
+        }
+        for (int s = 0; s < 6; ++s) {
+            mbar_init(up_full(s), INT4 ? kUnpackWarps : 1);
+            mbar_init(up_empty(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(acc_full(s), 1);
+            mbar_init(acc_empty(s), kEpiWarps);
+        }
+        mbar_init(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;  // global stage counter
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t per_b = a.tiles_m * a.tiles_n;
+                uint32_t b = tile / per_b, r = tile % per_b;
+                uint32_t tn = r / a.tiles_m, tm = r % a.tiles_m;
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    if (INT4) {
+                        uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
+                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, 1))) break;
+                        uint32_t dst = pk0 + s * C::kPackedStage;
+                        mbar_expect_tx(pk_full(s), C::kPackedStage);
+                        tma_load_3d(dst, &tmA, pk_full(s), ks * (BK / 2), tm * BM, b);
+                        tma_load_3d(dst + BM * (BK / 2), &tmB, pk_full(s), ks * (BK / 2), tn * BN, b);
+                    } else {
+                        uint32_t s = it % C::NUP, ph = (it / C::NUP) & 1;
+                        if (!(ok = mbar_wait(up_empty(s), ph ^ 1, abortp, 1))) break;
+                        uint32_t dst = up0 + s * C::kUnpackedStage;
+                        mbar_expect_tx(up_full(s), C::kUnpackedStage);
+                        tma_load_3d(dst, &tmA, up_full(s), ks * BK, tm * BM, b);
+                        tma_load_3d(dst + BM * BK, &tmB, up_full(s), ks * BK, tn * BN, b);
+                    }
+                }
+            }
+            if (!ok) {  // give copies already in flight time to land before the CTA retires
+                uint64_t t0 = globaltimer();
+                while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            uint32_t it = 0, lt = 0;
+            bool ok = true, issued = false;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+                uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
+                if (!(ok = mbar_wait(acc_empty(buf), aph ^ 1, abortp, 2))) break;
+                tc_fence_after();
+                uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    uint32_t s = it % C::NUP, ph = (it / C::NUP) & 1;
+                    if (!(ok = mbar_wait(up_full(s), ph, abortp, 3))) break;
+                    tc_fence_after();
+                    uint32_t sa = up0 + s * C::kUnpackedStage, sb = sa + BM * BK;
+                    uint64_t da = make_desc(sa), db = make_desc(sb);
+#pragma unroll
+                    for (int kk = 0; kk < BK / 32; ++kk)
+                        umma_i8(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (ks | kk) != 0);
+                    issued = true;
+                    umma_commit(up_empty(s));  // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full(buf));
+            }
+            if (!ok && issued) {  // aborting: let issued MMAs finish before TMEM is released
+                umma_commit(drain_bar);
+                uint64_t t0 = globaltimer();
+                while (!mbar_try(drain_bar, 0) && globaltimer() - t0 < kWaitLimitNs) __nanosleep(1000);
+            }
+        }
+    } else if (warp < 2 + kEpiWarps) {
+        // ---------------- epilogue ----------------
+        const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+        const uint32_t row_in_tile = quad * 32 + lane;
+        const int mode = a.epi.mode;
+        const uint32_t shift = INT4 ? 8 : 0;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+            uint32_t per_b = a.tiles_m * a.tiles_n;
+            uint32_t b = tile / per_b, r = tile % per_b;
+            uint32_t tn = r / a.tiles_m, tm = r % a.tiles_m;
+            uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
+            const uint32_t n0 = tn * BN;
+            EpiParams pb = a.epi;
+            // Each epilogue warp keeps its own copy of the tile's column terms, so the four
+            // warps never have to meet at a barrier (a barrier a warp could miss when the CTA
+            // is leaving early).
+            __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
+            __syncwarp();  // previous tile's readers are done
+            if (mode != DUQ4_MODE_NONE) {
+                size_t co = (size_t)b * pb.col_vec_stride;
+                if (pb.s_col1) pb.s_col1 += co;
+                if (pb.z_col1) pb.z_col1 += co;
+                if (pb.s_col2) pb.s_col2 += co;
+                if (pb.z_col2) pb.z_col2 += co;
+                if (pb.bias) pb.bias += co;
+                for (int c = lane; c < BN; c += 32) {
+                    uint32_t n = n0 + c;
+                    ColTerms t;
+                    t.s = t.z = t.b = __ushort_as_half(0);
+                    if (n < a.N) t = load_col_terms(pb, n);
+                    cs[c] = t.s;
+                    cz[c] = t.z;
+                    cb[c] = t.b;
+                }
+            }
+            __syncwarp();
+            if (!(ok = mbar_wait(acc_full(buf), aph, abortp, 4))) break;
+            tc_fence_after();
+
+            const uint32_t m = tm * BM + row_in_tile;
+            const bool row_ok = m < a.M;
+            __half sr = __ushort_as_half(0), zr = __ushort_as_half(0);
+            if (row_ok && mode != DUQ4_MODE_NONE) {
+                sr = pb.s_row[(size_t)b * pb.row_vec_stride + m];
+                if (pb.z_row) zr = pb.z_row[(size_t)b * pb.row_vec_stride + m];
+            }
+            const bool has_bias = pb.bias != nullptr;
+            const bool asym = mode == DUQ4_MODE_ASYM || mode == DUQ4_MODE_ASYM_DUAL;
+            __half *orow = a.out ? a.out + ((size_t)b * a.M + m) * pb.ldo + n0 : nullptr;
+            int32_t *arow = a.acc_out ? a.acc_out + ((size_t)b * a.M + m) * a.N + n0 : nullptr;
+            const bool vec_ok = ((pb.ldo & 7u) == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0);
+            const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t v[32];
+                __syncwarp();  // tcgen05.ld is warp-collective
+                tmem_ld32(taddr + ch * 32, v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                const uint32_t c0 = ch * 32;
+                if (n0 + c0 >= a.N) continue;
+                const bool full = n0 + c0 + 32 <= a.N;
+                int acc[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = ((int)v[j]) >> shift;
+                if (arow) {
+                    if (full && avec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<int4 *>(arow + c0 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < a.N) arow[c0 + j] = acc[j];
+                    }
+                }
+                if (mode != DUQ4_MODE_NONE) {
+                    __align__(16) __half o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        __half e = __int2half_rn(acc[j]);
+                        __half ss = __hmul_rn(sr, cs[c0 + j]);
+                        __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
+                        if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
+                        o[j] = val;
+                    }
+                    if (full && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *reinterpret_cast<uint4 *>(orow + c0 + j) = *reinterpret_cast<const uint4 *>(&o[j]);
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+    } else if (INT4) {
+        // ---------------- unpack warps: packed int4 -> swizzled int8 ----------------
+        const int ut = (warp - 2 - kEpiWarps) * 32 + lane;  // 0..127
+        constexpr int kChunks = (BM + BN) * 4;              // 16-byte packed chunks per stage
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
+                uint32_t u = it % C::NUP, uph = (it / C::NUP) & 1;
+                if (!(ok = mbar_wait(pk_full(s), ph, abortp, 5))) break;
+                if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, 6))) break;
+                const uint32_t src = pk0 + s * C::kPackedStage, dst = up0 + u * C::kUnpackedStage;
+#pragma unroll 4
+                for (int idx = ut; idx < kChunks; idx += kUnpackWarps * 32) {
+                    uint32_t w0, w1, w2, w3;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                                 : "r"(src + idx * 16));
+                    const uint32_t row = idx >> 2, c = idx & 3, sw = row & 7;
+                    const uint32_t rowaddr = dst + row * 128;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowaddr + (((2 * c) ^ sw) << 4)),
+                                 "r"(nib_lo(w0)), "r"(nib_lo(w1)), "r"(nib_lo(w2)), "r"(nib_lo(w3))
+                                 : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowaddr + (((2 * c + 1) ^ sw) << 4)),
+                                 "r"(nib_hi(w0)), "r"(nib_hi(w1)), "r"(nib_hi(w2)), "r"(nib_hi(w3))
+                                 : "memory");
+                }
+                fence_proxy_async();  // make the generic-proxy writes visible to the MMA (async proxy)
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(pk_empty(s));
+                    mbar_arrive(up_full(u));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void *ptr;
+    uint64_t kbytes, rows, batch;
+    uint32_t box_k, box_rows, swizzle;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && kbytes == o.kbytes && rows == o.rows && batch == o.batch && box_k == o.box_k &&
+               box_rows == o.box_rows && swizzle == o.swizzle;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = std::hash<const void *>()(k.ptr);
+        auto mix = [&](uint64_t v) { h ^= std::hash<uint64_t>()(v) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+        mix(k.kbytes); mix(k.rows); mix(k.batch); mix(k.box_k); mix(k.box_rows); mix(k.swizzle);
+        return h;
+    }
+};
+
+// Byte tensor [batch, rows, kbytes] (kbytes contiguous); box = [1, box_rows, box_k].
+static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
+                   bool swizzle128, CUtensorMap *out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, kbytes, rows, batch, box_k, box_rows, swizzle128 ? 1u : 0u};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return DUQ4_OK;
+        }
+    }
+    EncodeFn fn = encode_fn();
+    if (!fn) return DUQ4_ERR_DEVICE;
+    cuuint64_t dims[3] = {kbytes, rows, batch};
+    cuuint64_t strides[2] = {kbytes, kbytes * rows};
+    cuuint32_t box[3] = {box_k, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return DUQ4_ERR_SHAPE;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (cache.size() > 4096) cache.clear();
+        cache[key] = m;
+    }
+    *out = m;
+    return DUQ4_OK;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <bool INT4, int BN>
+static int launch(const void *A, const void *B, const Args &args, cudaStream_t st) {
+    using C = Cfg<INT4, BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<INT4, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    const uint64_t kbytes = INT4 ? args.K / 2 : args.K;
+    const uint32_t box_k = INT4 ? BK / 2 : BK;
+    CUtensorMap ma, mb;
+    int rc = get_map(A, kbytes, args.M, args.batch, box_k, BM, !INT4, &ma);
+    if (rc) return rc;
+    rc = get_map(B, kbytes, args.N, args.batch, box_k, BN, !INT4, &mb);
+    if (rc) return rc;
+    uint32_t tiles = args.tiles_m * args.tiles_n * args.batch;
+    uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
+    gemm_tc_kernel<INT4, BN><<<grid, kThreads, C::kSmem, st>>>(ma, mb, args);
+    return launch_status();
+}
+
+}  // namespace tc
+
+// A [batch,M,K] x B [batch,N,K]^T. int4: A,B packed (K/2 bytes per row); int8 otherwise.
+int gemm_tc_launch(bool int4, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+    if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    if (int4 && K >= 131072u) return DUQ4_ERR_SHAPE;  // 256x-scaled accumulators must fit int32
+    tc::Args a{};
+    a.M = M; a.N = N; a.K = K; a.batch = batch;
+    a.epi = p;
+    a.out = (__half *)out;
+    a.acc_out = acc_out;
+    a.tiles_m = cdiv(M, tc::BM);
+    // 256-wide tiles halve the A-operand shared-memory traffic per MMA; fall back to 128
+    // when that would leave most SMs without a tile.
+    const bool wide = (uint64_t)a.tiles_m * cdiv(N, 256) * batch >= 120 || N > 128 * 148;
+    if (wide) {
+        a.tiles_n = cdiv(N, 256);
+        return int4 ? tc::launch<true, 256>(A, B, a, st) : tc::launch<false, 256>(A, B, a, st);
+    }
+    a.tiles_n = cdiv(N, 128);
+    return int4 ? tc::launch<true, 128>(A, B, a, st) : tc::launch<false, 128>(A, B, a, st);
+}
+
+int tc_status_read(cudaStream_t st, int32_t *out) {
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    *out = v;
+    if (v != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+    }
+    return DUQ4_OK;
+}
+
+}  // namespace duq4

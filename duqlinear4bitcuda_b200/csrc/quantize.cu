@@ -1,0 +1,404 @@
+// Per-token int4 activation quantizers (HBM-bound).
+//
+// Two families:
+//   *_given : scales (and zero-points) supplied by the caller -- the reference's
+//             sym/asym/sym_dual/asym_dual quantize launchers (src/kernels/quant.cu:12-61,
+//             :100-147 and src/kernels/quant2.cu:10-60, :102-156 of the reference).
+//   *_fused : row statistics, scale(/zero) computation and coding in ONE pass over x, which
+//             replaces the 4-7 torch kernels of the reference's quantizer modules
+//             (qlinear4bit/nn/quantizer.py:13, :27-31) plus the quantize launch.
+//
+// Data movement: 128-bit loads of 8 halves per thread, 32-bit stores of 8 codes; in the
+// fused kernels a CTA owns one token and keeps it in registers between the reduction and
+// the coding pass, so x is read from HBM exactly once.
+#include "duq_common.cuh"
+
+namespace duq4 {
+
+enum { QSYM = DUQ4_MODE_SYM, QSYM_DUAL = DUQ4_MODE_SYM_DUAL, QASYM = DUQ4_MODE_ASYM, QASYM_DUAL = DUQ4_MODE_ASYM_DUAL };
+
+struct RowQ {  // per-row quantization terms
+    __half s1, z1, s2, z2;
+    int zi1;  // rn(z1) for the single-scale asymmetric scheme
+};
+
+template <int MODE>
+__device__ __forceinline__ int code_at(__half x, uint32_t col, const RowQ &r) {
+    if (MODE == QSYM) return code_sym(x, r.s1);
+    if (MODE == QSYM_DUAL) return code_sym(x, col < kColK ? r.s1 : r.s2);
+    if (MODE == QASYM) return code_asym(x, r.s1, r.zi1);
+    return code_asym_dual(x, col < kColK ? r.s1 : r.s2, col < kColK ? r.z1 : r.z2);
+}
+
+// 8 halves (one uint4) starting at column col0 -> 8 nibbles (one uint32), low nibble first.
+template <int MODE>
+__device__ __forceinline__ uint32_t code8(const uint4 &v, uint32_t col0, const RowQ &r) {
+    const __half *h = reinterpret_cast<const __half *>(&v);
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out |= (uint32_t)(code_at<MODE>(h[i], col0 + i, r) & 0xF) << (4 * i);
+    return out;
+}
+
+template <int MODE>
+__device__ __forceinline__ RowQ load_rowq(const __half *s1, const __half *z1, const __half *s2, const __half *z2,
+                                          uint32_t row) {
+    RowQ r;
+    r.s1 = s1[row];
+    r.z1 = r.z2 = r.s2 = __ushort_as_half(0);
+    r.zi1 = 0;
+    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) r.s2 = s2[row];
+    if (MODE == QASYM || MODE == QASYM_DUAL) r.z1 = z1[row];
+    if (MODE == QASYM_DUAL) r.z2 = z2[row];
+    if (MODE == QASYM) r.zi1 = __half2int_rn(r.z1);
+    return r;
+}
+
+// ---- scales given: vector path (colsSrc % 8 == 0, colsDst == colsSrc/2, aligned) -------
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_given_vec_kernel(const __half *__restrict__ x, const __half *__restrict__ s1,
+                                                              const __half *__restrict__ z1,
+                                                              const __half *__restrict__ s2,
+                                                              const __half *__restrict__ z2, uint32_t rows,
+                                                              uint32_t vec_per_row, uint8_t *__restrict__ q) {
+    const size_t total = (size_t)rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t row = (uint32_t)(i / vec_per_row);
+        uint32_t v = (uint32_t)(i - (size_t)row * vec_per_row);
+        RowQ r = load_rowq<MODE>(s1, z1, s2, z2, row);
+        uint4 d = __ldg(reinterpret_cast<const uint4 *>(x) + i);
+        reinterpret_cast<uint32_t *>(q)[i] = code8<MODE>(d, v * 8, r);
+    }
+}
+
+// ---- scales given: generic path, one thread per output byte (any colsSrc / colsDst) ----
+template <int MODE>
+__global__ void quant_given_scalar_kernel(const __half *__restrict__ x, const __half *__restrict__ s1,
+                                          const __half *__restrict__ z1, const __half *__restrict__ s2,
+                                          const __half *__restrict__ z2, uint32_t rows, uint32_t colsSrc,
+                                          uint32_t colsDst, uint8_t *__restrict__ q) {
+    const size_t total = (size_t)rows * colsDst;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t row = (uint32_t)(i / colsDst);
+        uint32_t cd = (uint32_t)(i - (size_t)row * colsDst);
+        if (cd * 2 >= colsSrc) continue;  // the reference leaves such bytes unwritten
+        RowQ r = load_rowq<MODE>(s1, z1, s2, z2, row);
+        uint32_t b = 0;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            uint32_t col = cd * 2 + k;
+            if (col < colsSrc) b |= (uint32_t)(code_at<MODE>(x[(size_t)row * colsSrc + col], col, r) & 0xF) << (4 * k);
+        }
+        q[i] = (uint8_t)b;
+    }
+}
+
+// ---- fused ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Row statistics gathered by one thread. Symmetric schemes track max|x| (a: columns < 10
+// for the dual scheme, b: the rest / everything); asymmetric ones track min and max.
+struct Stats {
+    float a_hi, a_lo, b_hi, b_lo;
+};
+template <int MODE>
+__device__ __forceinline__ void stats_init(Stats &s) {
+    if (MODE == QSYM || MODE == QSYM_DUAL) {
+        s.a_hi = s.b_hi = 0.f;
+        s.a_lo = s.b_lo = 0.f;
+    } else {
+        s.a_hi = s.b_hi = -INFINITY;
+        s.a_lo = s.b_lo = INFINITY;
+    }
+}
+template <int MODE>
+__device__ __forceinline__ void stats_add(Stats &s, float v, uint32_t col) {
+    if (MODE == QSYM) {
+        s.b_hi = fmaxf(s.b_hi, fabsf(v));
+    } else if (MODE == QSYM_DUAL) {
+        if (col < kColK) s.a_hi = fmaxf(s.a_hi, fabsf(v)); else s.b_hi = fmaxf(s.b_hi, fabsf(v));
+    } else if (MODE == QASYM) {
+        s.b_hi = fmaxf(s.b_hi, v);
+        s.b_lo = fminf(s.b_lo, v);
+    } else {
+        if (col < kColK) { s.a_hi = fmaxf(s.a_hi, v); s.a_lo = fminf(s.a_lo, v); }
+        else { s.b_hi = fmaxf(s.b_hi, v); s.b_lo = fminf(s.b_lo, v); }
+    }
+}
+
+// Block-wide reduction of Stats over 256 threads; result valid in every thread.
+template <int MODE>
+__device__ __forceinline__ void stats_reduce(Stats &s, float (*sm)[4]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    s.b_hi = warp_max(s.b_hi);
+    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) s.a_hi = warp_max(s.a_hi);
+    if (MODE == QASYM || MODE == QASYM_DUAL) s.b_lo = warp_min(s.b_lo);
+    if (MODE == QASYM_DUAL) s.a_lo = warp_min(s.a_lo);
+    if (lane == 0) { sm[warp][0] = s.a_hi; sm[warp][1] = s.a_lo; sm[warp][2] = s.b_hi; sm[warp][3] = s.b_lo; }
+    __syncthreads();
+    Stats r;
+    stats_init<MODE>(r);
+    for (int w = 0; w < nwarp; ++w) {
+        r.a_hi = fmaxf(r.a_hi, sm[w][0]);
+        r.a_lo = fminf(r.a_lo, sm[w][1]);
+        r.b_hi = fmaxf(r.b_hi, sm[w][2]);
+        r.b_lo = fminf(r.b_lo, sm[w][3]);
+    }
+    s = r;
+}
+
+// torch semantics of the quantizer modules, each op rounded to fp16 (opmath fp32):
+//   sym : scale = half(half(amax) * (1/7)) * clip            (nn/quantizer.py:13)
+//   asym: scale = half(half(max - min) * (1/15)); zero = rint(half(-min / scale))   (:27-31)
+// torch's CUDA division of an fp16 tensor by a host scalar multiplies by the fp32
+// reciprocal; for every fp16 input that equals the correctly rounded quotient by 7 or 15.
+__device__ __forceinline__ __half sym_scale(float amax, float clip) {
+    __half s = __float2half_rn(amax * (1.0f / 7.0f));
+    return __float2half_rn(__half2float(s) * clip);
+}
+__device__ __forceinline__ void asym_scale_zero(float mn, float mx, __half &s, __half &z) {
+    __half d = __float2half_rn(mx - mn);
+    s = __float2half_rn(__half2float(d) * (1.0f / 15.0f));
+    __half zq = __float2half_rn(__fdiv_rn(-mn, __half2float(s)));
+    z = __float2half_rn(rintf(__half2float(zq)));
+}
+
+template <int MODE>
+__device__ __forceinline__ RowQ rowq_from_stats(const Stats &s, float clip) {
+    RowQ r;
+    r.s1 = r.s2 = r.z1 = r.z2 = __ushort_as_half(0);
+    r.zi1 = 0;
+    if (MODE == QSYM) {
+        r.s1 = sym_scale(s.b_hi, clip);
+    } else if (MODE == QSYM_DUAL) {
+        r.s1 = sym_scale(s.a_hi, clip);
+        r.s2 = sym_scale(s.b_hi, clip);
+    } else if (MODE == QASYM) {
+        asym_scale_zero(s.b_lo, s.b_hi, r.s1, r.z1);
+        r.zi1 = __half2int_rn(r.z1);
+    } else {
+        asym_scale_zero(s.a_lo, s.a_hi, r.s1, r.z1);
+        asym_scale_zero(s.b_lo, s.b_hi, r.s2, r.z2);
+    }
+    return r;
+}
+
+template <int MODE>
+__device__ __forceinline__ void store_rowq(const RowQ &r, uint32_t row, __half *s1, __half *z1, __half *s2, __half *z2) {
+    s1[row] = r.s1;
+    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) s2[row] = r.s2;
+    if (MODE == QASYM || MODE == QASYM_DUAL) z1[row] = r.z1;
+    if (MODE == QASYM_DUAL) z2[row] = r.z2;
+}
+
+// One CTA (256 threads) per token; the token lives in VPT uint4 registers per thread.
+// Requires cols % 8 == 0, cols <= 256*8*VPT, x 16-byte aligned.
+template <int MODE, int VPT>
+__global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__restrict__ x, uint32_t rows, uint32_t cols,
+                                                              float clip, uint8_t *__restrict__ q, __half *s1o,
+                                                              __half *z1o, __half *s2o, __half *z2o) {
+    __shared__ float sm[8][4];
+    const uint32_t nvec = cols >> 3;
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
+        uint4 d[VPT];
+        Stats st;
+        stats_init<MODE>(st);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            uint32_t v = threadIdx.x + i * 256;
+            if (v < nvec) d[i] = __ldg(xr + v);
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            uint32_t v = threadIdx.x + i * 256;
+            if (v < nvec) {
+                const __half *h = reinterpret_cast<const __half *>(&d[i]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) stats_add<MODE>(st, __half2float(h[k]), v * 8 + k);
+            }
+        }
+        __syncthreads();  // protects sm[] against the previous row's readers
+        stats_reduce<MODE>(st, sm);
+        RowQ r = rowq_from_stats<MODE>(st, clip);
+        if (threadIdx.x == 0) store_rowq<MODE>(r, row, s1o, z1o, s2o, z2o);
+        uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            uint32_t v = threadIdx.x + i * 256;
+            if (v < nvec) qr[v] = code8<MODE>(d[i], v * 8, r);
+        }
+    }
+}
+
+// Generic fused path: any cols; two passes over the row (the second one hits L2).
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_fused_scalar_kernel(const __half *__restrict__ x, uint32_t rows,
+                                                                 uint32_t cols, float clip, uint8_t *__restrict__ q,
+                                                                 __half *s1o, __half *z1o, __half *s2o, __half *z2o) {
+    __shared__ float sm[8][4];
+    const uint32_t cd = (cols + 1) >> 1;
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const __half *xr = x + (size_t)row * cols;
+        Stats st;
+        stats_init<MODE>(st);
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) stats_add<MODE>(st, __half2float(xr[c]), c);
+        __syncthreads();
+        stats_reduce<MODE>(st, sm);
+        RowQ r = rowq_from_stats<MODE>(st, clip);
+        if (threadIdx.x == 0) store_rowq<MODE>(r, row, s1o, z1o, s2o, z2o);
+        for (uint32_t b = threadIdx.x; b < cd; b += blockDim.x) {
+            uint32_t out = 0;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                uint32_t col = b * 2 + k;
+                if (col < cols) out |= (uint32_t)(code_at<MODE>(xr[col], col, r) & 0xF) << (4 * k);
+            }
+            q[(size_t)row * cd + b] = (uint8_t)out;
+        }
+    }
+}
+
+// 8-bit asymmetric quantizer of the reference's side path (src/kernels/quant.cu:245-266):
+// fp32 divide, both terms pass through fp16 before the integer rounding.
+__global__ void asym_quant8_kernel(const float *__restrict__ x, const float *__restrict__ scale,
+                                   const float *__restrict__ zeros, uint32_t rows, uint32_t cols,
+                                   int8_t *__restrict__ q) {
+    const size_t total = (size_t)rows * cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t row = (uint32_t)(i / cols);
+        float d = __fdiv_rn(x[i], scale[row]);
+        int v = __half2int_rn(__float2half_rn(d)) + __half2int_rn(__float2half_rn(zeros[row]));
+        q[i] = (int8_t)clampi(v, 0, kQmaxAsym8);
+    }
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int grid_for(size_t work_items, int block) {
+    size_t g = (work_items + block - 1) / block;
+    const size_t cap = 148 * 16;  // 16 CTAs of 256 threads per SM cover the machine; then grid-stride
+    if (g > cap) g = cap;
+    if (g == 0) g = 1;
+    return (int)g;
+}
+
+template <int MODE>
+static int launch_given(const void *x, const void *s1, const void *z1, const void *s2, const void *z2, uint32_t rows,
+                        uint32_t colsSrc, uint32_t colsDst, uint8_t *q, cudaStream_t st) {
+    if (!x || !s1 || !q) return DUQ4_ERR_NULL;
+    if ((MODE == QSYM_DUAL || MODE == QASYM_DUAL) && !s2) return DUQ4_ERR_NULL;
+    if ((MODE == QASYM || MODE == QASYM_DUAL) && !z1) return DUQ4_ERR_NULL;
+    if (MODE == QASYM_DUAL && !z2) return DUQ4_ERR_NULL;
+    if (rows == 0 || colsSrc == 0 || colsDst == 0) return DUQ4_OK;  // empty input: nothing to do
+    const __half *hx = (const __half *)x, *hs1 = (const __half *)s1, *hz1 = (const __half *)z1,
+                 *hs2 = (const __half *)s2, *hz2 = (const __half *)z2;
+    if (colsSrc % 8 == 0 && colsDst == colsSrc / 2 && aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
+        uint32_t vpr = colsSrc / 8;
+        quant_given_vec_kernel<MODE><<<grid_for((size_t)rows * vpr, 256), 256, 0, st>>>(hx, hs1, hz1, hs2, hz2, rows, vpr, q);
+    } else {
+        quant_given_scalar_kernel<MODE><<<grid_for((size_t)rows * colsDst, 256), 256, 0, st>>>(hx, hs1, hz1, hs2, hz2, rows,
+                                                                                              colsSrc, colsDst, q);
+    }
+    return launch_status();
+}
+
+template <int MODE>
+static int launch_fused(const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1, void *z1, void *s2,
+                        void *z2, cudaStream_t st) {
+    if (!x || !q || !s1) return DUQ4_ERR_NULL;
+    if ((MODE == QSYM_DUAL || MODE == QASYM_DUAL) && !s2) return DUQ4_ERR_NULL;
+    if ((MODE == QASYM || MODE == QASYM_DUAL) && !z1) return DUQ4_ERR_NULL;
+    if (MODE == QASYM_DUAL && !z2) return DUQ4_ERR_NULL;
+    if (rows == 0) return DUQ4_OK;
+    if (cols == 0) return DUQ4_ERR_SHAPE;
+    const __half *hx = (const __half *)x;
+    __half *a = (__half *)s1, *b = (__half *)z1, *c = (__half *)s2, *d = (__half *)z2;
+    uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    bool vec = cols % 8 == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 3) == 0 && cols <= 256u * 8u * 16u;
+    if (!vec) {
+        quant_fused_scalar_kernel<MODE><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+    } else if (cols <= 256u * 8u * 2u) {
+        quant_fused_vec_kernel<MODE, 2><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+    } else if (cols <= 256u * 8u * 4u) {
+        quant_fused_vec_kernel<MODE, 4><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+    } else if (cols <= 256u * 8u * 8u) {
+        quant_fused_vec_kernel<MODE, 8><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+    } else {
+        quant_fused_vec_kernel<MODE, 16><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+    }
+    return launch_status();
+}
+
+// Used by the fused linear entry point (abi.cu).
+int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
+                            void *z1, void *s2, void *z2, cudaStream_t st) {
+    switch (mode) {
+        case QSYM: return launch_fused<QSYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
+        case QSYM_DUAL: return launch_fused<QSYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
+        case QASYM: return launch_fused<QASYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
+        case QASYM_DUAL: return launch_fused<QASYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
+        default: return DUQ4_ERR_MODE;
+    }
+}
+
+}  // namespace duq4
+
+using namespace duq4;
+
+extern "C" {
+
+int duq4_sym_quant(const void *x, const void *scale, uint32_t rows, uint32_t colsSrc, uint32_t colsDst, uint8_t *q,
+                   void *stream) {
+    return launch_given<QSYM>(x, scale, nullptr, nullptr, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
+}
+int duq4_sym_dual_quant(const void *x, const void *scale_1, const void *scale_2, uint32_t rows, uint32_t colsSrc,
+                        uint32_t colsDst, uint8_t *q, void *stream) {
+    return launch_given<QSYM_DUAL>(x, scale_1, nullptr, scale_2, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
+}
+int duq4_asym_quant(const void *x, const void *scale, const void *zeros, uint32_t rows, uint32_t colsSrc,
+                    uint32_t colsDst, uint8_t *q, void *stream) {
+    return launch_given<QASYM>(x, scale, zeros, nullptr, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
+}
+int duq4_asym_dual_quant(const void *x, const void *scale_1, const void *zeros_1, const void *scale_2,
+                         const void *zeros_2, uint32_t rows, uint32_t colsSrc, uint32_t colsDst, uint8_t *q,
+                         void *stream) {
+    return launch_given<QASYM_DUAL>(x, scale_1, zeros_1, scale_2, zeros_2, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
+}
+int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros, uint32_t rows, uint32_t cols,
+                         int8_t *q, void *stream) {
+    if (!x || !scale || !zeros || !q) return DUQ4_ERR_NULL;
+    if (rows == 0 || cols == 0) return DUQ4_OK;
+    asym_quant8_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, zeros, rows, cols, q);
+    return launch_status();
+}
+
+int duq4_quantize_sym_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q, void *scale_out,
+                            void *stream) {
+    return launch_fused<QSYM>(x, rows, cols, clip_ratio, q, scale_out, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+int duq4_quantize_asym_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q, void *scale_out, void *zeros_out,
+                             void *stream) {
+    return launch_fused<QASYM>(x, rows, cols, 1.0f, q, scale_out, zeros_out, nullptr, nullptr, (cudaStream_t)stream);
+}
+int duq4_quantize_sym_dual_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q,
+                                 void *scale_1_out, void *scale_2_out, void *stream) {
+    return launch_fused<QSYM_DUAL>(x, rows, cols, clip_ratio, q, scale_1_out, nullptr, scale_2_out, nullptr,
+                                   (cudaStream_t)stream);
+}
+int duq4_quantize_asym_dual_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q, void *scale_1_out,
+                                  void *zeros_1_out, void *scale_2_out, void *zeros_2_out, void *stream) {
+    return launch_fused<QASYM_DUAL>(x, rows, cols, 1.0f, q, scale_1_out, zeros_1_out, scale_2_out, zeros_2_out,
+                                    (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,206 @@
+/*
+ * duq4.h -- C ABI of libduq4.so, the sm_100a (B200) W4A4 linear-layer library.
+ *
+ * One entry point per host launcher of the DUQLinear4bitCUDA reference
+ * (include/quant.h and include/gemm.h of that project; cited per function below as
+ * "ref:"), plus fused entry points the reference does not have. Conventions:
+ *
+ *   - every pointer is a DEVICE pointer unless the comment says otherwise; the caller
+ *     owns every buffer; nothing here allocates device memory;
+ *   - "fp16" buffers are IEEE binary16 (CUDA `half`), passed as `const void *`;
+ *   - packed int4 tensors are uint8, row-major [rows, K/2]; element 2j sits in the LOW
+ *     nibble of byte j, element 2j+1 in the HIGH nibble, two's complement
+ *     (ref: include/int4.h:86-98, qlinear4bit/tools/quantization.py:40-47);
+ *   - the trailing `stream` is a cudaStream_t (NULL = legacy default stream, which is
+ *     what every launch of the reference uses);
+ *   - return value: 0 = ok, < 0 = argument rejected before any launch (DUQ4_ERR_*),
+ *     > 0 = a cudaError_t reported by the launch.
+ *   - all functions are re-entrant; the only process-wide state is a mutex-guarded
+ *     cache of TMA descriptors keyed by (pointer, shape).
+ */
+#ifndef DUQ4_H_
+#define DUQ4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DUQ4_OK 0
+#define DUQ4_ERR_NULL (-1)        /* a required pointer is NULL */
+#define DUQ4_ERR_SHAPE (-2)       /* a dimension is zero, not a multiple the kernel needs, or too large */
+#define DUQ4_ERR_MODE (-3)        /* unknown epilogue / quantizer mode */
+#define DUQ4_ERR_WORKSPACE (-4)   /* workspace missing, too small or misaligned */
+#define DUQ4_ERR_ALIGN (-5)       /* a pointer is not aligned as required */
+#define DUQ4_ERR_DEVICE (-6)      /* not an sm_100 device / driver entry point unavailable */
+#define DUQ4_ERR_TIMEOUT (-7)     /* a bounded device-side wait gave up (see duq4_last_device_status) */
+
+/* Column split of the dual-uniform schemes (ref: include/quant.h:5, QUANT_COL_K). */
+#define DUQ4_QUANT_COL_K 10
+
+/* Quantizer / dequantizer variants. */
+#define DUQ4_MODE_NONE 0       /* no dequant: int32 accumulators only */
+#define DUQ4_MODE_SYM 1        /* ref: sym_quant_host / sym_dequant_host */
+#define DUQ4_MODE_SYM_DUAL 2   /* ref: sym_dual_quant_host / sym_dual_dequant_host */
+#define DUQ4_MODE_ASYM 3       /* ref: asym_quant_host / asym_dequant_host */
+#define DUQ4_MODE_ASYM_DUAL 4  /* ref: asym_dual_quant_host / asym_dual_dequant_host */
+
+const char *duq4_version(void);
+const char *duq4_error_string(int status);
+/* Value exported by the reference's pybind module as get_dual_quant_col_k()
+ * (ref: src/export/bindings.cpp:471-473). */
+int duq4_dual_quant_col_k(void);
+
+/* ---- quantize, scales (and zero-points) supplied by the caller ------------------------ */
+
+/* ref: include/quant.h:9-16 sym_quant_host -> src/kernels/quant.cu:12-61.
+ * q = clamp(rn(x / scale[row]), -8, 6) packed two per byte; colsDst = ceil(colsSrc/2). */
+int duq4_sym_quant(const void *x, const void *scale, uint32_t rows, uint32_t colsSrc,
+                   uint32_t colsDst, uint8_t *q, void *stream);
+/* ref: include/quant.h:29-37 sym_dual_quant_host -> src/kernels/quant2.cu:10-60.
+ * Columns < 10 use scale_1[row], the rest scale_2[row]. */
+int duq4_sym_dual_quant(const void *x, const void *scale_1, const void *scale_2, uint32_t rows,
+                        uint32_t colsSrc, uint32_t colsDst, uint8_t *q, void *stream);
+/* ref: include/quant.h:49-57 asym_quant_host -> src/kernels/quant.cu:100-147.
+ * q = clamp(rn(x/scale[row]) + rn(zeros[row]), 0, 15). */
+int duq4_asym_quant(const void *x, const void *scale, const void *zeros, uint32_t rows,
+                    uint32_t colsSrc, uint32_t colsDst, uint8_t *q, void *stream);
+/* ref: include/quant.h:92-103 asym_dual_quant_host -> src/kernels/quant2.cu:102-156.
+ * q = clamp(rn(x/s + z), 0, 15), (s,z) = set 1 for columns < 10 else set 2. Argument
+ * order follows the reference's DEFINITION (x, s1, z1, s2, z2), which is also how its
+ * binding calls it; the reference header lists (s1, s2, z1, z2). */
+int duq4_asym_dual_quant(const void *x, const void *scale_1, const void *zeros_1,
+                         const void *scale_2, const void *zeros_2, uint32_t rows,
+                         uint32_t colsSrc, uint32_t colsDst, uint8_t *q, void *stream);
+/* ref: include/quant.h:70-77 asym_quant_host_8bit -> src/kernels/quant.cu:245-279.
+ * fp32 in; q = clamp(rn(half(x/s)) + rn(half(z)), 0, 126) as int8. */
+int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros, uint32_t rows,
+                         uint32_t cols, int8_t *q, void *stream);
+
+/* ---- fused per-token quantize: statistics, scale(/zero) and codes in one pass --------- */
+/* No single reference function; each replaces the torch ops of a quantizer module plus
+ * the quantize launch (ref: qlinear4bit/nn/quantizer.py:10-16 SymQuantizer,
+ * :24-35 AsymQuantizer; src/module/quant_tensor.cu:151-161 Quantizer4bit::forward).
+ * x fp16 [rows, cols], cols even; q uint8 [rows, cols/2]; scale/zeros fp16 [rows] out.
+ * Dual variants compute one (scale[,zero]) over columns [0,10) and one over [10,cols). */
+int duq4_quantize_sym_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio,
+                            uint8_t *q, void *scale_out, void *stream);
+int duq4_quantize_asym_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q,
+                             void *scale_out, void *zeros_out, void *stream);
+int duq4_quantize_sym_dual_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio,
+                                 uint8_t *q, void *scale_1_out, void *scale_2_out, void *stream);
+int duq4_quantize_asym_dual_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q,
+                                  void *scale_1_out, void *zeros_1_out, void *scale_2_out,
+                                  void *zeros_2_out, void *stream);
+
+/* ---- dequantize an int32 accumulator tensor ------------------------------------------- */
+
+/* ref: include/quant.h:19-26 sym_dequant_host -> src/kernels/quant.cu:64-97.
+ * x = (scale_row[r] * scale_col[c]) * half(q), every product rounded to fp16. */
+int duq4_sym_dequant(const int32_t *q, const void *scale_row, const void *scale_col,
+                     uint32_t rows, uint32_t cols, void *x, void *stream);
+/* ref: include/quant.h:40-48 sym_dual_dequant_host -> src/kernels/quant2.cu:63-98.
+ * scale_col = scale_col_1[c] for output column c < 10, else scale_col_2[c]. */
+int duq4_sym_dual_dequant(const int32_t *q, const void *scale_row, const void *scale_col_1,
+                          const void *scale_col_2, uint32_t rows, uint32_t cols, void *x,
+                          void *stream);
+/* ref: include/quant.h:59-68 asym_dequant_host -> src/kernels/quant.cu:150-188.
+ * x = (s_row*s_col) * ((half(q) - z_row) - z_col). */
+int duq4_asym_dequant(const int32_t *q, const void *scale_row, const void *zeros_row,
+                      const void *scale_col, const void *zeros_col, uint32_t rows, uint32_t cols,
+                      void *x, void *stream);
+/* ref: include/quant.h:106-117 asym_dual_dequant_host -> src/kernels/quant2.cu:159-208.
+ * Column set 1 is used for output column 0 only (the reference's selector
+ * `(QUANT_COL_ST << col) & 1`), set 2 elsewhere. */
+int duq4_asym_dual_dequant(const int32_t *q, const void *scale_row, const void *zeros_row,
+                           const void *scale_col_1, const void *zeros_col_1,
+                           const void *scale_col_2, const void *zeros_col_2, uint32_t rows,
+                           uint32_t cols, void *x, void *stream);
+/* ref: include/quant.h:79-89 asym_batch_dequant_host -> src/kernels/quant.cu:191-239.
+ * q [batches, rows, cols]; row vectors [batches, rows], column vectors [batches, cols]. */
+int duq4_asym_batch_dequant(const int32_t *q, const void *scale_row, const void *zeros_row,
+                            const void *scale_col, const void *zeros_col, uint32_t batches,
+                            uint32_t rows, uint32_t cols, void *x, void *stream);
+/* ref: include/quant.h:118-127 asym_dequant_host_hprec -> src/kernels/quant.cu:282-323.
+ * fp32: x = (s_row*s_col) * (float(q) - (z_row + z_col)). */
+int duq4_asym_dequant_hprec(const int32_t *q, const float *scale_row, const float *zeros_row,
+                            const float *scale_col, const float *zeros_col, uint32_t rows,
+                            uint32_t cols, float *x, void *stream);
+
+/* ---- integer GEMMs, C[M,N] = A[M,K] * B[N,K]^T, int32 out ----------------------------- */
+
+/* ref: include/gemm.h:5-12 matmul_host_4bit -> src/kernels/gemm.cu:8-43 (CUTLASS Sm80
+ * int4 tensor-op GEMM). A, B packed signed int4; K % 64 == 0 (the reference asserts
+ * packed-K % 32 == 0, qlinear4bit/tools/tensor_utils.py:52). */
+int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K,
+                     int32_t *C, void *stream);
+/* ref: include/gemm.h:14-21 matmul_host_8bit -> src/kernels/gemm.cu:46-81. K % 16 == 0. */
+int duq4_matmul_8bit(const int8_t *A, const int8_t *B, uint32_t M, uint32_t N, uint32_t K,
+                     int32_t *C, void *stream);
+/* ref: include/gemm.h:23-31 batch_matmul_host_4bit -> src/kernels/gemm.cu:83-117, with
+ * the contiguous layout its binding builds (src/export/bindings.cpp:46-57):
+ * A [batch, M, K/2], B [batch, N, K/2] -> C [batch, M, N]. The reference passes HOST
+ * arrays of pointers to a device kernel and does not work; this one does. */
+int duq4_batch_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N,
+                           uint32_t K, int32_t *C, uint32_t batch_count, void *stream);
+
+/* ---- fused linear layer: int4 GEMM with the dequant (and bias) in its epilogue -------- */
+
+/* What the GEMM epilogue applies. Column vectors are indexed by the LOCAL column
+ * c in [0, N); `col_offset` is the global index of local column 0 and only enters the
+ * dual-uniform selectors (c + col_offset < 10, c + col_offset == 0), so that an
+ * N-sharded layer gives the same result as the unsharded one. */
+typedef struct duq4_epilogue {
+    int32_t mode;            /* DUQ4_MODE_* */
+    uint32_t col_offset;
+    const void *scale_row;   /* fp16 [M]   per-token scales              (all modes but NONE) */
+    const void *zeros_row;   /* fp16 [M]   per-token zero-points         (ASYM, ASYM_DUAL)    */
+    const void *scale_col_1; /* fp16 [N]   per-output-channel scales                           */
+    const void *zeros_col_1; /* fp16 [N]                                 (ASYM, ASYM_DUAL)    */
+    const void *scale_col_2; /* fp16 [N]                                 (SYM_DUAL, ASYM_DUAL) */
+    const void *zeros_col_2; /* fp16 [N]                                 (ASYM_DUAL)          */
+    const void *bias;        /* fp16 [N] or NULL; added last as a separate fp16 add
+                                (ref: qlinear4bit/nn/linear.py:53-54)                          */
+    uint32_t ldo;            /* row stride of `out` in elements; 0 means N */
+} duq4_epilogue;
+
+/* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches
+ * matmul + *_dequant + bias add of the reference's module forwards
+ * (ref: qlinear4bit/nn/linear.py:42-56, :104-115, :167-176, :239-250;
+ *  src/module/linear.cu:108-153, :200-246). `acc_out` (int32 [M,N], row stride N) is
+ * optional and receives the exact accumulators. M <= 16 runs the HBM-bound small-M
+ * kernel, larger M the tcgen05 tensor-core kernel. K % 64 == 0. */
+int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
+                     const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream);
+
+/* Batched form: A [batch,M,K/2], W [batch,N,K/2], out [batch,M,N]; the epilogue's row
+ * vectors are [batch,M] and its column vectors [batch,N] (the layout of the reference's
+ * asym_batch_dequant, src/kernels/quant.cu:211-218). */
+int duq4_linear_w4a4_batched(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
+                             uint32_t K, uint32_t batch_count, const duq4_epilogue *epi,
+                             void *out, int32_t *acc_out, void *stream);
+
+/* Bytes of caller-provided scratch duq4_linear_w4a4_from_fp16 needs for [M,K] tokens. */
+size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K);
+
+/* x fp16 [M,K] -> per-token quantize (act_mode: DUQ4_MODE_*, scales computed on the fly
+ * as in the fused quantizers) -> GEMM -> dequant. epi->scale_row / zeros_row are ignored
+ * and replaced by the computed ones, which live in `workspace` (256-byte aligned, at
+ * least duq4_linear_from_fp16_workspace_bytes(M,K)). For ASYM_DUAL/SYM_DUAL activation
+ * modes the epilogue uses set 1 of the computed row scales, as the reference modules do
+ * (they only ever carry one row-scale vector, qlinear4bit/tools/tensor_utils.py:20-27). */
+int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N,
+                               uint32_t K, int act_mode, float clip_ratio,
+                               const duq4_epilogue *epi, void *out, void *workspace,
+                               size_t workspace_bytes, void *stream);
+
+/* Device-side status word of the most recent tensor-core GEMM on the current device:
+ * 0 = no bounded wait expired. Reads back 4 bytes (synchronises the stream given). */
+int duq4_last_device_status(void *stream, int32_t *status_out /* host pointer */);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DUQ4_H_ */
