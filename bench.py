@@ -1,0 +1,431 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 linear hot path (per-token int4 quantize -> int4 GEMM -> dequant).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward of one W4A4 linear layer over a batch of synthetic tokens:
+fp16 activations [M,K] -> fused per-token symmetric quantize -> int4 x int4 -> int32 GEMM on
+tcgen05 tensor cores -> fp16 dequant epilogue, at the Llama-70B MLP up-projection shape
+K=8192 -> N=28672 with M=4096 tokens (the M=4096 point of the headline metric). The M=1
+point (decode, Llama-2-7B shapes, weight-bandwidth bound) is measured in the same run and
+reported under "decode". With --gpus N > 1 the layer is column-sharded over N ranks (one
+process per GPU, NCCL all-gather of the fp16 output shards) -- total work fixed: "strong".
+
+`value` is timed with inputs resident in HBM; `e2e` is the same layer through the C-ABI
+entry point with the activations coming from pinned host memory and the output going back
+to it inside the timed region. `--impl reference` times the CPU restatement of the
+reference arithmetic (oracle/) on the host cores over a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+K_IN, N_OUT, M_TOK = 8192, 28672, 4096
+DECODE_SHAPES = [(4096, 12288), (4096, 4096), (4096, 22016), (11008, 4096)]  # (K, N), Llama-2-7B
+NOMINAL_HBM_GBS, NOMINAL_INT8_TOPS = 8000.0, 4500.0
+WORKLOAD = f"prefill_llama70b_mlp_up_K{K_IN}_N{N_OUT}_M{M_TOK}_sym_w4a4"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = str(gpu_index)
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+def synth_activations(torch, M, K, seed, pinned=True):
+    """fp16 ~N(0,1) with 1% of the K channels scaled x20 (outliers); seeded on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((M, K), generator=g, dtype=torch.float32)
+    ch = torch.randperm(K, generator=g)[: K // 100]
+    x[:, ch] *= 20.0
+    x = x.to(torch.float16)
+    return x.pin_memory() if pinned else x
+
+
+def synth_weights(torch, N, K, seed, device):
+    """Random-init weights ~N(0,0.015), per-output-channel symmetric int4 (scale = absmax/7,
+    clamp [-8,7]), packed two per byte. Built on the GPU in row chunks."""
+    from duqlinear4bitcuda_b200.tools.quantization import pack_i4
+    g = torch.Generator(device=device).manual_seed(seed)
+    qw = torch.empty((N, K // 2), dtype=torch.uint8, device=device)
+    sw = torch.empty((N,), dtype=torch.float16, device=device)
+    for r0 in range(0, N, 4096):
+        r1 = min(N, r0 + 4096)
+        w = (torch.randn((r1 - r0, K), generator=g, device=device, dtype=torch.float32) * 0.015).to(torch.float16)
+        s = (w.abs().amax(dim=1, keepdim=True).float() / 7.0).to(torch.float16)
+        q = torch.clamp(torch.round(w / s), -8, 7).to(torch.int8)
+        qw[r0:r1] = pack_i4(q)
+        sw[r0:r1] = s.view(-1)
+    return qw, sw
+
+
+def cpu_baseline(sample_rows=None, threads=None, budget_s=12.0):
+    """The oracle (CPU restatement of the reference arithmetic) on a bounded sample: the first
+    `rows` tokens of the same workload against the full weight matrix."""
+    import numpy as np
+    from oracle import oracle as o
+    threads = threads or os.cpu_count()
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    rng = np.random.default_rng(0)
+    qw = rng.integers(0, 256, (N_OUT, K_IN // 2), dtype=np.uint8)
+    sw = (0.002 + 0.01 * rng.random(N_OUT)).astype(np.float16)
+
+    def run(rows):
+        x = rng.standard_normal((rows, K_IN)).astype(np.float16)
+        t0 = time.perf_counter()
+        s = o.sym_scales(x)
+        qa = o.sym_quant(x, s)
+        acc = o.matmul_4bit(qa, qw)
+        o.sym_dequant(acc, s, sw)
+        return time.perf_counter() - t0
+
+    if sample_rows is None:
+        t = run(4)
+        sample_rows = int(max(4, min(512, 4 * budget_s / max(t, 1e-3))))
+    t = run(sample_rows)
+    tops = 2.0 * sample_rows * N_OUT * K_IN / t / 1e12
+    return {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port",
+            "sample": f"first {sample_rows} of {M_TOK} tokens x full {K_IN}->{N_OUT} layer (quantize+int4 matmul+dequant), "
+                      f"{t:.2f} s, oracle/duq_oracle.c with OpenMP"}, t, sample_rows
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times, rows = [], None
+    for i in range(args.warmup + args.steps):
+        cb, t, rows = cpu_baseline(sample_rows=rows, budget_s=6.0)
+        if i >= args.warmup:
+            times.append(t)
+    t = sum(times) / len(times)
+    tops = 2.0 * rows * N_OUT * K_IN / t / 1e12
+    cb["value"] = tops
+    line = {"impl": "reference", "metric": "w4a4_linear_tops_M4096", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int4xint4->int32, fp16 epilogue", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample_rows_per_step": rows, "note": "CPU path of the reference arithmetic "
+                       "(oracle port); the reference's CUDA kernels need a GPU and are not the CPU arm"},
+            "cpu_baseline": cb,
+            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+def time_decode(torch, L, device, peaks, Ms=(1, 16)):
+    """us/layer of the small-M kernel on the Llama-2-7B shapes with COLD weights: a CUDA graph
+    walks over enough distinct weight buffers to exceed L2 (126 MB) before reusing one."""
+    out = []
+    st = L.current_stream()
+    for (K, N) in DECODE_SHAPES:
+        wbytes = N * K // 2
+        ncopy = max(4, int(320e6 // wbytes) + 1)
+        W = torch.randint(0, 256, (ncopy, N, K // 2), dtype=torch.uint8, device=device)
+        sw = (torch.rand(N, device=device) * 0.01 + 0.002).to(torch.float16)
+        for M in Ms:
+            qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=device)
+            sa = (torch.rand(M, device=device) * 0.1 + 0.01).to(torch.float16)
+            y = torch.empty((M, N), dtype=torch.float16, device=device)
+            epi = L.make_epilogue("sym", sa, None, sw)
+
+            def body():
+                for c in range(ncopy):
+                    L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi),
+                           L.ptr(y), None, L.current_stream())
+
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                body()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    body()
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 10
+                e0.record(s)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(s)
+                torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy)
+            gbs = wbytes / (us * 1e-6) / 1e9
+            out.append({"K": K, "N": N, "M": M, "us_per_layer": round(us, 3), "weight_GBps": round(gbs, 1),
+                        "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                        "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4), "cold_weight_buffers": ncopy})
+            del g
+        del W
+    return out
+
+
+def int8_cublas_tops(torch, device):
+    """cuBLASLt int8 GEMM (torch._int_mm) at 8192^3, best of 5: context for the tensor-pipe peak."""
+    try:
+        a = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device=device)
+        b = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device=device).t()
+        for _ in range(2):
+            torch._int_mm(a, b)
+        best = 1e9
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch._int_mm(a, b); e1.record(); torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+    except Exception as ex:  # pragma: no cover
+        return f"unavailable: {type(ex).__name__}"
+
+
+def run_profile_case(args):
+    """A few launches of one kernel on a reduced case, for `ncu` captures (no timing)."""
+    import torch
+    import duqlinear4bitcuda_b200.lib as L
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    st = L.current_stream
+    if args.profile_case == "gemm":
+        M, N, K = 2048, 8192, 8192
+        qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev)
+        qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev)
+        sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        epi = L.make_epilogue("sym", sa, None, sw)
+        for _ in range(4):
+            L.call("duq4_linear_w4a4", L.ptr(qa), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
+    elif args.profile_case == "decode":
+        M, N, K = 1, 22016, 4096
+        W = torch.randint(0, 256, (8, N, K // 2), dtype=torch.uint8, device=dev)  # 8 x 45 MB: cold in L2
+        qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev)
+        sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        epi = L.make_epilogue("sym", sa, None, sw)
+        for c in range(8):
+            L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
+    elif args.profile_case == "quantize":
+        M, K = 4096, 8192
+        xs = [torch.randn((M, K), device=dev).half() for _ in range(4)]  # 4 x 64 MB
+        q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev); s = torch.empty(M, dtype=torch.float16, device=dev)
+        for x in xs:
+            L.call("duq4_quantize_sym_fused", L.ptr(x), M, K, 1.0, L.ptr(q), L.ptr(s), st())
+    else:
+        raise SystemExit("unknown --profile-case")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": args.profile_case, "ok": True}))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import duqlinear4bitcuda_b200.lib as L  # raises if libduq4.so is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    peaks = measured_peaks()
+    M, K, N = M_TOK, K_IN, N_OUT
+    assert N % world == 0
+    Ns = N // world
+    st = L.current_stream
+
+    x_host = synth_activations(torch, M, K, seed=0)
+    x = x_host.to(device)
+    qw_full_seeded = synth_weights(torch, Ns, K, seed=1000 + rank, device=device)  # this rank's N-shard
+    qw, sw = qw_full_seeded
+    out_shard = torch.empty((M, Ns), dtype=torch.float16, device=device)
+    out_full = torch.empty((M, N), dtype=torch.float16, device=device) if world > 1 else out_shard
+    gathered = torch.empty((world, M, Ns), dtype=torch.float16, device=device) if world > 1 else None
+    out_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
+    codes = torch.empty((M, K), dtype=torch.int8, device=device)   # tensor-core-ready activation codes
+    sa = torch.empty((M,), dtype=torch.float16, device=device)
+    ws_bytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+    epi = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns)
+    epi_e2e = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns)
+
+    def step(ev=None):
+        # the two launches duq4_linear_w4a4_from_fp16 makes, issued separately so that the GEMM
+        # launch can be bracketed by its own events
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(codes), L.ptr(sa), None, None, None, st())
+        if ev:
+            ev[0].record()
+        L.call("duq4_linear_w4a4_preunpacked", L.ptr(codes), L.ptr(qw), M, Ns, K, ctypes.byref(epi), L.ptr(out_shard), None, st())
+        if ev:
+            ev[1].record()
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
+            out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
+
+    def step_e2e():
+        x.copy_(x_host, non_blocking=True)
+        L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_e2e),
+               L.ptr(out_shard), L.ptr(ws), ws_bytes, st())
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
+            out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
+        out_host.copy_(out_full, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, per_kernel=False):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)] if per_kernel else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(evs[i]) if per_kernel else fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        kms = [a.elapsed_time(b) for a, b in evs] if per_kernel else None
+        return ms, kms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total_ms, gemm_ms = timed(step, args.steps, args.warmup, per_kernel=True)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_ms, _ = timed(step_e2e, args.steps, args.warmup)
+
+    status = ctypes.c_int32(-1)
+    L.call("duq4_last_device_status", st(), ctypes.byref(status))
+    if status.value != 0:
+        raise SystemExit(f"device-side bounded wait expired (code {status.value}); result invalid")
+
+    ops = 2.0 * M * N * K
+    ms_step = total_ms / args.steps
+    tops = ops / (ms_step * 1e-3) / 1e12
+    e2e_tops = ops / (e2e_ms / args.steps * 1e-3) / 1e12
+    gemm_avg_ms = sum(gemm_ms) / len(gemm_ms)
+    gemm_tops = (2.0 * M * Ns * K) / (gemm_avg_ms * 1e-3) / 1e12  # this rank's GEMM launch
+    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+
+    line = {"metric": "w4a4_linear_tops_M4096", "value": round(tops, 2), "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int4xint4->int32 (kind::i8 tensor cores), fp16 epilogue", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "parallelism": f"column-parallel N/{world} + all-gather" if world > 1 else "single GPU",
+                       "cache": "operands (weights 117 MB + activations 64 MB + output 235 MB) exceed the 126 MB L2; no flush",
+                       "weights": "N(0,0.015) per-channel symmetric int4", "activations": "N(0,1), 1% channels x20, per-token symmetric int4"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_tops, 2), "unit": "TOPS", "ms_per_step": round(e2e_ms / args.steps, 4),
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "api": "duq4_linear_w4a4_from_fp16 (C ABI), activations from pinned host memory, output back to pinned host memory"},
+            "gpu_launches": args.steps * 2,
+            "roofline": {"kernel": "gemm_tc_kernel<A int8 pre-unpacked by the quantizer, W int4 unpacked in smem, 128x256x128> (tcgen05.mma kind::i8)", "bound": "tensor",
+                         "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
+                         "frac": round(gemm_tops / int8_peak, 4), "traffic": None,
+                         "avg_launch_ms": round(gemm_avg_ms, 4),
+                         "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); no int8 entry there",
+                         "frac_of_nominal_4500": round(gemm_tops / NOMINAL_INT8_TOPS, 4)}}
+    if rank == 0 and world == 1:
+        line["roofline"]["cublaslt_int8_8192cubed_tops"] = int8_cublas_tops(torch, device)
+        if not args.no_decode:
+            line["decode"] = time_decode(torch, L, device, peaks)
+        if not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline()[0]
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize"],
+                    help="run a few launches of one kernel on a reduced case (for ncu) and exit")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -6,11 +6,11 @@
 namespace duq4 {
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
-int gemm_tc_launch(bool int4, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
-                            void *z1, void *s2, void *z2, cudaStream_t st);
+                            void *z1, void *s2, void *z2, cudaStream_t st, bool out8);
 
 constexpr uint32_t kSmallM = 16;  // at or below this many tokens the layer is weight-bandwidth bound
 
@@ -51,7 +51,7 @@ static int linear_dispatch(const uint8_t *A, const uint8_t *W, uint32_t M, uint3
     if (M == 0 || N == 0 || batch == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
     if (M <= kSmallM) return gemv_w4a4_launch(A, W, M, N, K, batch, p, out, acc_out, st);
-    return gemm_tc_launch(true, A, W, M, N, K, batch, p, out, acc_out, st);
+    return gemm_tc_launch(1 /* both operands packed int4 */, A, W, M, N, K, batch, p, out, acc_out, st);
 }
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -94,7 +94,7 @@ int duq4_matmul_8bit(const int8_t *A, const int8_t *B, uint32_t M, uint32_t N, u
     EpiParams p{};
     p.mode = DUQ4_MODE_NONE;
     p.ldo = N;
-    return gemm_tc_launch(false, A, B, M, N, K, 1, p, nullptr, C, (cudaStream_t)stream);
+    return gemm_tc_launch(0 /* int8 operands */, A, B, M, N, K, 1, p, nullptr, C, (cudaStream_t)stream);
 }
 
 int duq4_batch_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C,
@@ -124,9 +124,26 @@ int duq4_linear_w4a4_batched(const uint8_t *A, const uint8_t *W, uint32_t M, uin
     return linear_dispatch(A, W, M, N, K, batch_count, p, out, acc_out, (cudaStream_t)stream);
 }
 
+int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
+                                 const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream) {
+    EpiParams p;
+    int rc = check_epi(epi, N, true, &p);
+    if (rc) return rc;
+    if (!A_i8 || !W) return DUQ4_ERR_NULL;
+    if (p.mode != DUQ4_MODE_NONE && !out) return DUQ4_ERR_NULL;
+    if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, A_i8, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
+}
+
+// Scratch layout of duq4_linear_w4a4_from_fp16: activation codes, then four fp16 vectors [M]
+// (scale_1, zeros_1, scale_2, zeros_2), each region 256-byte aligned. M <= 16 stores packed
+// codes [M, K/2]; larger M stores tensor-core-ready int8 codes [M, K].
+static size_t codes_bytes(uint32_t M, uint32_t K) { return M <= kSmallM ? (size_t)M * (K / 2) : (size_t)M * K; }
+
 size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K) {
-    // codes [M, K/2] then four fp16 vectors [M] (scale_1, zeros_1, scale_2, zeros_2), each 256-byte aligned
-    return align_up((size_t)M * (K / 2), 256) + 4 * align_up((size_t)M * 2, 256);
+    return align_up(codes_bytes(M, K), 256) + 4 * align_up((size_t)M * 2, 256);
 }
 
 int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
@@ -145,17 +162,19 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
     if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
     uint8_t *ws = (uint8_t *)workspace;
     uint8_t *codes = ws;
-    size_t off = align_up((size_t)M * (K / 2), 256), vec = align_up((size_t)M * 2, 256);
+    size_t off = align_up(codes_bytes(M, K), 256), vec = align_up((size_t)M * 2, 256);
+    const bool small = M <= kSmallM;
     void *s1 = ws + off, *z1 = ws + off + vec, *s2 = ws + off + 2 * vec, *z2 = ws + off + 3 * vec;
     cudaStream_t st = (cudaStream_t)stream;
-    rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, codes, s1, z1, s2, z2, st);
-    if (rc) return rc;
     const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
     const bool act_asym = act_mode == DUQ4_MODE_ASYM || act_mode == DUQ4_MODE_ASYM_DUAL;
     if (epi_asym && !act_asym) return DUQ4_ERR_MODE;  // an asymmetric epilogue needs per-token zero-points
+    rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, codes, s1, z1, s2, z2, st, !small);
+    if (rc) return rc;
     p.s_row = (const __half *)s1;
     p.z_row = epi_asym ? (const __half *)z1 : nullptr;
-    return linear_dispatch(codes, W, M, N, K, 1, p, out, nullptr, st);
+    if (small) return linear_dispatch(codes, W, M, N, K, 1, p, out, nullptr, st);
+    return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, codes, W, M, N, K, 1, p, out, nullptr, st);
 }
 
 int duq4_last_device_status(void *stream, int32_t *status_out) {

@@ -21,6 +21,7 @@
 // epilogue of tile i overlaps the main loop of tile i+1. Every mbarrier wait is bounded
 // (1 s of %globaltimer); on expiry the CTA raises a status word and leaves in order.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -35,9 +36,14 @@ namespace tc {
 
 constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // K elements per pipeline stage (= one 128-byte swizzle row of int8)
-constexpr int kUnpackWarps = 4;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps);
+// Operand formats of one launch.
+constexpr int MODE_I8 = 0;     // A and B int8: TMA writes the swizzled tiles, no unpack
+constexpr int MODE_I4 = 1;     // A and B packed int4: both unpacked in shared memory
+constexpr int MODE_A8B4 = 2;   // A already unpacked in HBM (int8 = 16*s4, K permuted per 128-block
+                               // exactly as the in-kernel unpack permutes it), B packed int4
+// warps: 0 TMA producer, 1 MMA issuer, 2..5 epilogue, 6..6+UW-1 unpack, last: second TMA producer (A of MODE_A8B4)
+__host__ __device__ constexpr int threads_for(int uw) { return 32 * (2 + kEpiWarps + uw + 1); }
 constexpr uint64_t kWaitLimitNs = 1000000000ull;
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -143,12 +149,14 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
 __device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
 __device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return w & 0xF0F0F0F0u; }
 
-template <bool INT4, int BN>
+template <int MODE, int BN, int UW_, int NPK_, int NUP_>
 struct Cfg {
-    static constexpr int kPackedStage = INT4 ? (BM + BN) * (BK / 2) : 0;
+    static constexpr int UW = UW_;
+    static constexpr int kPackedStage = MODE == MODE_I4 ? (BM + BN) * (BK / 2) : (MODE == MODE_A8B4 ? BN * (BK / 2) : 0);
     static constexpr int kUnpackedStage = (BM + BN) * BK;
-    static constexpr int NPK = INT4 ? 4 : 1;
-    static constexpr int NUP = INT4 ? (BN == 256 ? 2 : 4) : (BN == 256 ? 4 : 6);
+    static constexpr int NPK = MODE == MODE_I8 ? 1 : NPK_;   // packed-tile ring (TMA -> unpack warps)
+    static constexpr int NUP = NUP_;                          // swizzled int8 ring (-> MMA)
+    static_assert(NPK <= 4 && NUP <= 6, "barrier map holds 4 packed and 6 unpacked stages");
     static constexpr int kColTerms = kEpiWarps * 3 * BN * 2;  // per epilogue warp: (scale, zero, bias) x BN halves
     static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
@@ -162,10 +170,13 @@ struct Args {
     int32_t *acc_out;
 };
 
-template <bool INT4, int BN>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                              const __grid_constant__ CUtensorMap tmB, const Args a) {
-    using C = Cfg<INT4, BN>;
+template <int MODE, int BN, int UW, int NPK_, int NUP_>
+__global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                     const __grid_constant__ CUtensorMap tmB, const Args a) {
+    using C = Cfg<MODE, BN, UW, NPK_, NUP_>;
+    constexpr bool INT4 = MODE != MODE_I8;
+    constexpr int kUnpackWarps = UW;
+    constexpr int kLastWarp = 2 + kEpiWarps + UW;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -198,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             mbar_init(pk_empty(s), kUnpackWarps);
         }
         for (int s = 0; s < 6; ++s) {
-            mbar_init(up_full(s), INT4 ? kUnpackWarps : 1);
+            mbar_init(up_full(s), MODE == MODE_I8 ? 1 : (MODE == MODE_I4 ? kUnpackWarps : kUnpackWarps + 1));
             mbar_init(up_empty(s), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -228,13 +239,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 uint32_t b = tile / per_b, r = tile % per_b;
                 uint32_t tn = r / a.tiles_m, tm = r % a.tiles_m;
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
-                    if (INT4) {
+                    if (MODE == MODE_I4) {
                         uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
                         if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, 1))) break;
                         uint32_t dst = pk0 + s * C::kPackedStage;
                         mbar_expect_tx(pk_full(s), C::kPackedStage);
                         tma_load_3d(dst, &tmA, pk_full(s), ks * (BK / 2), tm * BM, b);
                         tma_load_3d(dst + BM * (BK / 2), &tmB, pk_full(s), ks * (BK / 2), tn * BN, b);
+                    } else if (MODE == MODE_A8B4) {
+                        uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
+                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, 1))) break;
+                        mbar_expect_tx(pk_full(s), C::kPackedStage);
+                        tma_load_3d(pk0 + s * C::kPackedStage, &tmB, pk_full(s), ks * (BK / 2), tn * BN, b);
                     } else {
                         uint32_t s = it % C::NUP, ph = (it / C::NUP) & 1;
                         if (!(ok = mbar_wait(up_empty(s), ph ^ 1, abortp, 1))) break;
@@ -246,6 +262,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 }
             }
             if (!ok) {  // give copies already in flight time to land before the CTA retires
+                uint64_t t0 = globaltimer();
+                while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+            }
+        }
+    } else if (MODE == MODE_A8B4 && warp == kLastWarp) {
+        // ---------------- second TMA producer: pre-unpacked A straight into the MMA ring ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t per_b = a.tiles_m * a.tiles_n;
+                uint32_t b = tile / per_b, r = tile % per_b;
+                uint32_t tm = r % a.tiles_m;
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    uint32_t u = it % C::NUP, uph = (it / C::NUP) & 1;
+                    if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, 7))) break;
+                    mbar_expect_tx(up_full(u), BM * BK);
+                    tma_load_3d(up0 + u * C::kUnpackedStage, &tmA, up_full(u), ks * BK, tm * BM, b);
+                }
+            }
+            if (!ok) {
                 uint64_t t0 = globaltimer();
                 while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
             }
@@ -383,10 +420,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
         }
-    } else if (INT4) {
+    } else if (INT4 && warp < kLastWarp) {
         // ---------------- unpack warps: packed int4 -> swizzled int8 ----------------
-        const int ut = (warp - 2 - kEpiWarps) * 32 + lane;  // 0..127
-        constexpr int kChunks = (BM + BN) * 4;              // 16-byte packed chunks per stage
+        const int ut = (warp - 2 - kEpiWarps) * 32 + lane;
+        constexpr int kRows = MODE == MODE_I4 ? BM + BN : BN;   // packed rows per stage
+        constexpr int kChunks = kRows * 4;                      // 16-byte packed chunks per stage
+        constexpr uint32_t kDstOff = MODE == MODE_I4 ? 0 : BM * BK;  // MODE_A8B4 fills the B half only
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -395,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 uint32_t u = it % C::NUP, uph = (it / C::NUP) & 1;
                 if (!(ok = mbar_wait(pk_full(s), ph, abortp, 5))) break;
                 if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, 6))) break;
-                const uint32_t src = pk0 + s * C::kPackedStage, dst = up0 + u * C::kUnpackedStage;
+                const uint32_t src = pk0 + s * C::kPackedStage, dst = up0 + u * C::kUnpackedStage + kDstOff;
 #pragma unroll 4
                 for (int idx = ut; idx < kChunks; idx += kUnpackWarps * 32) {
                     uint32_t w0, w1, w2, w3;
@@ -511,50 +550,72 @@ static int sm_count() {
     return n;
 }
 
-template <bool INT4, int BN>
+template <int MODE, int BN, int UW, int NPK_, int NUP_>
 static int launch(const void *A, const void *B, const Args &args, cudaStream_t st) {
-    using C = Cfg<INT4, BN>;
+    using C = Cfg<MODE, BN, UW, NPK_, NUP_>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<INT4, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, UW, NPK_, NUP_>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    const uint64_t kbytes = INT4 ? args.K / 2 : args.K;
-    const uint32_t box_k = INT4 ? BK / 2 : BK;
+    const bool a_packed = MODE == MODE_I4, b_packed = MODE != MODE_I8;
     CUtensorMap ma, mb;
-    int rc = get_map(A, kbytes, args.M, args.batch, box_k, BM, !INT4, &ma);
+    int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma);
     if (rc) return rc;
-    rc = get_map(B, kbytes, args.N, args.batch, box_k, BN, !INT4, &mb);
+    rc = get_map(B, b_packed ? args.K / 2 : args.K, args.N, args.batch, b_packed ? BK / 2 : BK, BN, !b_packed, &mb);
     if (rc) return rc;
     uint32_t tiles = args.tiles_m * args.tiles_n * args.batch;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
-    gemm_tc_kernel<INT4, BN><<<grid, kThreads, C::kSmem, st>>>(ma, mb, args);
+    gemm_tc_kernel<MODE, BN, UW, NPK_, NUP_><<<grid, threads_for(UW), C::kSmem, st>>>(ma, mb, args);
     return launch_status();
+}
+
+// Debug override of the pipeline shape (DUQ4_TC_VARIANT=0..2); unset = the tuned default.
+static int variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("DUQ4_TC_VARIANT");
+        v = e ? atoi(e) : 1;
+        if (v < 0 || v > 2) v = 1;
+    }
+    return v;
 }
 
 }  // namespace tc
 
-// A [batch,M,K] x B [batch,N,K]^T. int4: A,B packed (K/2 bytes per row); int8 otherwise.
-int gemm_tc_launch(bool int4, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+// A [batch,M,K] x B [batch,N,K]^T. mode: tc::MODE_I8 / MODE_I4 / MODE_A8B4 (see above).
+int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+    using namespace tc;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
-    if (int4 && K >= 131072u) return DUQ4_ERR_SHAPE;  // 256x-scaled accumulators must fit int32
-    tc::Args a{};
+    if (mode != MODE_I8 && K >= 131072u) return DUQ4_ERR_SHAPE;  // 256x-scaled accumulators must fit int32
+    Args a{};
     a.M = M; a.N = N; a.K = K; a.batch = batch;
     a.epi = p;
     a.out = (__half *)out;
     a.acc_out = acc_out;
-    a.tiles_m = cdiv(M, tc::BM);
+    a.tiles_m = cdiv(M, BM);
     // 256-wide tiles halve the A-operand shared-memory traffic per MMA; fall back to 128
     // when that would leave most SMs without a tile.
     const bool wide = (uint64_t)a.tiles_m * cdiv(N, 256) * batch >= 120 || N > 128 * 148;
-    if (wide) {
-        a.tiles_n = cdiv(N, 256);
-        return int4 ? tc::launch<true, 256>(A, B, a, st) : tc::launch<false, 256>(A, B, a, st);
+    a.tiles_n = cdiv(N, wide ? 256 : 128);
+    const int v = variant();
+    if (mode == MODE_I8) return wide ? launch<MODE_I8, 256, 4, 1, 4>(A, B, a, st) : launch<MODE_I8, 128, 4, 1, 6>(A, B, a, st);
+    if (mode == MODE_I4) {
+        if (!wide) return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st);
+        if (v == 0) return launch<MODE_I4, 256, 4, 4, 2>(A, B, a, st);
+        if (v == 2) return launch<MODE_I4, 256, 8, 4, 2>(A, B, a, st);
+        return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st);
     }
-    a.tiles_n = cdiv(N, 128);
-    return int4 ? tc::launch<true, 128>(A, B, a, st) : tc::launch<false, 128>(A, B, a, st);
+    if (mode == MODE_A8B4) {
+        if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st);
+        if (v == 0) return launch<MODE_A8B4, 256, 4, 4, 3>(A, B, a, st);
+        if (v == 2) return launch<MODE_A8B4, 256, 8, 4, 3>(A, B, a, st);
+        return launch<MODE_A8B4, 256, 12, 4, 3>(A, B, a, st);
+    }
+    return DUQ4_ERR_MODE;
 }
 
 int tc_status_read(cudaStream_t st, int32_t *out) {

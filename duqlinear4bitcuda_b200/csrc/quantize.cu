@@ -205,7 +205,7 @@ __device__ __forceinline__ void store_rowq(const RowQ &r, uint32_t row, __half *
 template <int MODE, int VPT>
 __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__restrict__ x, uint32_t rows, uint32_t cols,
                                                               float clip, uint8_t *__restrict__ q, __half *s1o,
-                                                              __half *z1o, __half *s2o, __half *z2o) {
+                                                              __half *z1o, __half *s2o, __half *z2o, bool out8) {
     __shared__ float sm[8][4];
     const uint32_t nvec = cols >> 3;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -231,11 +231,30 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
         stats_reduce<MODE>(st, sm);
         RowQ r = rowq_from_stats<MODE>(st, clip);
         if (threadIdx.x == 0) store_rowq<MODE>(r, row, s1o, z1o, s2o, z2o);
-        uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
+        if (!out8) {
+            uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            uint32_t v = threadIdx.x + i * 256;
-            if (v < nvec) qr[v] = code8<MODE>(d[i], v * 8, r);
+            for (int i = 0; i < VPT; ++i) {
+                uint32_t v = threadIdx.x + i * 256;
+                if (v < nvec) qr[v] = code8<MODE>(d[i], v * 8, r);
+            }
+        } else {
+            // Tensor-core-ready activations: one int8 (= 16 * code) per element, stored in the K
+            // order the GEMM's in-kernel weight unpack produces. Inside each block of 128
+            // elements, the low nibbles of 32 consecutive codes form bytes [32c, 32c+16) and the
+            // high nibbles bytes [32c+16, 32c+32). The 8 codes of one vector are one packed word w;
+            // (w<<4)&0xF0F0F0F0 holds its even elements, w&0xF0F0F0F0 its odd ones.
+            uint8_t *qr = q + (size_t)row * cols;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                uint32_t v = threadIdx.x + i * 256;
+                if (v < nvec) {
+                    uint32_t w = code8<MODE>(d[i], v * 8, r);
+                    uint32_t off = (v >> 4) * 128 + ((v & 15) >> 2) * 32 + (v & 3) * 4;
+                    *reinterpret_cast<uint32_t *>(qr + off) = (w << 4) & 0xF0F0F0F0u;
+                    *reinterpret_cast<uint32_t *>(qr + off + 16) = w & 0xF0F0F0F0u;
+                }
+            }
         }
     }
 }
@@ -314,7 +333,7 @@ static int launch_given(const void *x, const void *s1, const void *z1, const voi
 
 template <int MODE>
 static int launch_fused(const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1, void *z1, void *s2,
-                        void *z2, cudaStream_t st) {
+                        void *z2, cudaStream_t st, bool out8 = false) {
     if (!x || !q || !s1) return DUQ4_ERR_NULL;
     if ((MODE == QSYM_DUAL || MODE == QASYM_DUAL) && !s2) return DUQ4_ERR_NULL;
     if ((MODE == QASYM || MODE == QASYM_DUAL) && !z1) return DUQ4_ERR_NULL;
@@ -325,28 +344,29 @@ static int launch_fused(const void *x, uint32_t rows, uint32_t cols, float clip,
     __half *a = (__half *)s1, *b = (__half *)z1, *c = (__half *)s2, *d = (__half *)z2;
     uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
     bool vec = cols % 8 == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 3) == 0 && cols <= 256u * 8u * 16u;
+    if (out8 && (!vec || cols % 64 != 0)) return DUQ4_ERR_SHAPE;
     if (!vec) {
         quant_fused_scalar_kernel<MODE><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
     } else if (cols <= 256u * 8u * 2u) {
-        quant_fused_vec_kernel<MODE, 2><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+        quant_fused_vec_kernel<MODE, 2><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
     } else if (cols <= 256u * 8u * 4u) {
-        quant_fused_vec_kernel<MODE, 4><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+        quant_fused_vec_kernel<MODE, 4><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
     } else if (cols <= 256u * 8u * 8u) {
-        quant_fused_vec_kernel<MODE, 8><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+        quant_fused_vec_kernel<MODE, 8><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
     } else {
-        quant_fused_vec_kernel<MODE, 16><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+        quant_fused_vec_kernel<MODE, 16><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
     }
     return launch_status();
 }
 
 // Used by the fused linear entry point (abi.cu).
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
-                            void *z1, void *s2, void *z2, cudaStream_t st) {
+                            void *z1, void *s2, void *z2, cudaStream_t st, bool out8) {
     switch (mode) {
-        case QSYM: return launch_fused<QSYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
-        case QSYM_DUAL: return launch_fused<QSYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
-        case QASYM: return launch_fused<QASYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
-        case QASYM_DUAL: return launch_fused<QASYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st);
+        case QSYM: return launch_fused<QSYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st, out8);
+        case QSYM_DUAL: return launch_fused<QSYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st, out8);
+        case QASYM: return launch_fused<QASYM>(x, rows, cols, clip, q, s1, z1, s2, z2, st, out8);
+        case QASYM_DUAL: return launch_fused<QASYM_DUAL>(x, rows, cols, clip, q, s1, z1, s2, z2, st, out8);
         default: return DUQ4_ERR_MODE;
     }
 }
@@ -380,6 +400,12 @@ int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros,
     if (rows == 0 || cols == 0) return DUQ4_OK;
     asym_quant8_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, zeros, rows, cols, q);
     return launch_status();
+}
+
+int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols, float clip_ratio, int8_t *q_i8,
+                           void *scale_1_out, void *zeros_1_out, void *scale_2_out, void *zeros_2_out, void *stream) {
+    return quantize_fused_dispatch(mode, x, rows, cols, clip_ratio, (uint8_t *)q_i8, scale_1_out, zeros_1_out, scale_2_out,
+                                   zeros_2_out, (cudaStream_t)stream, true);
 }
 
 int duq4_quantize_sym_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q, void *scale_out,

@@ -95,6 +95,18 @@ int duq4_quantize_asym_dual_fused(const void *x, uint32_t rows, uint32_t cols, u
                                   void *scale_1_out, void *zeros_1_out, void *scale_2_out,
                                   void *zeros_2_out, void *stream);
 
+/* Fused quantizer writing TENSOR-CORE-READY activations for duq4_linear_w4a4_preunpacked:
+ * q_i8 [rows, cols] holds one int8 = 16 * code per element (the nibble in the high four bits),
+ * and inside every block of 128 columns the elements are permuted the way the GEMM's own
+ * in-kernel int4 unpack permutes them (position 32c+b <- column 32c+2b, position 32c+16+b <-
+ * column 32c+2b+1, b in [0,16), c in [0,4)). The buffer is an opaque operand of that GEMM, not
+ * a format of the reference. mode is DUQ4_MODE_SYM/SYM_DUAL/ASYM/ASYM_DUAL; outputs a mode
+ * does not produce may be NULL. cols % 64 == 0. No reference counterpart: it removes the
+ * activation half of the shared-memory unpack work from the GEMM. */
+int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols, float clip_ratio,
+                           int8_t *q_i8, void *scale_1_out, void *zeros_1_out, void *scale_2_out,
+                           void *zeros_2_out, void *stream);
+
 /* ---- dequantize an int32 accumulator tensor ------------------------------------------- */
 
 /* ref: include/quant.h:19-26 sym_dequant_host -> src/kernels/quant.cu:64-97.
@@ -174,6 +186,13 @@ typedef struct duq4_epilogue {
  * kernel, larger M the tcgen05 tensor-core kernel. K % 64 == 0. */
 int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
                      const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream);
+
+/* Same layer with the activations given as the int8 buffer written by duq4_quantize_fused_i8
+ * (always the tensor-core kernel, any M >= 1). Results are identical to duq4_linear_w4a4 on
+ * the packed codes of the same activations. */
+int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t M, uint32_t N,
+                                 uint32_t K, const duq4_epilogue *epi, void *out, int32_t *acc_out,
+                                 void *stream);
 
 /* Batched form: A [batch,M,K/2], W [batch,N,K/2], out [batch,M,N]; the epilogue's row
  * vectors are [batch,M] and its column vectors [batch,N] (the layout of the reference's

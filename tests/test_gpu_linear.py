@@ -236,3 +236,52 @@ def test_full_size_property_prefill(env):
     idx = [0, 1, 127, 128, 2047, 4095]
     sub = o.matmul_4bit(qa[idx].cpu().numpy(), qw.cpu().numpy())
     assert np.array_equal(C[idx].cpu().numpy(), sub)
+
+
+@pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (130, 264, 192), (512, 1024, 2048)])
+def test_preunpacked_activations_match_packed_path(env, mode, M, N, K):
+    """duq4_quantize_fused_i8 + duq4_linear_w4a4_preunpacked give the scales and outputs of
+    duq4_quantize_*_fused + duq4_linear_w4a4, and the int32 accumulators of the oracle."""
+    torch, L, o = env
+    x = U.acts(M, K, M + K, mean=0.1 if "asym" in mode else 0.0)
+    dx = dev(torch, x)
+    qw = U.rand_codes(N, K, 3); dqw = dev(torch, qw)
+    sc1 = dev(torch, U.rand_scales(N, 4)); zc1 = dev(torch, U.rand_zeros(N, 5))
+    sc2 = dev(torch, U.rand_scales(N, 6)); zc2 = dev(torch, U.rand_zeros(N, 7))
+    vec = lambda: torch.zeros(M, dtype=torch.float16, device="cuda")
+    st = L.current_stream()
+    s1, z1, s2, z2 = vec(), vec(), vec(), vec()
+    t1, y1, t2, y2 = vec(), vec(), vec(), vec()
+    q = torch.zeros((M, K // 2), dtype=torch.uint8, device="cuda")
+    a8 = torch.zeros((M, K), dtype=torch.int8, device="cuda")
+    if mode == "sym":
+        L.call("duq4_quantize_sym_fused", L.ptr(dx), M, K, 1.0, L.ptr(q), L.ptr(s1), st)
+    elif mode == "sym_dual":
+        L.call("duq4_quantize_sym_dual_fused", L.ptr(dx), M, K, 1.0, L.ptr(q), L.ptr(s1), L.ptr(s2), st)
+    elif mode == "asym":
+        L.call("duq4_quantize_asym_fused", L.ptr(dx), M, K, L.ptr(q), L.ptr(s1), L.ptr(z1), st)
+    else:
+        L.call("duq4_quantize_asym_dual_fused", L.ptr(dx), M, K, L.ptr(q), L.ptr(s1), L.ptr(z1), L.ptr(s2), L.ptr(z2), st)
+    L.call("duq4_quantize_fused_i8", L.MODES[mode], L.ptr(dx), M, K, 1.0, L.ptr(a8), L.ptr(t1), L.ptr(y1), L.ptr(t2), L.ptr(y2), st)
+    torch.cuda.synchronize()
+    assert torch.equal(s1.view(torch.int16), t1.view(torch.int16))
+    if "asym" in mode:
+        assert torch.equal(z1.view(torch.int16), y1.view(torch.int16))
+    # the int8 buffer is 16 * code, K-permuted inside 128-blocks: undo the permutation and compare
+    codes = o.unpack_s4(q.cpu().numpy()).astype(np.int16)
+    a = a8.cpu().numpy().astype(np.int16)
+    pos = np.arange(K); blk, r = pos // 128, pos % 128
+    src = blk * 128 + 32 * (r // 32) + 2 * (r % 16) + ((r % 32) // 16)
+    assert np.array_equal(a, 16 * codes[:, src])
+    asym = mode.startswith("asym"); dual = mode.endswith("dual")
+    epi = L.make_epilogue(mode, s1, z1 if asym else None, sc1, zc1 if asym else None, sc2 if dual else None,
+                          zc2 if mode == "asym_dual" else None)
+    out_a = torch.zeros((M, N), dtype=torch.float16, device="cuda"); out_b = torch.zeros_like(out_a)
+    acc_b = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    L.call("duq4_linear_w4a4", L.ptr(q), L.ptr(dqw), M, N, K, ctypes.byref(epi), L.ptr(out_a), None, st)
+    L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(dqw), M, N, K, ctypes.byref(epi), L.ptr(out_b), L.ptr(acc_b), st)
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert np.array_equal(acc_b.cpu().numpy(), o.matmul_4bit(q.cpu().numpy(), qw))
+    assert U.f16_equal_nan(out_a.cpu().numpy(), out_b.cpu().numpy())
