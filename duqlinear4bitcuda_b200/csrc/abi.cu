@@ -1,13 +1,15 @@
 // extern "C" entry points for the GEMMs and the fused linear layer, plus library metadata.
 // Argument checking happens here, before any launch; the kernels live in gemv_decode.cu
 // (M <= 16, HBM-bound) and gemm_tc.cu (tcgen05 tensor cores).
+#include <mutex>
+
 #include "duq_common.cuh"
 
 namespace duq4 {
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
+                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
                             void *z1, void *s2, void *z2, cudaStream_t st, bool out8);
@@ -74,6 +76,7 @@ const char *duq4_error_string(int status) {
         case DUQ4_ERR_ALIGN: return "pointer not 16-byte aligned";
         case DUQ4_ERR_DEVICE: return "device or driver does not provide what the kernel needs";
         case DUQ4_ERR_TIMEOUT: return "a bounded device-side wait expired";
+        case DUQ4_ERR_TOO_LARGE: return "problem needs more scratch than the library's built-in scratch array holds";
         default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown duq4 status";
     }
 }
@@ -175,6 +178,68 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
     p.z_row = epi_asym ? (const __half *)z1 : nullptr;
     if (small) return linear_dispatch(codes, W, M, N, K, 1, p, out, nullptr, st);
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, codes, W, M, N, K, 1, p, out, nullptr, st);
+}
+
+// ---- scratch held inside the library ------------------------------------------------------
+// duq4_linear_w4a4_from_fp16_static keeps its intermediate (activation codes and per-token
+// scales / zero-points) in this array instead of caller memory. The array is part of the
+// library image: every GPU on which the library's kernels get loaded carries its own copy
+// until the process exits. Inside host code the name `g_static_scratch` is only a handle for
+// the runtime, never a device address: the address used in launches is the one
+// cudaGetSymbolAddress returns for the device that is current at the time of the query.
+static __device__ __align__(256) unsigned char g_static_scratch[DUQ4_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void **out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void *addr[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return DUQ4_ERR_DEVICE;
+    std::lock_guard<std::mutex> g(mu);
+    if (!addr[dev]) {  // first use on this device: resolve the symbol with this device current
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p || (reinterpret_cast<uintptr_t>(p) & 255) != 0) return DUQ4_ERR_WORKSPACE;
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return DUQ4_OK;
+}
+
+int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                      float clip_ratio, const duq4_epilogue *epi, void *out, void *stream) {
+    if (!x || !W || !out || !epi) return DUQ4_ERR_NULL;
+    if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (duq4_linear_from_fp16_workspace_bytes(M, K) > (size_t)DUQ4_STATIC_SCRATCH_BYTES) return DUQ4_ERR_TOO_LARGE;
+    EpiParams p;
+    int rc = check_epi(epi, N, false, &p);
+    if (rc) return rc;
+    if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
+    const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
+    const bool act_asym = act_mode == DUQ4_MODE_ASYM || act_mode == DUQ4_MODE_ASYM_DUAL;
+    if (epi_asym && !act_asym) return DUQ4_ERR_MODE;
+    void *base = nullptr;
+    rc = static_scratch_address(&base);
+    if (rc) return rc;
+    uint8_t *ws = (uint8_t *)base;
+    const size_t off = align_up(codes_bytes(M, K), 256), vec = align_up((size_t)M * 2, 256);
+    const bool small = M <= kSmallM;
+    void *s1 = ws + off, *z1 = ws + off + vec, *s2 = ws + off + 2 * vec, *z2 = ws + off + 3 * vec;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Nothing in the scratch has to start at zero: the quantizer overwrites every code byte and
+    // every per-token vector entry the GEMM reads before the GEMM reads it.
+    rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, ws, s1, z1, s2, z2, st, !small);
+    if (rc) return rc;
+    p.s_row = (const __half *)s1;
+    p.z_row = epi_asym ? (const __half *)z1 : nullptr;
+    if (small) return linear_dispatch(ws, W, M, N, K, 1, p, out, nullptr, st);
+    // tensor maps are encoded on the stack for this call: no cache insertion, no host heap use
+    return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, ws, W, M, N, K, 1, p, out, nullptr, st, false);
 }
 
 int duq4_last_device_status(void *stream, int32_t *status_out) {

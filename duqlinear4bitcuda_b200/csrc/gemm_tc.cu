@@ -507,11 +507,11 @@ struct MapKeyHash {
 
 // Byte tensor [batch, rows, kbytes] (kbytes contiguous); box = [1, box_rows, box_k].
 static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
-                   bool swizzle128, CUtensorMap *out) {
+                   bool swizzle128, CUtensorMap *out, bool use_cache = true) {
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     MapKey key{ptr, kbytes, rows, batch, box_k, box_rows, swizzle128 ? 1u : 0u};
-    {
+    if (use_cache) {
         std::lock_guard<std::mutex> g(mu);
         auto it = cache.find(key);
         if (it != cache.end()) {
@@ -530,7 +530,7 @@ static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t bat
                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return DUQ4_ERR_SHAPE;
-    {
+    if (use_cache) {
         std::lock_guard<std::mutex> g(mu);
         if (cache.size() > 4096) cache.clear();
         cache[key] = m;
@@ -551,7 +551,7 @@ static int sm_count() {
 }
 
 template <int MODE, int BN, int UW, int NPK_, int NUP_>
-static int launch(const void *A, const void *B, const Args &args, cudaStream_t st) {
+static int launch(const void *A, const void *B, const Args &args, cudaStream_t st, bool cache_maps) {
     using C = Cfg<MODE, BN, UW, NPK_, NUP_>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -562,9 +562,9 @@ static int launch(const void *A, const void *B, const Args &args, cudaStream_t s
     }
     const bool a_packed = MODE == MODE_I4, b_packed = MODE != MODE_I8;
     CUtensorMap ma, mb;
-    int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma);
+    int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma, cache_maps);
     if (rc) return rc;
-    rc = get_map(B, b_packed ? args.K / 2 : args.K, args.N, args.batch, b_packed ? BK / 2 : BK, BN, !b_packed, &mb);
+    rc = get_map(B, b_packed ? args.K / 2 : args.K, args.N, args.batch, b_packed ? BK / 2 : BK, BN, !b_packed, &mb, cache_maps);
     if (rc) return rc;
     uint32_t tiles = args.tiles_m * args.tiles_n * args.batch;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
@@ -587,7 +587,7 @@ static int variant() {
 
 // A [batch,M,K] x B [batch,N,K]^T. mode: tc::MODE_I8 / MODE_I4 / MODE_A8B4 (see above).
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
     using namespace tc;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (mode != MODE_I8 && K >= 131072u) return DUQ4_ERR_SHAPE;  // 256x-scaled accumulators must fit int32
@@ -602,18 +602,18 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     const bool wide = (uint64_t)a.tiles_m * cdiv(N, 256) * batch >= 120 || N > 128 * 148;
     a.tiles_n = cdiv(N, wide ? 256 : 128);
     const int v = variant();
-    if (mode == MODE_I8) return wide ? launch<MODE_I8, 256, 4, 1, 4>(A, B, a, st) : launch<MODE_I8, 128, 4, 1, 6>(A, B, a, st);
+    if (mode == MODE_I8) return wide ? launch<MODE_I8, 256, 4, 1, 4>(A, B, a, st, cache_maps) : launch<MODE_I8, 128, 4, 1, 6>(A, B, a, st, cache_maps);
     if (mode == MODE_I4) {
-        if (!wide) return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st);
-        if (v == 0) return launch<MODE_I4, 256, 4, 4, 2>(A, B, a, st);
-        if (v == 2) return launch<MODE_I4, 256, 8, 4, 2>(A, B, a, st);
-        return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st);
+        if (!wide) return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
+        if (v == 0) return launch<MODE_I4, 256, 4, 4, 2>(A, B, a, st, cache_maps);
+        if (v == 2) return launch<MODE_I4, 256, 8, 4, 2>(A, B, a, st, cache_maps);
+        return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
     }
     if (mode == MODE_A8B4) {
-        if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st);
-        if (v == 0) return launch<MODE_A8B4, 256, 4, 4, 3>(A, B, a, st);
-        if (v == 2) return launch<MODE_A8B4, 256, 8, 4, 3>(A, B, a, st);
-        return launch<MODE_A8B4, 256, 12, 4, 3>(A, B, a, st);
+        if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
+        if (v == 0) return launch<MODE_A8B4, 256, 4, 4, 3>(A, B, a, st, cache_maps);
+        if (v == 2) return launch<MODE_A8B4, 256, 8, 4, 3>(A, B, a, st, cache_maps);
+        return launch<MODE_A8B4, 256, 12, 4, 3>(A, B, a, st, cache_maps);
     }
     return DUQ4_ERR_MODE;
 }

@@ -36,6 +36,7 @@ extern "C" {
 #define DUQ4_ERR_ALIGN (-5)       /* a pointer is not aligned as required */
 #define DUQ4_ERR_DEVICE (-6)      /* not an sm_100 device / driver entry point unavailable */
 #define DUQ4_ERR_TIMEOUT (-7)     /* a bounded device-side wait gave up (see duq4_last_device_status) */
+#define DUQ4_ERR_TOO_LARGE (-8)   /* duq4_linear_w4a4_from_fp16_static: scratch need exceeds DUQ4_STATIC_SCRATCH_BYTES */
 
 /* Column split of the dual-uniform schemes (ref: include/quant.h:5, QUANT_COL_K). */
 #define DUQ4_QUANT_COL_K 10
@@ -214,6 +215,36 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
                                uint32_t K, int act_mode, float clip_ratio,
                                const duq4_epilogue *epi, void *out, void *workspace,
                                size_t workspace_bytes, void *stream);
+
+/* Capacity of the scratch array built into the library (2 MiB per GPU that loads it). */
+#define DUQ4_STATIC_SCRATCH_BYTES (2u << 20)
+
+/* duq4_linear_w4a4_from_fp16 for callers that have no device memory to lend and may not
+ * allocate any: it takes no workspace argument and makes no allocation of any kind (no
+ * cudaMalloc/cudaFree, no pooled or library allocator, no host heap). Typical callers: a
+ * plugin running inside a serving process whose allocator has already claimed the whole GPU
+ * (a cudaMalloc there fails or stalls the device), code on a latency path where an allocation's
+ * implicit device synchronisation is not acceptable, and small embedders that only own their
+ * input and output tensors. This entry point has NO counterpart in the reference project.
+ *
+ * The intermediate (activation codes + per-token scales / zero-points) lives in a fixed array
+ * inside the library image, DUQ4_STATIC_SCRATCH_BYTES per GPU, resident on every GPU that loads
+ * the library until the process exits. Consequences:
+ *   - size limit: duq4_linear_from_fp16_workspace_bytes(M, K) must not exceed
+ *     DUQ4_STATIC_SCRATCH_BYTES (all M <= 16 decode shapes up to K = 131008 fit; e.g. M = 256 at
+ *     K = 8192 is just over). Larger problems are rejected with DUQ4_ERR_TOO_LARGE before any
+ *     launch; use duq4_linear_w4a4_from_fp16 with your own workspace for those.
+ *   - one array per GPU shared by ALL calls: two calls that can overlap on the same GPU
+ *     (different streams, or different host threads without ordering) race on it and produce
+ *     garbage. Serialise them on one stream or with events.
+ *   - the array keeps whatever the previous call left; every byte a call reads is written by
+ *     that same call first, so no clearing is needed between calls.
+ *   - the first call on each GPU looks up the array's device address (cudaGetSymbolAddress, with
+ *     that GPU current) and remembers it; make that first call outside any stream capture.
+ * Arguments, modes, results and status codes otherwise equal duq4_linear_w4a4_from_fp16. */
+int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t M, uint32_t N,
+                                      uint32_t K, int act_mode, float clip_ratio,
+                                      const duq4_epilogue *epi, void *out, void *stream);
 
 /* Device-side status word of the most recent tensor-core GEMM on the current device:
  * 0 = no bounded wait expired. Reads back 4 bytes (synchronises the stream given). */

@@ -1,0 +1,68 @@
+"""duq4_linear_w4a4_from_fp16_static -- the entry point for callers that cannot allocate or lend
+device memory (a plugin inside a server whose allocator owns the whole GPU, code on a latency
+path that must not trigger an allocation's device synchronisation). Its scratch is a fixed
+2 MiB array inside the library, so this test checks, through the C ABI:
+
+  * two calls in a row give exactly the output of the workspace-taking entry point
+    (bit-identical fp16, the tolerance the other GPU tests use), although the second call finds
+    the first call's leftovers in the shared array;
+  * a problem whose scratch need exceeds the array is refused with DUQ4_ERR_TOO_LARGE (-8)
+    before anything is launched.
+
+The file is named so that pytest collects it last."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,N,K,mode", [(4, 520, 1024, "sym"), (16, 384, 4096, "asym"), (100, 264, 2048, "sym")])
+def test_static_scratch_entry_matches_workspace_entry_twice(M, N, K, mode):
+    import torch
+    import duqlinear4bitcuda_b200.lib as L
+
+    st = L.current_stream()
+    dw = torch.from_numpy(U.rand_codes(N, K, 11)).cuda()
+    dsw = torch.from_numpy(U.rand_scales(N, 12)).cuda()
+    dzc = torch.from_numpy(U.rand_zeros(N, 13)).cuda()
+    bias = torch.from_numpy(np.random.default_rng(14).standard_normal(N).astype(np.float16)).cuda()
+    epi = L.make_epilogue(mode, None, None, dsw, dzc if mode == "asym" else None, bias=bias)
+    nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+    assert nbytes <= 2 << 20
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    for call in range(2):  # different activations per call: the second sees the first's leftovers
+        x = torch.from_numpy(U.acts(M, K, 20 + call, mean=0.1 if mode == "asym" else 0.0)).cuda()
+        want = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+        got = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+        L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), L.ptr(want),
+               L.ptr(ws), nbytes, st)
+        L.call("duq4_linear_w4a4_from_fp16_static", L.ptr(x), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi),
+               L.ptr(got), st)
+        torch.cuda.synchronize()
+        assert U.f16_equal_nan(got.cpu().numpy(), want.cpu().numpy()), f"call {call}"
+        assert not torch.isnan(got).all()
+    status = ctypes.c_int32(-1)
+    L.call("duq4_last_device_status", st, ctypes.byref(status))
+    assert status.value == 0
+
+
+def test_static_scratch_entry_rejects_oversized_problem():
+    import torch
+    import duqlinear4bitcuda_b200.lib as L
+
+    M, N, K = 512, 128, 8192  # needs 4 MiB of scratch
+    assert L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K) > 2 << 20
+    x = torch.zeros((M, K), dtype=torch.float16, device="cuda")
+    w = torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda")
+    s = torch.ones(N, dtype=torch.float16, device="cuda")
+    out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    epi = L.make_epilogue("sym", None, None, s)
+    rc = L.cdll.duq4_linear_w4a4_from_fp16_static(L.ptr(x), L.ptr(w), M, N, K, L.MODE_SYM, 1.0, ctypes.byref(epi), L.ptr(out),
+                                                  L.current_stream())
+    assert rc == -8
+    assert b"scratch" in L.cdll.duq4_error_string(rc)
+    torch.cuda.synchronize()
