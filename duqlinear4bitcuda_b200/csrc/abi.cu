@@ -11,6 +11,8 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
 int tc_status_read(cudaStream_t st, int32_t *out);
+int gemv_status_read(int32_t *out);
+extern int g_static_weights;
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
                             void *z1, void *s2, void *z2, cudaStream_t st, bool out8);
 
@@ -82,6 +84,12 @@ const char *duq4_error_string(int status) {
 }
 
 int duq4_dual_quant_col_k(void) { return DUQ4_QUANT_COL_K; }
+
+int duq4_set_static_weights(int on) {
+    int prev = g_static_weights;
+    g_static_weights = on ? 1 : 0;
+    return prev;
+}
 
 int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
     EpiParams p{};
@@ -244,7 +252,13 @@ int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t 
 
 int duq4_last_device_status(void *stream, int32_t *status_out) {
     if (!status_out) return DUQ4_ERR_NULL;
-    return tc_status_read((cudaStream_t)stream, status_out);
+    int32_t a = 0, b = 0;
+    int rc = tc_status_read((cudaStream_t)stream, &a);   // synchronises the stream
+    if (rc) return rc;
+    rc = gemv_status_read(&b);
+    if (rc) return rc;
+    *status_out = a ? a : (b ? 100 + b : 0);   // 1..9: tensor-core GEMM wait, 101..: small-M kernel wait
+    return DUQ4_OK;
 }
 
 }  // extern "C"

@@ -27,12 +27,15 @@
 #include <unordered_map>
 
 #include "duq_common.cuh"
+#include "duq_ptx.cuh"
 
 namespace duq4 {
 
 __device__ int g_tc_status = 0;  // 0 = ok, else code of the wait that expired
 
 namespace tc {
+
+using namespace ptx;
 
 constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // K elements per pipeline stage (= one 128-byte swizzle row of int8)
@@ -44,57 +47,8 @@ constexpr int MODE_A8B4 = 2;   // A already unpacked in HBM (int8 = 16*s4, K per
                                // exactly as the in-kernel unpack permutes it), B packed int4
 // warps: 0 TMA producer, 1 MMA issuer, 2..5 epilogue, 6..6+UW-1 unpack, last: second TMA producer (A of MODE_A8B4)
 __host__ __device__ constexpr int threads_for(int uw) { return 32 * (2 + kEpiWarps + uw + 1); }
-constexpr uint64_t kWaitLimitNs = 1000000000ull;
+constexpr uint64_t kWaitLimitNs = kPtxWaitLimitNs;
 
-// ---- PTX wrappers ---------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint64_t globaltimer() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait. Returns false when the CTA is aborting (this or another wait expired).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try(bar, parity)) return true;
-        if ((it & 0xFFu) == 0) {
-            if (*abort_flag) return false;
-            uint64_t now = globaltimer();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                atomicCAS(&g_tc_status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -241,19 +195,19 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                     if (MODE == MODE_I4) {
                         uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
-                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, 1))) break;
+                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc_status, 1))) break;
                         uint32_t dst = pk0 + s * C::kPackedStage;
                         mbar_expect_tx(pk_full(s), C::kPackedStage);
                         tma_load_3d(dst, &tmA, pk_full(s), ks * (BK / 2), tm * BM, b);
                         tma_load_3d(dst + BM * (BK / 2), &tmB, pk_full(s), ks * (BK / 2), tn * BN, b);
                     } else if (MODE == MODE_A8B4) {
                         uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
-                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, 1))) break;
+                        if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc_status, 1))) break;
                         mbar_expect_tx(pk_full(s), C::kPackedStage);
                         tma_load_3d(pk0 + s * C::kPackedStage, &tmB, pk_full(s), ks * (BK / 2), tn * BN, b);
                     } else {
                         uint32_t s = it % C::NUP, ph = (it / C::NUP) & 1;
-                        if (!(ok = mbar_wait(up_empty(s), ph ^ 1, abortp, 1))) break;
+                        if (!(ok = mbar_wait(up_empty(s), ph ^ 1, abortp, &g_tc_status, 1))) break;
                         uint32_t dst = up0 + s * C::kUnpackedStage;
                         mbar_expect_tx(up_full(s), C::kUnpackedStage);
                         tma_load_3d(dst, &tmA, up_full(s), ks * BK, tm * BM, b);
@@ -277,7 +231,7 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
                 uint32_t tm = r % a.tiles_m;
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                     uint32_t u = it % C::NUP, uph = (it / C::NUP) & 1;
-                    if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, 7))) break;
+                    if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc_status, 7))) break;
                     mbar_expect_tx(up_full(u), BM * BK);
                     tma_load_3d(up0 + u * C::kUnpackedStage, &tmA, up_full(u), ks * BK, tm * BM, b);
                 }
@@ -295,12 +249,12 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
             bool ok = true, issued = false;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
                 uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
-                if (!(ok = mbar_wait(acc_empty(buf), aph ^ 1, abortp, 2))) break;
+                if (!(ok = mbar_wait(acc_empty(buf), aph ^ 1, abortp, &g_tc_status, 2))) break;
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + buf * BN;
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                     uint32_t s = it % C::NUP, ph = (it / C::NUP) & 1;
-                    if (!(ok = mbar_wait(up_full(s), ph, abortp, 3))) break;
+                    if (!(ok = mbar_wait(up_full(s), ph, abortp, &g_tc_status, 3))) break;
                     tc_fence_after();
                     uint32_t sa = up0 + s * C::kUnpackedStage, sb = sa + BM * BK;
                     uint64_t da = make_desc(sa), db = make_desc(sb);
@@ -356,7 +310,7 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
                 }
             }
             __syncwarp();
-            if (!(ok = mbar_wait(acc_full(buf), aph, abortp, 4))) break;
+            if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc_status, 4))) break;
             tc_fence_after();
 
             const uint32_t m = tm * BM + row_in_tile;
@@ -432,8 +386,8 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                 uint32_t s = it % C::NPK, ph = (it / C::NPK) & 1;
                 uint32_t u = it % C::NUP, uph = (it / C::NUP) & 1;
-                if (!(ok = mbar_wait(pk_full(s), ph, abortp, 5))) break;
-                if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, 6))) break;
+                if (!(ok = mbar_wait(pk_full(s), ph, abortp, &g_tc_status, 5))) break;
+                if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc_status, 6))) break;
                 const uint32_t src = pk0 + s * C::kPackedStage, dst = up0 + u * C::kUnpackedStage + kDstOff;
 #pragma unroll 4
                 for (int idx = ut; idx < kChunks; idx += kUnpackWarps * 32) {
@@ -538,6 +492,15 @@ static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t bat
     *out = m;
     return DUQ4_OK;
 }
+
+}  // namespace tc
+
+int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
+                      bool swizzle128, CUtensorMap *out) {
+    return tc::get_map(ptr, kbytes, rows, batch, box_k, box_rows, swizzle128, out, true);
+}
+
+namespace tc {
 
 static int sm_count() {
     static int n = 0;

@@ -14,9 +14,11 @@
 //
 // A CTA owns 16*R consecutive weight rows; its 8 warps split K and reduce through shared
 // memory, so no global scratch is needed and the result does not depend on scheduling.
-#include <mma.h>
+#include <cuda.h>
+#include <stdlib.h>
 
 #include "duq_common.cuh"
+#include "duq_ptx.cuh"
 
 namespace duq4 {
 
@@ -29,6 +31,10 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+// Programmatic dependent launch (no-ops unless the launch carries the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
 __device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return w & 0xF0F0F0F0u; }
@@ -88,6 +94,13 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         ap[h] = reinterpret_cast<const uint4 *>(A + (size_t)(aok[h] ? m : 0) * kb);
     }
 
+    // Weights are parameters: with the "static weights" option on, the launch carries the
+    // programmatic-serialization attribute and this grid may start while the previous kernel of
+    // the stream is still draining. Its first batch of weight loads is issued right away; the
+    // activations (and every write) wait for the previous grid. Without the attribute both
+    // instructions do nothing.
+    pdl_launch_dependents();
+    bool waited = false;
     constexpr int U = 4;  // k-steps in flight per warp
     for (uint32_t s0 = warp * U; s0 < nstep; s0 += kGemvWarps * U) {
         uint4 wv[U][R][2], av[U][TH];
@@ -100,6 +113,15 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
                 wv[u][r][0] = ok ? ldg_stream(wp[r][0] + ch) : make_uint4(0, 0, 0, 0);
                 wv[u][r][1] = ok ? ldg_stream(wp[r][1] + ch) : make_uint4(0, 0, 0, 0);
             }
+        }
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            uint32_t ch = (s0 + u) * 4 + t;
+            bool ok = ch < nchunk;
 #pragma unroll
             for (int h = 0; h < TH; ++h) av[u][h] = (ok && aok[h]) ? __ldg(ap[h] + ch) : make_uint4(0, 0, 0, 0);
         }
@@ -122,6 +144,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         }
     }
 
+    if (!waited) pdl_wait();
     // Cross-warp (split-K) reduction. Fragment element i of acc[r][h]: weight row
     // 16r + g + 8*(i>>1), token 8h + 2t + (i&1).
 #pragma unroll
@@ -149,23 +172,280 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// TMA-streamed variant (used for 9..16 tokens on layers with many rows).
+//
+// Same arithmetic as gemv_w4a4_kernel, different data movement: a persistent CTA per SM keeps a
+// ring of shared-memory stages filled by TMA (one elected thread issues cp.async.bulk.tensor
+// copies of [16*R weight rows] x [1 KiB of K], 128B-swizzled), so HBM requests stay in flight
+// across row blocks instead of draining at every CTA boundary. Eight consumer warps each own one
+// 128-byte K slice of a stage; a ninth warp is the producer. Partial sums of the eight warps meet
+// in shared memory once per row block (double-buffered, one named barrier per block).
+// Control flow never depends on a failed wait: after a bounded wait expires every remaining
+// wait is skipped, all warps still reach every barrier, and the status word is raised.
+__device__ int g_gemv_status = 0;
+
+constexpr int kStageKBytes = 1024;   // K bytes per row per stage (8 warps x 128 B)
+
+template <int R>
+struct GemvSmem {
+    static constexpr int kRows = 16 * R;
+    static constexpr int kStageBytes = kRows * kStageKBytes;
+    static constexpr int kStages = R == 2 ? 5 : 8;   // 160 KiB / 128 KiB of weights in flight per SM
+    static constexpr int kRedInts = 2 * kGemvWarps * 16 * (kRows + 1);
+    static constexpr int kBytes = 1024 + kStages * kStageBytes + kRedInts * 4 + 2 * kStages * 8 + 16;
+};
+
+template <int R, int TH>
+__global__ void __launch_bounds__((kGemvWarps + 1) * 32, 1)
+gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__restrict__ A, uint32_t M, uint32_t N,
+                     uint32_t K, uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0) {
+    using namespace ptx;
+    using S = GemvSmem<R>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int abort_flag;
+    const uint32_t raw = smem_u32(smem_raw), base = (raw + 1023u) & ~1023u;
+    int *red = reinterpret_cast<int *>(smem_raw + (base - raw) + S::kStages * S::kStageBytes);
+    const uint32_t bar0 = base + S::kStages * S::kStageBytes + S::kRedInts * 4;
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (S::kStages + s); };
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t kb = K >> 1;
+    const uint32_t nks = (kb + kStageKBytes - 1) / kStageKBytes;       // stages per row block
+    const uint32_t blocks_per_b = (N + S::kRows - 1) / S::kRows;
+    const uint32_t units = blocks_per_b * batch;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < S::kStages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), kGemvWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *abortp = &abort_flag;
+    pdl_launch_dependents();   // see gemv_w4a4_kernel: weights may stream before the previous grid ends
+
+    if (warp == kGemvWarps) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
+                const uint32_t b = u / blocks_per_b, row0 = (u % blocks_per_b) * S::kRows;
+                for (uint32_t ks = 0; ks < nks; ++ks, ++it) {
+                    const uint32_t s = it % S::kStages, ph = (it / S::kStages) & 1;
+                    if (ok) ok = mbar_wait(empty(s), ph ^ 1, abortp, &g_gemv_status, 1);
+                    if (!ok) continue;
+                    const uint32_t k0 = ks * kStageKBytes;
+                    const uint32_t nbox = min(8u, (kb - k0 + 127u) / 128u);   // boxes with any K inside the row
+                    mbar_expect_tx(full(s), nbox * 128u * S::kRows);
+                    const uint32_t dst = base + s * S::kStageBytes;
+                    for (uint32_t j = 0; j < nbox; ++j)
+                        tma_load_3d(dst + j * (128u * S::kRows), &tmW, full(s), (int)(k0 + j * 128u), (int)row0, (int)b);
+                }
+            }
+            if (!ok) {  // let copies already issued land before the CTA retires
+                uint64_t t0 = globaltimer();
+                while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t it = 0, lu = 0;
+        bool ok = true;
+        pdl_wait();   // activations come from the previous grid; outputs may still be read by it
+        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, ++lu) {
+            const uint32_t b = u / blocks_per_b, row0 = (u % blocks_per_b) * S::kRows;
+            const uint8_t *Ab = A + (size_t)b * M * kb;
+            int acc[R][TH][4];
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int h = 0; h < TH; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[r][h][i] = 0;
+
+            for (uint32_t ks = 0; ks < nks; ++ks, ++it) {
+                const uint32_t s = it % S::kStages, ph = (it / S::kStages) & 1;
+                // token slice for this warp's 128 bytes of K: issued before the wait, it does not depend on it
+                const uint32_t kbyte = ks * kStageKBytes + warp * 128u + 32u * t;
+                const bool kin = kbyte < kb;   // kb is a multiple of 32: in range means the whole 32 bytes are
+                uint4 tk[TH][2];
+#pragma unroll
+                for (int h = 0; h < TH; ++h) {
+                    const uint32_t m = g + 8 * h;
+                    const bool lok = kin && m < M;
+                    const uint4 *ap = reinterpret_cast<const uint4 *>(Ab + (size_t)(lok ? m : 0) * kb + (lok ? kbyte : 0));
+                    tk[h][0] = lok ? __ldg(ap) : make_uint4(0, 0, 0, 0);
+                    tk[h][1] = lok ? __ldg(ap + 1) : make_uint4(0, 0, 0, 0);
+                }
+                if (ok) ok = mbar_wait(full(s), ph, abortp, &g_gemv_status, 2);
+                if (ok && ks * kStageKBytes + warp * 128u < kb) {
+                    const uint32_t box = base + s * S::kStageBytes + warp * (128u * S::kRows);
+                    const uint32_t c0 = (uint32_t)((2 * t) ^ g) << 4, c1 = (uint32_t)((2 * t + 1) ^ g) << 4;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t ra = box + (16 * r + g) * 128u, rb = ra + 8 * 128u;
+                        uint32_t wa[2][4], wb[2][4];
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wa[0][0]), "=r"(wa[0][1]), "=r"(wa[0][2]), "=r"(wa[0][3]) : "r"(ra + c0));
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wa[1][0]), "=r"(wa[1][1]), "=r"(wa[1][2]), "=r"(wa[1][3]) : "r"(ra + c1));
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wb[0][0]), "=r"(wb[0][1]), "=r"(wb[0][2]), "=r"(wb[0][3]) : "r"(rb + c0));
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wb[1][0]), "=r"(wb[1][1]), "=r"(wb[1][2]), "=r"(wb[1][3]) : "r"(rb + c1));
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t a0 = nib_lo(wa[q][j]), a1 = nib_lo(wb[q][j]), a2 = nib_hi(wa[q][j]), a3 = nib_hi(wb[q][j]);
+#pragma unroll
+                                for (int h = 0; h < TH; ++h) {
+                                    const uint32_t tw = reinterpret_cast<const uint32_t *>(&tk[h][q])[j];
+                                    mma_s8(acc[r][h], a0, a1, a2, a3, nib_lo(tw), nib_hi(tw));
+                                }
+                            }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty(s));
+            }
+
+            // split-K reduction across the eight warps, then the dequant epilogue
+            int *rd = red + (lu & 1) * (kGemvWarps * 16 * (S::kRows + 1));
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int h = 0; h < TH; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        rd[(warp * 16 + 8 * h + 2 * t + (i & 1)) * (S::kRows + 1) + 16 * r + g + 8 * (i >> 1)] = acc[r][h][i];
+            asm volatile("bar.sync 1, %0;" ::"n"(kGemvWarps * 32) : "memory");
+            const EpiParams p = epi_for_batch(p0, b);
+            for (uint32_t o = threadIdx.x; o < (uint32_t)S::kRows * 8u * TH; o += kGemvWarps * 32) {
+                const uint32_t nl = o % S::kRows, m = o / S::kRows, n = row0 + nl;
+                if (m >= M || n >= N) continue;
+                int sum = 0;
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) sum += rd[(w * 16 + m) * (S::kRows + 1) + nl];
+                sum >>= 8;  // exact: a multiple of 256
+                if (acc0) acc0[((size_t)b * M + m) * N + n] = sum;
+                if (p.mode != DUQ4_MODE_NONE) {
+                    ColTerms ct = load_col_terms(p, n);
+                    __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
+                    out0[((size_t)b * M + m) * p.ldo + n] = dequant_one(p.mode, sum, p.s_row[m], zr, ct);
+                }
+            }
+        }
+    }
+}
+
+int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
+                     bool swizzle128, CUtensorMap *out);
+
+// Set through duq4_set_static_weights(): the caller promises that weight tensors are not
+// written by earlier work of the same stream, which lets small-M kernels start fetching them
+// while the previous kernel is still finishing.
+int g_static_weights = 0;
+
+template <int R, int TH>
+static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p,
+                      __half *out, int32_t *acc_out, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemvWarps * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_kernel<R, TH>, A, W, M, N, K, p, out, acc_out);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)e;
+    }
+    return launch_status();
+}
+
+template <int R, int TH>
+static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms) {
+    using S = GemvSmem<R>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    CUtensorMap mw;
+    int rc = tma_map_bytes_3d(W, K / 2, N, batch, 128, S::kRows, true, &mw);
+    if (rc) return rc;
+    const uint32_t units = cdiv(N, S::kRows) * batch;
+    const uint32_t grid = units < (uint32_t)sms ? units : (uint32_t)sms;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((kGemvWarps + 1) * 32);
+    cfg.dynamicSmemBytes = S::kBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_tma_kernel<R, TH>, mw, A, M, N, K, batch, p, (__half *)out, acc_out);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)e;
+    }
+    return launch_status();
+}
+
+int gemv_status_read(int32_t *out) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_gemv_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    *out = v;
+    if (v != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int));
+    }
+    return DUQ4_OK;
+}
+
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    static int sms = 0, force = -1;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        const char *e = getenv("DUQ4_GEMV_VARIANT");   // debug: 0 = register-streamed kernel, 1 = TMA-streamed kernel
+        force = e ? atoi(e) : -1;
+    }
+    // Measured on B200 (cold weights, CUDA-graph chain): the TMA-streamed kernel wins once there
+    // are at least two 32-row blocks per SM and more than 8 tokens; the register-streamed one
+    // has the shorter start-up and wins elsewhere.
+    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && M > 8 && (uint64_t)cdiv(N, 32) * batch >= 2ull * sms);
+    if (use_tma) {
+        const bool two = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
+        if (M <= 8) return two ? launch_tma<2, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms)
+                               : launch_tma<1, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+        return two ? launch_tma<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms)
+                   : launch_tma<1, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+    }
     // Two row groups per CTA halve the token re-reads; one keeps at least ~2 CTAs per SM
     // busy when N is small.
     const bool r2 = (uint64_t)(N / 32) * batch >= 2 * 148;
     const uint32_t rows_per_cta = r2 ? 32 : 16;
     dim3 grid(cdiv(N, rows_per_cta), batch), block(kGemvWarps * 32);
     __half *o = (__half *)out;
-    if (M <= 8) {
-        if (r2) gemv_w4a4_kernel<2, 1><<<grid, block, 0, st>>>(A, W, M, N, K, p, o, acc_out);
-        else gemv_w4a4_kernel<1, 1><<<grid, block, 0, st>>>(A, W, M, N, K, p, o, acc_out);
-    } else {
-        if (r2) gemv_w4a4_kernel<2, 2><<<grid, block, 0, st>>>(A, W, M, N, K, p, o, acc_out);
-        else gemv_w4a4_kernel<1, 2><<<grid, block, 0, st>>>(A, W, M, N, K, p, o, acc_out);
-    }
-    return launch_status();
+    (void)block;
+    if (M <= 8) return r2 ? launch_reg<2, 1>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 1>(grid, A, W, M, N, K, p, o, acc_out, st);
+    return r2 ? launch_reg<2, 2>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 2>(grid, A, W, M, N, K, p, o, acc_out, st);
 }
 
 }  // namespace duq4

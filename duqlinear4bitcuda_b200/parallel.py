@@ -1,0 +1,118 @@
+"""Column-parallel W4A4 linear: the output channels (weight rows) of one layer are split into
+contiguous blocks over the ranks of a torch.distributed group, one process per GPU.
+
+The reference has no multi-GPU code. The layer shards naturally: output column n depends only on
+weight row n, its per-channel vectors and the (replicated) activations. Every rank quantizes the
+activations itself, so codes and per-token scales are bit-identical everywhere, computes its
+[M, N/G] block with the fused kernel, and the blocks are exchanged with ONE all-gather (NCCL on
+GPUs, gloo in the CPU tests of the host logic). Results equal the unsharded layer bit for bit;
+the dual-uniform selectors, which depend on the GLOBAL output column, receive the shard's
+column offset.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n_out: int, world: int, rank: int):
+    """[begin, end) of the output channels owned by `rank`. Blocks are contiguous and as even as
+    possible, each a multiple of 8 channels wide (16-byte fp16 row segments) except possibly the
+    last."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    per = -(-n_out // world)
+    per = -(-per // 8) * 8
+    b = min(n_out, rank * per)
+    return b, min(n_out, b + per)
+
+
+def shard_rows(t: torch.Tensor, world: int, rank: int):
+    """Rows [begin,end) of a per-channel tensor ([N, ...]) for `rank`."""
+    b, e = shard_bounds(t.shape[0], world, rank)
+    return t[b:e].contiguous()
+
+
+def gather_columns(local: torch.Tensor, n_out: int, group=None, out: torch.Tensor = None):
+    """All-gather of the column blocks: `local` is this rank's [M, n_local] block (n_local per
+    shard_bounds); returns the row-major [M, n_out] tensor on every rank. Even shards take one
+    all_gather_into_tensor plus one strided copy; ragged shards (last rank narrower) are padded to
+    the common width first."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    M = local.shape[0]
+    width = shard_bounds(n_out, world, 0)[1]
+    b, e = shard_bounds(n_out, world, rank)
+    if local.shape[1] != e - b:
+        raise ValueError(f"rank {rank}: block has {local.shape[1]} columns, shard_bounds says {e - b}")
+    if e - b != width:
+        padded = local.new_zeros((M, width))
+        padded[:, : e - b] = local
+        local = padded
+    gathered = local.new_empty((world, M, width))
+    dist.all_gather_into_tensor(gathered.view(world * M, width), local.contiguous(), group=group)
+    full = gathered.permute(1, 0, 2).reshape(M, world * width)
+    if world * width != n_out:
+        full = full[:, :n_out]
+    if out is not None:
+        out.copy_(full)
+        return out
+    return full.contiguous()
+
+
+class ColumnParallelLinear4bit(torch.nn.Module):
+    """One W4A4 layer sharded over a process group. Holds this rank's weight rows and channel
+    vectors; forward takes replicated fp16 activations [.., K] and returns the full fp16 [.., N]
+    on every rank.
+
+    mode: "sym" / "sym_dual" / "asym" / "asym_dual" (activation quantizer and dequant variant).
+    Build it from full-size tensors with `from_full` (each rank keeps only its slice)."""
+
+    def __init__(self, mode, n_out, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None,
+                 clip_ratio=1.0, group=None):
+        super().__init__()
+        self.mode, self.n_out, self.clip_ratio, self.group = mode, n_out, clip_ratio, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.col_begin, self.col_end = shard_bounds(n_out, self.world, self.rank)
+        for name, t in (("weight", weight), ("scales_1", scales_1), ("zeros_1", zeros_1), ("scales_2", scales_2),
+                        ("zeros_2", zeros_2), ("bias", bias)):
+            if t is not None:
+                if t.shape[0] != self.col_end - self.col_begin:
+                    raise ValueError(f"{name}: expected {self.col_end - self.col_begin} rows, got {t.shape[0]}")
+                self.register_buffer(name, t.contiguous())
+            else:
+                setattr(self, name, None)
+        self._ws = None
+
+    @classmethod
+    def from_full(cls, mode, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None, clip_ratio=1.0,
+                  group=None):
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        cut = lambda t: None if t is None else shard_rows(t, world, rank)
+        return cls(mode, weight.shape[0], cut(weight), cut(scales_1), cut(zeros_1), cut(scales_2), cut(zeros_2), cut(bias),
+                   clip_ratio, group)
+
+    def local_forward(self, x2d: torch.Tensor):
+        """This rank's [M, n_local] block through the fused C-ABI entry point."""
+        from . import lib as L
+        M, K = x2d.shape
+        n_local = self.col_end - self.col_begin
+        need = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+        if self._ws is None or self._ws.numel() < need or self._ws.device != x2d.device:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=x2d.device)
+        flat = lambda t: None if t is None else t.reshape(-1)
+        epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                              flat(self.zeros_2), self.bias, col_offset=self.col_begin)
+        out = torch.empty((M, n_local), dtype=torch.float16, device=x2d.device)
+        with torch.cuda.device(x2d.device):
+            L.call("duq4_linear_w4a4_from_fp16", L.ptr(x2d), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
+                   float(self.clip_ratio), ctypes.byref(epi), L.ptr(out), L.ptr(self._ws), self._ws.numel(), L.current_stream())
+        return out
+
+    def forward(self, x: torch.Tensor):
+        x2d = x.reshape(-1, x.shape[-1]).contiguous()
+        local = self.local_forward(x2d)
+        full = local if self.world == 1 else gather_columns(local, self.n_out, self.group)
+        return full.view(*x.shape[:-1], self.n_out)

@@ -79,6 +79,48 @@ def test_decode_linear_modes(env, mode, M):
     run_linear(torch, L, o, mode, M, 264, 512, seed=M + 200, col0=8)  # sharded: global column offset
 
 
+@pytest.mark.parametrize("mode", ["sym_dual", "asym", "asym_dual"])
+@pytest.mark.parametrize("M,N,K", [(1, 264, 4096), (7, 1000, 4160), (16, 4744, 8192), (12, 40, 5120)])
+def test_decode_streaming_kernel_modes(env, mode, M, N, K):
+    """Ragged N, K not a multiple of the 2048-element stage, every epilogue mode, sharded column
+    offset, on both small-M kernels (the dispatcher picks by shape; the debug variable
+    DUQ4_GEMV_VARIANT pins one)."""
+    torch, L, o = env
+    run_linear(torch, L, o, mode, M, N, K, seed=M + N, bias=(M != 7), col0=(6 if M == 16 else 0))
+
+
+@pytest.mark.parametrize("variant", ["0", "1"])
+def test_decode_both_kernels_pinned(variant):
+    """Each small-M kernel forced for every shape, in a fresh process (the choice is read once)."""
+    import os, subprocess, sys
+    env2 = dict(os.environ, DUQ4_GEMV_VARIANT=variant)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", os.path.abspath(__file__), "-k",
+                        "decode_streaming_kernel_modes or decode_linear_sym or decode_few_tokens or decode_streaming_kernel_batched"],
+                       env=env2, capture_output=True, text=True, cwd=U.ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(1, 64), (8, 64), (333, 1088), (4096, 4096), (5000, 11008), (130, 28672)])
+def test_decode_few_tokens_shapes(env, M, N, K):
+    """1..4 tokens: single rows, ragged N, K that is not a multiple of a k-step, long rows."""
+    torch, L, o = env
+    mode = ["sym", "asym", "sym_dual", "asym_dual"][M - 1]
+    run_linear(torch, L, o, mode, M, N, K, seed=M * 3 + N, bias=(N % 2 == 0), col0=(3 if M == 4 else 0))
+
+
+def test_decode_streaming_kernel_batched(env):
+    torch, L, o = env
+    B, M, N, K = 3, 5, 200, 4096
+    qa = U.rand_codes(B * M, K, 1).reshape(B, M, K // 2); qw = U.rand_codes(B * N, K, 2).reshape(B, N, K // 2)
+    da, dw = dev(torch, qa), dev(torch, qw)
+    C = torch.zeros((B, M, N), dtype=torch.int32, device="cuda")
+    L.call("duq4_batch_matmul_4bit", L.ptr(da), L.ptr(dw), M, N, K, L.ptr(C), B, L.current_stream())
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert np.array_equal(C.cpu().numpy(), o.batch_matmul_4bit(qa, qw))
+
+
 def test_decode_matmul_int32_all_nibble_pairs(env):
     torch, L, o = env
     v = np.arange(-8, 8, dtype=np.int8)
@@ -285,3 +327,32 @@ def test_preunpacked_activations_match_packed_path(env, mode, M, N, K):
     assert tc_status(L) == 0
     assert np.array_equal(acc_b.cpu().numpy(), o.matmul_4bit(q.cpu().numpy(), qw))
     assert U.f16_equal_nan(out_a.cpu().numpy(), out_b.cpu().numpy())
+
+
+@pytest.mark.parametrize("K", [512, 4096])
+def test_decode_static_weights_overlap_keeps_stream_order(env, K):
+    """With duq4_set_static_weights(1) the small-M kernels start streaming weights before the
+    previous kernel of the stream has finished. Activations written by that previous kernel
+    (here: a device copy queued right before each call) must still be seen, and a chain of calls
+    that reuse one output buffer must leave the last result."""
+    torch, L, o = env
+    M, N = 4, 1032
+    qw = U.rand_codes(N, K, 1); sw = U.rand_scales(N, 2)
+    dw, dsw = dev(torch, qw), dev(torch, sw)
+    srcs = [dev(torch, U.rand_codes(M, K, 10 + i)) for i in range(6)]
+    sa = dev(torch, U.rand_scales(M, 3))
+    qa = torch.zeros((M, K // 2), dtype=torch.uint8, device="cuda")
+    outs = [torch.zeros((M, N), dtype=torch.float16, device="cuda") for _ in range(6)]
+    epi = L.make_epilogue("sym", sa, None, dsw)
+    prev = L.cdll.duq4_set_static_weights(1)
+    try:
+        for i in range(6):
+            tmp = torch.bitwise_xor(srcs[i], 0)   # a kernel that produces the activations ...
+            qa = tmp                               # ... consumed by the very next launch
+            L.call("duq4_linear_w4a4", L.ptr(qa), L.ptr(dw), M, N, K, ctypes.byref(epi), L.ptr(outs[i]), None, L.current_stream())
+        torch.cuda.synchronize()
+    finally:
+        L.cdll.duq4_set_static_weights(prev)
+    for i in range(6):
+        _, want = o.linear_w4a4("sym", srcs[i].cpu().numpy(), qw, sa.cpu().numpy(), None, sw, None, None, None)
+        assert U.f16_equal_nan(outs[i].cpu().numpy(), want), i
