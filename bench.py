@@ -318,12 +318,31 @@ def run_ours(args):
     epi = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns)
     epi_e2e = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns)
 
+    peer = None
+    gather_mode = "none" if world == 1 else args.gather
+    if world > 1 and args.gather == "fused":
+        try:
+            from duqlinear4bitcuda_b200.parallel import PeerOutput
+            peer = PeerOutput(M, N, device)
+            epi_f = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns))
+            epi_f_e2e = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns))
+        except Exception as ex:  # symmetric memory not available on this box: use the collective
+            peer = None
+            gather_mode = f"nccl (symmetric memory unavailable: {type(ex).__name__})"
+
     def step(ev=None):
         # the two launches duq4_linear_w4a4_from_fp16 makes, issued separately so that the GEMM
         # launch can be bracketed by its own events
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(codes), L.ptr(sa), None, None, None, st())
         if ev:
             ev[0].record()
+        if peer is not None:
+            peer.barrier()   # every rank has consumed the previous result
+            L.call("duq4_linear_w4a4_preunpacked", L.ptr(codes), L.ptr(qw), M, Ns, K, ctypes.byref(epi_f), None, None, st())
+            if ev:
+                ev[1].record()
+            peer.barrier()   # every rank's block has landed everywhere
+            return
         L.call("duq4_linear_w4a4_preunpacked", L.ptr(codes), L.ptr(qw), M, Ns, K, ctypes.byref(epi), L.ptr(out_shard), None, st())
         if ev:
             ev[1].record()
@@ -333,6 +352,13 @@ def run_ours(args):
 
     def step_e2e():
         x.copy_(x_host, non_blocking=True)
+        if peer is not None:
+            peer.barrier()
+            L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_f_e2e),
+                   None, L.ptr(ws), ws_bytes, st())
+            peer.barrier()
+            out_host.copy_(peer.buf, non_blocking=True)
+            return
         L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_e2e),
                L.ptr(out_shard), L.ptr(ws), ws_bytes, st())
         if world > 1:
@@ -387,7 +413,7 @@ def run_ours(args):
     line = {"metric": "w4a4_linear_tops_M4096", "value": round(tops, 2), "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4xint4->int32 (kind::i8 tensor cores), fp16 epilogue", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "parallelism": f"column-parallel N/{world} + all-gather" if world > 1 else "single GPU",
+            "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "parallelism": f"column-parallel N/{world}, gather={gather_mode}" if world > 1 else "single GPU",
                        "cache": "operands (weights 117 MB + activations 64 MB + output 235 MB) exceed the 126 MB L2; no flush",
                        "weights": "N(0,0.015) per-channel symmetric int4", "activations": "N(0,1), 1% channels x20, per-token symmetric int4"},
             "clocks": clocks,
@@ -419,6 +445,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize"],

@@ -37,6 +37,12 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
     p->bias = (const __half *)e->bias;
     p->ldo = e->ldo ? e->ldo : N;
     if (p->ldo < N) return DUQ4_ERR_SHAPE;
+    if (e->n_out_peers > DUQ4_MAX_OUT_PEERS) return DUQ4_ERR_SHAPE;
+    p->n_peers = e->n_out_peers;
+    for (uint32_t i = 0; i < e->n_out_peers; ++i) {
+        if (!e->out_peers[i]) return DUQ4_ERR_NULL;
+        p->peers[i] = (__half *)e->out_peers[i];
+    }
     if (e->mode == DUQ4_MODE_NONE) return DUQ4_OK;
     const bool asym = e->mode == DUQ4_MODE_ASYM || e->mode == DUQ4_MODE_ASYM_DUAL;
     const bool dual = e->mode == DUQ4_MODE_SYM_DUAL || e->mode == DUQ4_MODE_ASYM_DUAL;
@@ -50,7 +56,7 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
 static int linear_dispatch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                            const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
     if (!A || !W) return DUQ4_ERR_NULL;
-    if (p.mode != DUQ4_MODE_NONE && !out) return DUQ4_ERR_NULL;
+    if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
     if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0 || batch == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
@@ -141,7 +147,7 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
     if (!A_i8 || !W) return DUQ4_ERR_NULL;
-    if (p.mode != DUQ4_MODE_NONE && !out) return DUQ4_ERR_NULL;
+    if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
     if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
@@ -160,7 +166,7 @@ size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K) {
 int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
                                size_t workspace_bytes, void *stream) {
-    if (!x || !W || !out || !epi) return DUQ4_ERR_NULL;
+    if (!x || !W || !epi || (!out && !epi->n_out_peers)) return DUQ4_ERR_NULL;
     if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;

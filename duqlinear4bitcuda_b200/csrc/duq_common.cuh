@@ -49,7 +49,32 @@ struct EpiParams {
     uint32_t ldo;
     // batched launches: element strides between consecutive problems
     uint32_t row_vec_stride, col_vec_stride;
+    // Fused all-gather: when n_peers > 0 every output element is stored into each of these
+    // buffers (same layout and offsets in all of them; peer-mapped device pointers, this rank's
+    // own buffer included) instead of the single `out` pointer.
+    uint32_t n_peers;
+    __half *peers[DUQ4_MAX_OUT_PEERS];
 };
+
+// Output bases of a launch: the peer list if there is one, else the plain `out` pointer.
+struct OutBases {
+    __half *base[DUQ4_MAX_OUT_PEERS];
+    int n;
+};
+__device__ __forceinline__ OutBases out_bases(const EpiParams &p, __half *out) {
+    OutBases o;
+    if (p.n_peers) {
+        o.n = (int)p.n_peers;
+#pragma unroll
+        for (int i = 0; i < DUQ4_MAX_OUT_PEERS; ++i) o.base[i] = p.peers[i];
+    } else {
+        o.n = out ? 1 : 0;
+        o.base[0] = out;
+#pragma unroll
+        for (int i = 1; i < DUQ4_MAX_OUT_PEERS; ++i) o.base[i] = nullptr;
+    }
+    return o;
+}
 
 // Epilogue operands of problem `b` of a batched launch.
 __host__ __device__ inline EpiParams epi_for_batch(EpiParams p, uint32_t b) {

@@ -82,6 +82,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major, 128-byte-swizzled operand descriptor: rows of 128 bytes, 8-row groups 1024 bytes
@@ -322,51 +331,59 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
             }
             const bool has_bias = pb.bias != nullptr;
             const bool asym = mode == DUQ4_MODE_ASYM || mode == DUQ4_MODE_ASYM_DUAL;
-            __half *orow = a.out ? a.out + ((size_t)b * a.M + m) * pb.ldo + n0 : nullptr;
+            const size_t ooff = ((size_t)b * a.M + m) * pb.ldo + n0;
             int32_t *arow = a.acc_out ? a.acc_out + ((size_t)b * a.M + m) * a.N + n0 : nullptr;
-            const bool vec_ok = ((pb.ldo & 7u) == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0);
+            const OutBases ob = out_bases(pb, a.out);
+            uintptr_t obits = 0;
+#pragma unroll
+            for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
+                if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
+            const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
             const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                uint32_t v[32];
+            for (int ch = 0; ch < BN / 16; ++ch) {
+                uint32_t v[16];
                 __syncwarp();  // tcgen05.ld is warp-collective
-                tmem_ld32(taddr + ch * 32, v);
+                tmem_ld16(taddr + ch * 16, v);
                 tmem_ld_wait();
                 if (!row_ok) continue;
-                const uint32_t c0 = ch * 32;
+                const uint32_t c0 = ch * 16;
                 if (n0 + c0 >= a.N) continue;
-                const bool full = n0 + c0 + 32 <= a.N;
-                int acc[32];
+                const bool full = n0 + c0 + 16 <= a.N;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = ((int)v[j]) >> shift;
+                for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> shift);
                 if (arow) {
                     if (full && avec_ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<int4 *>(arow + c0 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<int4 *>(arow + c0 + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
                     } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c0 + j < a.N) arow[c0 + j] = acc[j];
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + c0 + j < a.N) arow[c0 + j] = (int)v[j];
                     }
                 }
                 if (mode != DUQ4_MODE_NONE) {
-                    __align__(16) __half o[32];
+                    __align__(16) __half o[16];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        __half e = __int2half_rn(acc[j]);
+                    for (int j = 0; j < 16; ++j) {
+                        __half e = __int2half_rn((int)v[j]);
                         __half ss = __hmul_rn(sr, cs[c0 + j]);
                         __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
                         if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
                         o[j] = val;
                     }
-                    if (full && vec_ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            *reinterpret_cast<uint4 *>(orow + c0 + j) = *reinterpret_cast<const uint4 *>(&o[j]);
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
+                    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
+                        if (pi >= ob.n) break;
+                        __half *orow = ob.base[pi] + ooff;
+                        if (full && vec_ok) {
+                            *reinterpret_cast<uint4 *>(orow + c0) = *reinterpret_cast<const uint4 *>(&o[0]);
+                            *reinterpret_cast<uint4 *>(orow + c0 + 8) = *reinterpret_cast<const uint4 *>(&o[8]);
+                        } else {
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
+                        }
                     }
                 }
             }

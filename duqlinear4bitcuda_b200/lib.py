@@ -27,6 +27,8 @@ class Epilogue(ctypes.Structure):
         ("zeros_col_2", ctypes.c_void_p),
         ("bias", ctypes.c_void_p),
         ("ldo", ctypes.c_uint32),
+        ("n_out_peers", ctypes.c_uint32),
+        ("out_peers", ctypes.c_void_p * 8),
     ]
 
 
@@ -107,7 +109,7 @@ def current_stream():
 
 
 def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
-                  zeros_col_2=None, bias=None, col_offset=0, ldo=0):
+                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None):
     e = Epilogue()
     e.mode = MODES[mode] if isinstance(mode, str) else int(mode)
     e.col_offset = col_offset
@@ -116,4 +118,10 @@ def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_
                  ("bias", bias)):
         setattr(e, k, None if v is None else v.data_ptr())
     e.ldo = ldo
+    if out_peers:   # raw device addresses (ints), this rank's own buffer included
+        if len(out_peers) > 8:
+            raise ValueError("at most 8 output peers")
+        e.n_out_peers = len(out_peers)
+        for i, a in enumerate(out_peers):
+            e.out_peers[i] = int(a)
     return e

@@ -68,7 +68,7 @@ class Linear4bitSQ(_PackedLinearBase):
             new.weight_scales.copy_(weight_scales.to(w.dtype))
             new.weight.copy_(qz.sym_weight_quant(w, weight_scales.cuda()))
             if module.bias is not None:
-                new.bias.copy_(module.bias)
+                new.bias.copy_(module.bias.detach())
         return new
 
 
@@ -103,7 +103,7 @@ class Linear4bitDUSQ(_PackedLinearBase):
                                (w[:, split:] / weight_scales_2.cuda()).round()], dim=-1)
             new.weight.copy_(qz.pack_i4(codes.to(torch.int8)).cpu())
             if module.bias is not None:
-                new.bias.copy_(module.bias)
+                new.bias.copy_(module.bias.detach())
         return new
 
 
@@ -135,7 +135,7 @@ class Linear4bitASQ(_PackedLinearBase):
         new.weight_scales.copy_(scale)
         new.weight_zeros.copy_(zeros)
         if module.bias is not None:
-            new.bias.copy_(module.bias)
+            new.bias.copy_(module.bias.detach())
         return new
 
 
@@ -175,7 +175,7 @@ class LinearQuant4bitDUASQ(_PackedLinearBase):
             getattr(new, f"weight_zeros_{idx}").copy_(zeros)
         new.weight.copy_(qz.pack_i4(torch.cat(halves, dim=-1).to(torch.int8), sym=False).cpu())
         if module.bias is not None:
-            new.bias.copy_(module.bias)
+            new.bias.copy_(module.bias.detach())
         return new
 
 
@@ -221,5 +221,5 @@ class LinearQuant8bitASQ(torch.nn.Module):
         new.weight_scales.copy_(scale.to(torch.float32))
         new.weight_zeros.copy_(zeros)
         if module.bias is not None:
-            new.bias.copy_(module.bias)
+            new.bias.copy_(module.bias.detach())
         return new

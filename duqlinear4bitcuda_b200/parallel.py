@@ -60,6 +60,29 @@ def gather_columns(local: torch.Tensor, n_out: int, group=None, out: torch.Tenso
     return full.contiguous()
 
 
+class PeerOutput:
+    """A [M, N] fp16 result buffer that exists on every rank and is mapped into every other
+    rank's address space (torch symmetric memory over NVLink). The GEMM epilogue of each rank
+    stores its column block straight into all of these buffers (`duq4_epilogue.out_peers`), so
+    the all-gather is fused into the kernel: no separate collective, no re-layout copy.
+    `barrier()` is a device-side barrier across the ranks on the current stream."""
+
+    def __init__(self, M, N, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.M, self.N = M, N
+        self.buf = symm.empty((M, N), dtype=torch.float16, device=device)
+        self.hdl = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        if len(self.ptrs) > 8:
+            raise ValueError("fused all-gather supports at most 8 ranks")
+
+    def column_ptrs(self, col_begin):
+        return [p + 2 * col_begin for p in self.ptrs]
+
+    def barrier(self):
+        self.hdl.barrier()
+
+
 class ColumnParallelLinear4bit(torch.nn.Module):
     """One W4A4 layer sharded over a process group. Holds this rank's weight rows and channel
     vectors; forward takes replicated fp16 activations [.., K] and returns the full fp16 [.., N]
@@ -69,11 +92,12 @@ class ColumnParallelLinear4bit(torch.nn.Module):
     Build it from full-size tensors with `from_full` (each rank keeps only its slice)."""
 
     def __init__(self, mode, n_out, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None,
-                 clip_ratio=1.0, group=None):
+                 clip_ratio=1.0, group=None, unsharded=False):
         super().__init__()
         self.mode, self.n_out, self.clip_ratio, self.group = mode, n_out, clip_ratio, group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        use_dist = dist.is_initialized() and not unsharded   # unsharded=True: the whole layer on this GPU
+        self.world = dist.get_world_size(group) if use_dist else 1
+        self.rank = dist.get_rank(group) if use_dist else 0
         self.col_begin, self.col_end = shard_bounds(n_out, self.world, self.rank)
         for name, t in (("weight", weight), ("scales_1", scales_1), ("zeros_1", zeros_1), ("scales_2", scales_2),
                         ("zeros_2", zeros_2), ("bias", bias)):
@@ -84,6 +108,7 @@ class ColumnParallelLinear4bit(torch.nn.Module):
             else:
                 setattr(self, name, None)
         self._ws = None
+        self._peer = None
 
     @classmethod
     def from_full(cls, mode, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None, clip_ratio=1.0,
@@ -94,8 +119,9 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         return cls(mode, weight.shape[0], cut(weight), cut(scales_1), cut(zeros_1), cut(scales_2), cut(zeros_2), cut(bias),
                    clip_ratio, group)
 
-    def local_forward(self, x2d: torch.Tensor):
-        """This rank's [M, n_local] block through the fused C-ABI entry point."""
+    def local_forward(self, x2d: torch.Tensor, peer: "PeerOutput" = None):
+        """This rank's [M, n_local] block through the fused C-ABI entry point. With `peer`, the
+        block is stored into every rank's [M, N] buffer instead of a local tensor."""
         from . import lib as L
         M, K = x2d.shape
         n_local = self.col_end - self.col_begin
@@ -103,16 +129,39 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         if self._ws is None or self._ws.numel() < need or self._ws.device != x2d.device:
             self._ws = torch.empty(need, dtype=torch.uint8, device=x2d.device)
         flat = lambda t: None if t is None else t.reshape(-1)
-        epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
-                              flat(self.zeros_2), self.bias, col_offset=self.col_begin)
-        out = torch.empty((M, n_local), dtype=torch.float16, device=x2d.device)
-        with torch.cuda.device(x2d.device):
-            L.call("duq4_linear_w4a4_from_fp16", L.ptr(x2d), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
-                   float(self.clip_ratio), ctypes.byref(epi), L.ptr(out), L.ptr(self._ws), self._ws.numel(), L.current_stream())
+        if peer is None:
+            out = torch.empty((M, n_local), dtype=torch.float16, device=x2d.device)
+            epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                                  flat(self.zeros_2), self.bias, col_offset=self.col_begin)
+        else:
+            out = None
+            epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                                  flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=self.n_out,
+                                  out_peers=peer.column_ptrs(self.col_begin))
+        if n_local:
+            with torch.cuda.device(x2d.device):
+                L.call("duq4_linear_w4a4_from_fp16", L.ptr(x2d), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
+                       float(self.clip_ratio), ctypes.byref(epi), L.ptr(out), L.ptr(self._ws), self._ws.numel(),
+                       L.current_stream())
         return out
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, gather: str = "nccl"):
+        """gather="nccl": compute the local block, then one NCCL all-gather (+ re-layout copy).
+        gather="fused": the kernel's epilogue writes the block into every rank's result buffer over
+        NVLink (peer stores); two device-side barriers bracket the launch (peers finished reading
+        the previous result / everybody finished writing this one). The returned tensor is a view
+        of that shared buffer: it is overwritten by the next fused forward of the same shape."""
         x2d = x.reshape(-1, x.shape[-1]).contiguous()
-        local = self.local_forward(x2d)
-        full = local if self.world == 1 else gather_columns(local, self.n_out, self.group)
+        if self.world == 1:
+            full = self.local_forward(x2d)
+        elif gather == "fused":
+            M = x2d.shape[0]
+            if self._peer is None or self._peer.M != M:
+                self._peer = PeerOutput(M, self.n_out, x2d.device, self.group)
+            self._peer.barrier()
+            self.local_forward(x2d, self._peer)
+            self._peer.barrier()
+            full = self._peer.buf
+        else:
+            full = gather_columns(self.local_forward(x2d), self.n_out, self.group)
         return full.view(*x.shape[:-1], self.n_out)

@@ -41,6 +41,10 @@ extern "C" {
 /* Column split of the dual-uniform schemes (ref: include/quant.h:5, QUANT_COL_K). */
 #define DUQ4_QUANT_COL_K 10
 
+#ifndef DUQ4_MAX_OUT_PEERS
+#define DUQ4_MAX_OUT_PEERS 8
+#endif
+
 /* Quantizer / dequantizer variants. */
 #define DUQ4_MODE_NONE 0       /* no dequant: int32 accumulators only */
 #define DUQ4_MODE_SYM 1        /* ref: sym_quant_host / sym_dequant_host */
@@ -186,6 +190,15 @@ typedef struct duq4_epilogue {
     const void *bias;        /* fp16 [N] or NULL; added last as a separate fp16 add
                                 (ref: qlinear4bit/nn/linear.py:53-54)                          */
     uint32_t ldo;            /* row stride of `out` in elements; 0 means N */
+    /* Fused all-gather for N-sharded layers (optional, no reference counterpart): with
+     * n_out_peers > 0 the kernel stores every output element into EACH of out_peers[0..n) at the
+     * offset it would use in `out` (which is then ignored and may be NULL). The pointers are
+     * device addresses valid on the launching GPU: its own buffer and peer-mapped buffers of the
+     * other ranks (CUDA IPC / VMM / torch symmetric memory), all [M, ldo] with identical layout;
+     * point each at this shard's first column. Plain st.global over NVLink; the caller
+     * synchronises the ranks before anyone reads the gathered result. */
+    uint32_t n_out_peers;
+    void *out_peers[8];
 } duq4_epilogue;
 
 /* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches

@@ -35,13 +35,17 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
                                                    zc2 if mode == "asym_dual" else None, bias)
         y = layer(x)
         torch.cuda.synchronize()
+        y_fused = layer(x, gather="fused").clone()   # epilogue peer stores instead of the collective
+        y_fused2 = layer(x, gather="fused").clone()  # reuse of the shared buffer
+        torch.cuda.synchronize()
         # the unsharded layer on this GPU alone
         single = ColumnParallelLinear4bit(mode, N, qw, sc1, zc1 if asym else None, sc2 if dual else None,
-                                          zc2 if mode == "asym_dual" else None, bias)
-        single.world, single.rank, single.col_begin, single.col_end = 1, 0, 0, N
+                                          zc2 if mode == "asym_dual" else None, bias, unsharded=True)
         y1 = single(x)
         torch.cuda.synchronize()
         ok = torch.equal(y.view(torch.int16), y1.view(torch.int16)) and tuple(y.shape) == (M, N)
+        ok = ok and torch.equal(y_fused.view(torch.int16), y1.view(torch.int16))
+        ok = ok and torch.equal(y_fused2.view(torch.int16), y1.view(torch.int16))
         open(os.path.join(tmp, f"r{rank}"), "w").write(str(int(ok)))
     finally:
         dist.destroy_process_group()

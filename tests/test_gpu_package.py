@@ -1,0 +1,167 @@
+"""The qlinear4bit-compatible Python package on a GPU: module forwards against the CPU oracle
+(bit-exact), buffer names of the reference's state_dict, the `qlinear4bit` import alias."""
+import numpy as np
+import pytest
+
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    import qlinear4bit.nn as qnn                      # the alias a user of the reference imports
+    import qlinear4bit.tools.tensor_utils as tu
+    from oracle import oracle as o
+    return torch, qnn, tu, o
+
+
+def _lin(torch, K, N, seed, bias=True, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    lin = torch.nn.Linear(K, N, bias=bias)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(N, K, generator=g) * std)
+        if bias:
+            lin.bias.copy_(torch.randn(N, generator=g))
+    return lin.half()
+
+
+def test_alias_and_state_dict_names(env):
+    torch, qnn, tu, o = env
+    import duqlinear4bitcuda_b200.nn as impl
+    assert qnn.Linear4bitSQ is impl.Linear4bitSQ
+    assert sorted(qnn.Linear4bitSQ(64, 8, bias=True).state_dict()) == ["bias", "weight", "weight_scales"]
+    assert sorted(qnn.Linear4bitDUSQ(64, 8).state_dict()) == ["weight", "weight_scales_1", "weight_scales_2"]
+    assert sorted(qnn.Linear4bitASQ(64, 8, bias=True).state_dict()) == ["bias", "weight", "weight_scales", "weight_zeros"]
+    assert sorted(qnn.LinearQuant4bitDUASQ(64, 8).state_dict()) == [
+        "weight", "weight_scales_1", "weight_scales_2", "weight_zeros_1", "weight_zeros_2"]
+    m = qnn.Linear4bitASQ(64, 8)
+    assert m.weight.dtype == torch.uint8 and tuple(m.weight.shape) == (8, 32) and m.weight_scales.dtype == torch.float16
+    assert tuple(m.weight_zeros.shape) == (8, 1)
+    assert tu.get_dual_quant_col() == 10
+
+
+@pytest.mark.parametrize("shape", [(3, 256), (2, 40, 256), (1, 300, 512)])
+def test_sym_quantizer_and_linear(env, shape):
+    torch, qnn, tu, o = env
+    K, N = shape[-1], 136
+    lin = _lin(torch, K, N, 1)
+    w = lin.weight.data
+    scales = (w.abs().amax(dim=1, keepdim=True).float() / 7).half()
+    mod = qnn.Linear4bitSQ.from_float(lin, weight_scales=scales).cuda()
+    quant = qnn.SymQuantizer(input_clip_ratio=0.9)
+    x = torch.from_numpy(U.acts(int(np.prod(shape[:-1])), K, 3)).view(*shape).cuda()
+    packed = quant(x)
+    y = mod(packed)
+    assert tuple(y.shape) == (*shape[:-1], N) and y.dtype == torch.float16
+    # oracle pipeline
+    x2 = x.view(-1, K).cpu().numpy()
+    s = o.sym_scales(x2, 0.9)
+    assert np.array_equal(packed.scales_x.reshape(-1).cpu().numpy().view(np.uint16), s.view(np.uint16))
+    assert packed.scales_x.shape == ((shape[0], 1) if len(shape) == 2 else (shape[0], 1, shape[1]))   # the reference's unsqueeze(1)
+    qa = packed.quantized_x.view(-1, K // 2).cpu().numpy()
+    qw = mod.weight.cpu().numpy()
+    _, want = o.linear_w4a4("sym", qa, qw, s, None, mod.weight_scales.cpu().numpy(), None, None, None,
+                            mod.bias.cpu().numpy())
+    assert U.f16_equal_nan(y.view(-1, N).cpu().numpy(), want)
+    # the reference's three-call sequence through the functional wrappers gives the same tensor
+    acc = tu.matmul(packed.quantized_x, mod.weight)
+    y3 = tu.sym_dequant(acc, packed.scales_x, mod.weight_scales) + mod.bias
+    assert torch.equal(y3.view(torch.int16), y.view(torch.int16))
+
+
+def test_asym_modules(env, golden):
+    torch, qnn, tu, o = env
+    lin = _lin(torch, 128, 24, 5)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(golden["asq_w"])); lin.bias.copy_(torch.from_numpy(golden["asq_b"]))
+    m = qnn.Linear4bitASQ.from_linear(lin, require_quantizer=True)
+    assert np.array_equal(m.weight.numpy(), golden["asq_weight"])                   # reference's own from_linear output
+    assert np.array_equal(m.weight_zeros.numpy().view(np.uint16), golden["asq_zeros"].view(np.uint16))
+    d = qnn.LinearQuant4bitDUASQ.from_linear(lin, require_quantizer=True)
+    assert np.array_equal(d.weight.numpy(), golden["duasq_weight"])
+    for k in ("weight_scales_1", "weight_zeros_1", "weight_scales_2", "weight_zeros_2"):
+        assert np.array_equal(getattr(d, k).numpy().view(np.uint16), golden["duasq_" + k].view(np.uint16))
+    x = torch.from_numpy(U.acts(37, 128, 7, mean=0.1)).cuda()
+    x2 = x.cpu().numpy()
+    s, z = o.asym_scales_zeros(x2); qa = o.asym_quant(x2, s, z)
+    for mod, mode in ((m.cuda(), "asym"), (d.cuda(), "asym_dual")):
+        y = mod(x)
+        sc1 = (mod.weight_scales if mode == "asym" else mod.weight_scales_1).cpu().numpy()
+        zc1 = (mod.weight_zeros if mode == "asym" else mod.weight_zeros_1).cpu().numpy()
+        sc2 = None if mode == "asym" else mod.weight_scales_2.cpu().numpy()
+        zc2 = None if mode == "asym" else mod.weight_zeros_2.cpu().numpy()
+        _, want = o.linear_w4a4(mode, qa, mod.weight.cpu().numpy(), s, z, sc1, zc1, sc2, zc2, mod.bias.cpu().numpy())
+        got = y.cpu().numpy()
+        bad = [r for r in range(37) if not U.f16_equal_nan(got[r], want[r])]
+        assert len(bad) <= 1, bad   # a token may differ where the GPU divide sits on a rounding boundary
+
+
+def test_dual_sym_module(env):
+    torch, qnn, tu, o = env
+    K, N = 192, 72
+    lin = _lin(torch, K, N, 9, bias=False)
+    w = lin.weight.data
+    s1 = (w[:, :10].abs().amax(dim=1, keepdim=True).float() / 7).half()
+    s2 = (w[:, 10:].abs().amax(dim=1, keepdim=True).float() / 7).half()
+    mod = qnn.Linear4bitDUSQ.from_float(lin, s1, s2).cuda()
+    x = torch.from_numpy(U.acts(20, K, 2)).cuda()
+    packed = qnn.SymQuantizer()(x)
+    y = mod(packed)
+    qa = packed.quantized_x.cpu().numpy(); sa = packed.scales_x.reshape(-1).cpu().numpy()
+    _, want = o.linear_w4a4("sym_dual", qa, mod.weight.cpu().numpy(), sa, None, s1.numpy(), None, s2.numpy(), None)
+    assert U.f16_equal_nan(y.cpu().numpy(), want)
+
+
+def test_quant_matmul_modules(env):
+    torch, qnn, tu, o = env
+    A = torch.from_numpy(U.acts(2 * 3 * 20, 128, 1, mean=0.1)).view(2, 3, 20, 128).cuda()
+    B = torch.from_numpy(U.acts(2 * 3 * 24, 128, 2, mean=-0.1)).view(2, 3, 24, 128).cuda()
+    C = qnn.AsymQuantMatMul()(A, B)
+    assert tuple(C.shape) == (2, 3, 20, 24)
+    a2 = A.view(6, 20, 128).cpu().numpy(); b2 = B.view(6, 24, 128).cpu().numpy()
+    bad = 0
+    for i in range(6):
+        sa, za = o.asym_scales_zeros(a2[i]); sb, zb = o.asym_scales_zeros(b2[i])
+        acc = o.matmul_4bit(o.asym_quant(a2[i], sa, za), o.asym_quant(b2[i], sb, zb))
+        want = o.asym_dequant(acc, sa, za, sb, zb)
+        bad += int(not U.f16_equal_nan(C.view(6, 20, 24)[i].cpu().numpy(), want))
+    assert bad <= 1
+    S = qnn.SymQuantMatMul()(A[0, 0], B[0, 0])
+    sa = o.sym_scales(a2[0]); sb = o.sym_scales(b2[0])
+    want = o.sym_dequant(o.matmul_4bit(o.sym_quant(a2[0], sa), o.sym_quant(b2[0], sb)), sa, sb)
+    got = S.cpu().numpy()
+    assert sum(not U.f16_equal_nan(got[r], want[r]) for r in range(20)) <= 1
+
+
+def test_8bit_side_path(env):
+    torch, qnn, tu, o = env
+    lin = _lin(torch, 128, 40, 11).float()
+    mod = qnn.LinearQuant8bitASQ.from_linear(lin).cuda()
+    x = (torch.randn(33, 128, generator=torch.Generator().manual_seed(3)) * 2).cuda()
+    y = mod(x)
+    assert y.dtype == torch.float32 and tuple(y.shape) == (33, 40)
+    q = mod.quantizer(x)
+    acc = o.matmul_8bit(q.quantized_x.cpu().numpy(), mod.weight.cpu().numpy())
+    want = o.asym_dequant_hprec(acc, q.scales_x.cpu().numpy(), q.zeros_x.cpu().numpy(), mod.weight_scales.cpu().numpy(),
+                                mod.weight_zeros.cpu().numpy()) + mod.bias.cpu().numpy()
+    assert np.array_equal(y.cpu().numpy(), want.astype(np.float32))
+
+
+def test_operator_argument_checks(env):
+    torch, qnn, tu, o = env
+    import qlinear4bit._CUDA as ops
+    x = torch.zeros((4, 64), dtype=torch.float16, device="cuda"); s = torch.ones(4, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.sym_quant(x.cpu(), s)                    # not a CUDA tensor
+    with pytest.raises(RuntimeError):
+        ops.sym_quant(x.t(), s)                      # not contiguous
+    with pytest.raises(RuntimeError):
+        ops.sym_quant(x, s[:3])                      # scale.size(0) != rows
+    with pytest.raises(RuntimeError, match="Unsupported data type"):
+        ops.sym_dequant(torch.zeros((4, 4), dtype=torch.int32, device="cuda"), s, s, 16)
+    with pytest.raises(AssertionError):
+        tu.matmul(torch.zeros((4, 24), dtype=torch.uint8, device="cuda"), torch.zeros((4, 24), dtype=torch.uint8, device="cuda"))
+    q = ops.asym_dual_quant(x, s, s, s, s)           # returns its tensor (the reference's binding does not)
+    assert q.dtype == torch.uint8 and tuple(q.shape) == (4, 32)
