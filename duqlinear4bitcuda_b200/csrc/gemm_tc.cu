@@ -121,7 +121,14 @@ struct Cfg {
     static constexpr int NUP = NUP_;                          // swizzled int8 ring (-> MMA)
     static_assert(NPK <= 4 && NUP <= 6, "barrier map holds 4 packed and 6 unpacked stages");
     static constexpr int kColTerms = kEpiWarps * 3 * BN * 2;  // per epilogue warp: (scale, zero, bias) x BN halves
-    static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + 256 /*barriers*/;
+    // Output staging (per epilogue warp 32 rows x 64 fp16, rows padded to 144 bytes): lets the
+    // epilogue turn its one-row-per-lane registers into 128-byte row segments before they go to
+    // global or peer memory. Only where the rings leave room (not in MODE_I4).
+    static constexpr bool kStaged = MODE != MODE_I4;
+    static constexpr int kStageOutWarp = 32 * 144;
+    static constexpr int kStageOut = kStaged ? kEpiWarps * kStageOutWarp : 0;
+    static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kStageOut + 256 /*barriers*/;
+    static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
     static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
 };
 
@@ -151,7 +158,8 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
     const uint32_t pk0 = up0 + C::NUP * C::kUnpackedStage;       // packed stages
     const uint32_t ct_off = C::NUP * C::kUnpackedStage + C::NPK * C::kPackedStage;
     __half *colterms = reinterpret_cast<__half *>(gbase + ct_off);
-    const uint32_t bar0 = base + ct_off + C::kColTerms;
+    uint8_t *stage_out = gbase + ct_off + C::kColTerms;
+    const uint32_t bar0 = base + ct_off + C::kColTerms + C::kStageOut;
     // barrier map (8 bytes each)
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
     auto pk_empty = [&](int s) { return bar0 + 8u * (4 + s); };
@@ -341,19 +349,19 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
             const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
             const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+            uint8_t *stg = stage_out + (warp - 2) * C::kStageOutWarp;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 16; ++ch) {
                 uint32_t v[16];
                 __syncwarp();  // tcgen05.ld is warp-collective
                 tmem_ld16(taddr + ch * 16, v);
                 tmem_ld_wait();
-                if (!row_ok) continue;
                 const uint32_t c0 = ch * 16;
-                if (n0 + c0 >= a.N) continue;
+                const bool col_any = n0 + c0 < a.N;
                 const bool full = n0 + c0 + 16 <= a.N;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> shift);
-                if (arow) {
+                if (arow && row_ok && col_any) {
                     if (full && avec_ok) {
 #pragma unroll
                         for (int j = 0; j < 16; j += 4)
@@ -363,16 +371,18 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
                             if (n0 + c0 + j < a.N) arow[c0 + j] = (int)v[j];
                     }
                 }
-                if (mode != DUQ4_MODE_NONE) {
-                    __align__(16) __half o[16];
+                if (mode == DUQ4_MODE_NONE) continue;
+                __align__(16) __half o[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        __half e = __int2half_rn((int)v[j]);
-                        __half ss = __hmul_rn(sr, cs[c0 + j]);
-                        __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
-                        if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
-                        o[j] = val;
-                    }
+                for (int j = 0; j < 16; ++j) {
+                    __half e = __int2half_rn((int)v[j]);
+                    __half ss = __hmul_rn(sr, cs[c0 + j]);
+                    __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
+                    if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
+                    o[j] = val;
+                }
+                if (!C::kStaged) {
+                    if (!row_ok || !col_any) continue;
 #pragma unroll
                     for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
                         if (pi >= ob.n) break;
@@ -385,7 +395,36 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
                                 if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
                         }
                     }
+                    continue;
                 }
+                // staged: lane = row writes its 32 bytes; after four chunks (64 columns) the warp
+                // reads the block back as 128-byte row segments, four rows per store instruction
+                *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
+                *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
+                if ((ch & 3) != 3) continue;
+                __syncwarp();
+                const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first column of this lane's 8 (tile-relative)
+                const bool seg_full = n0 + g0 + 8 <= a.N;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const uint32_t r = it * 4 + (lane >> 3);
+                    const uint32_t mr = tm * BM + quad * 32 + r;
+                    if (mr >= a.M || n0 + g0 >= a.N) continue;
+                    const uint4 seg = *reinterpret_cast<const uint4 *>(stg + r * 144 + (lane & 7) * 16);
+                    const size_t off = ((size_t)b * a.M + mr) * pb.ldo + n0 + g0;
+#pragma unroll
+                    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
+                        if (pi >= ob.n) break;
+                        if (seg_full && vec_ok) {
+                            *reinterpret_cast<uint4 *>(ob.base[pi] + off) = seg;
+                        } else {
+                            const __half *hs = reinterpret_cast<const __half *>(&seg);
+                            for (int j = 0; j < 8; ++j)
+                                if (n0 + g0 + j < a.N) ob.base[pi][off + j] = hs[j];
+                        }
+                    }
+                }
+                __syncwarp();   // the block is free for the next 64 columns
             }
             tc_fence_before();
             __syncwarp();
@@ -591,9 +630,9 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     }
     if (mode == MODE_A8B4) {
         if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
-        if (v == 0) return launch<MODE_A8B4, 256, 4, 4, 3>(A, B, a, st, cache_maps);
-        if (v == 2) return launch<MODE_A8B4, 256, 8, 4, 3>(A, B, a, st, cache_maps);
-        return launch<MODE_A8B4, 256, 12, 4, 3>(A, B, a, st, cache_maps);
+        if (v == 0) return launch<MODE_A8B4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
+        if (v == 2) return launch<MODE_A8B4, 256, 10, 3, 3>(A, B, a, st, cache_maps);
+        return launch<MODE_A8B4, 256, 12, 3, 3>(A, B, a, st, cache_maps);
     }
     return DUQ4_ERR_MODE;
 }
