@@ -93,6 +93,93 @@ __global__ void quant_given_scalar_kernel(const __half *__restrict__ x, const __
     }
 }
 
+// ---- fast coding path of the fused kernels -------------------------------------------------
+// Same codes as code8<MODE>, far fewer instructions (the fused kernel is otherwise issue-bound,
+// not HBM-bound). Valid for a row whose scales are finite and non-zero, whose zero-points are
+// finite (|rint(z)| <= 400 for the single-scale asymmetric scheme) and which contains no
+// inf/NaN -- everything else takes code8<MODE>.
+//   * __hdiv(x, s) is half(rcp.approx.ftz(float(s)) * float(x)) plus a refinement that only
+//     fires for quotients below 8.6e-6, which round to the same code either way; the reciprocal
+//     is taken once per row with the same instruction.
+//   * rounding to integer and clamping happen in fp16x2: adding 1024 + offset to a value already
+//     clamped to a 16-wide integer window rounds it to nearest-even exactly like
+//     __half2int_rn, and leaves the code in the low four bits of each half.
+__device__ __forceinline__ float rcp_approx_ftz(float b) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+    return r;
+}
+struct FastQ {
+    float r1, r2;          // reciprocals of scale set 1 / 2
+    __half2 z1, z2;        // zero-point terms, duplicated in both halves (rint(z) for QASYM)
+    bool ok;
+};
+__device__ __forceinline__ bool finite_nonzero(__half h) {
+    const unsigned short b = __half_as_ushort(h) & 0x7FFFu;
+    return b != 0 && b < 0x7C00u;
+}
+__device__ __forceinline__ bool finite_h(__half h) { return (__half_as_ushort(h) & 0x7FFFu) < 0x7C00u; }
+
+template <int MODE>
+__device__ __forceinline__ FastQ make_fastq(const RowQ &r, bool row_special) {
+    FastQ f;
+    f.ok = !row_special && finite_nonzero(r.s1);
+    f.r1 = rcp_approx_ftz(__half2float(r.s1));
+    f.r2 = f.r1;
+    f.z1 = f.z2 = __float2half2_rn(0.f);
+    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) {
+        f.ok = f.ok && finite_nonzero(r.s2);
+        f.r2 = rcp_approx_ftz(__half2float(r.s2));
+    }
+    if (MODE == QASYM) {
+        f.ok = f.ok && finite_h(r.z1) && fabsf(__half2float(r.z1)) <= 400.f;
+        f.z1 = __float2half2_rn(rintf(__half2float(r.z1)));
+    }
+    if (MODE == QASYM_DUAL) {
+        f.ok = f.ok && finite_h(r.z1) && finite_h(r.z2);
+        f.z1 = __half2half2(r.z1);
+        f.z2 = __half2half2(r.z2);
+    }
+    return f;
+}
+
+// One 32-bit word (two halves) -> two codes in bits [0,4) and [16,20).
+template <int MODE>
+__device__ __forceinline__ uint32_t code2_fast(uint32_t w, float rcp, __half2 z) {
+    const __half2 h = *reinterpret_cast<const __half2 *>(&w);
+    const float2 f = __half22float2(h);
+    const __half2 q = __floats2half2_rn(__fmul_rn(rcp, f.x), __fmul_rn(rcp, f.y));
+    __half2 t;
+    if (MODE == QSYM || MODE == QSYM_DUAL) {
+        const __half2 c = __hmin2(__hmax2(q, __float2half2_rn(-8.f)), __float2half2_rn(6.f));
+        t = __hadd2(c, __float2half2_rn(1032.f));            // 0x6400 + (code + 8)
+    } else if (MODE == QASYM) {
+        const __half2 c = __hmin2(__hmax2(q, __float2half2_rn(-500.f)), __float2half2_rn(500.f));
+        const __half2 s = __hadd2(__hadd2(c, __float2half2_rn(1536.f)), z);   // rint(x/s) + rint(z) + 1536
+        t = __hmin2(__hmax2(s, __float2half2_rn(1536.f)), __float2half2_rn(1551.f));   // 0x6600 + code
+    } else {
+        const __half2 c = __hmin2(__hmax2(__hadd2(q, z), __float2half2_rn(0.f)), __float2half2_rn(15.f));
+        t = __hadd2(c, __float2half2_rn(1024.f));            // 0x6400 + code
+    }
+    return *reinterpret_cast<const uint32_t *>(&t) & 0x000F000Fu;
+}
+
+// 8 halves -> 8 nibbles, low nibble first. col0 >= 16 for the dual schemes (set 2 only).
+template <int MODE>
+__device__ __forceinline__ uint32_t code8_fast(const uint4 &v, const FastQ &f) {
+    const bool dual = MODE == QSYM_DUAL || MODE == QASYM_DUAL;
+    const float rcp = dual ? f.r2 : f.r1;
+    const __half2 z = dual ? f.z2 : f.z1;
+    const uint32_t a = code2_fast<MODE>(v.x, rcp, z), b = code2_fast<MODE>(v.y, rcp, z);
+    const uint32_t c = code2_fast<MODE>(v.z, rcp, z), d = code2_fast<MODE>(v.w, rcp, z);
+    // word -> byte: element 0 in bits 0..3, element 1 (bits 16..19) moved to bits 4..7
+    const uint32_t b0 = (a | (a >> 12)) & 0xFFu, b1 = (b | (b >> 12)) & 0xFFu;
+    const uint32_t b2 = (c | (c >> 12)) & 0xFFu, b3 = (d | (d >> 12)) & 0xFFu;
+    uint32_t out = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    if (MODE == QSYM || MODE == QSYM_DUAL) out ^= 0x88888888u;   // (code + 8) -> two's complement nibble
+    return out;
+}
+
 // ---- fused ---------------------------------------------------------------------------
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -218,25 +305,72 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
             uint32_t v = threadIdx.x + i * 256;
             if (v < nvec) d[i] = __ldg(xr + v);
         }
+        // Row statistics on the raw bit patterns: for symmetric schemes the integer maximum of
+        // (bits & 0x7FFF) IS max|x|; asymmetric ones use fp16x2 min/max. The same integer maximum
+        // tells whether the row holds an inf or NaN (>= 0x7C00), which sends it to the slow path.
+        constexpr bool kDual = MODE == QSYM_DUAL || MODE == QASYM_DUAL;
+        constexpr bool kAsym = MODE == QASYM || MODE == QASYM_DUAL;
+        uint32_t am = 0, am_head = 0;
+        __half2 hmx = __float2half2_rn(-INFINITY), hmn = __float2half2_rn(INFINITY);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             uint32_t v = threadIdx.x + i * 256;
             if (v < nvec) {
-                const __half *h = reinterpret_cast<const __half *>(&d[i]);
+                const uint32_t w[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
+                if (kDual && v < 2) {   // columns 0..15 straddle the split at column 10: per element
+                    const __half *h = reinterpret_cast<const __half *>(&d[i]);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) stats_add<MODE>(st, __half2float(h[k]), v * 8 + k);
+                    for (int k = 0; k < 8; ++k) stats_add<MODE>(st, __half2float(h[k]), v * 8 + k);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) am_head = __vmaxu2(am_head, w[k] & 0x7FFF7FFFu);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        am = __vmaxu2(am, w[k] & 0x7FFF7FFFu);
+                        if (kAsym) {
+                            const __half2 hv = *reinterpret_cast<const __half2 *>(&w[k]);
+                            hmx = __hmax2(hmx, hv);
+                            hmn = __hmin2(hmn, hv);
+                        }
+                    }
+                }
             }
         }
-        __syncthreads();  // protects sm[] against the previous row's readers
+        const uint32_t am16 = max(am & 0xFFFFu, am >> 16), amh16 = max(am_head & 0xFFFFu, am_head >> 16);
+        if (kAsym) {
+            st.b_hi = fmaxf(st.b_hi, fmaxf(__low2float(hmx), __high2float(hmx)));
+            st.b_lo = fminf(st.b_lo, fminf(__low2float(hmn), __high2float(hmn)));
+        } else if (am16 < 0x7C00u) {
+            st.b_hi = fmaxf(st.b_hi, __half2float(__ushort_as_half((unsigned short)am16)));
+        }
+        // (also the barrier that protects sm[] against the previous row's readers)
+        const bool row_special = __syncthreads_or((am16 >= 0x7C00u) || (amh16 >= 0x7C00u));
+        if (row_special) {   // rare: redo the statistics element by element, as the slow path defines them
+            stats_init<MODE>(st);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                uint32_t v = threadIdx.x + i * 256;
+                if (v < nvec) {
+                    const __half *h = reinterpret_cast<const __half *>(&d[i]);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) stats_add<MODE>(st, __half2float(h[k]), v * 8 + k);
+                }
+            }
+        }
         stats_reduce<MODE>(st, sm);
         RowQ r = rowq_from_stats<MODE>(st, clip);
         if (threadIdx.x == 0) store_rowq<MODE>(r, row, s1o, z1o, s2o, z2o);
+        const FastQ fq = make_fastq<MODE>(r, row_special);
+        auto code = [&](const uint4 &dv, uint32_t v) -> uint32_t {
+            if (fq.ok && !(kDual && v < 2)) return code8_fast<MODE>(dv, fq);
+            return code8<MODE>(dv, v * 8, r);
+        };
         if (!out8) {
             uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 uint32_t v = threadIdx.x + i * 256;
-                if (v < nvec) qr[v] = code8<MODE>(d[i], v * 8, r);
+                if (v < nvec) qr[v] = code(d[i], v);
             }
         } else {
             // Tensor-core-ready activations: one int8 (= 16 * code) per element, stored in the K
@@ -249,7 +383,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
             for (int i = 0; i < VPT; ++i) {
                 uint32_t v = threadIdx.x + i * 256;
                 if (v < nvec) {
-                    uint32_t w = code8<MODE>(d[i], v * 8, r);
+                    uint32_t w = code(d[i], v);
                     uint32_t off = (v >> 4) * 128 + ((v & 15) >> 2) * 32 + (v & 3) * 4;
                     *reinterpret_cast<uint32_t *>(qr + off) = (w << 4) & 0xF0F0F0F0u;
                     *reinterpret_cast<uint32_t *>(qr + off + 16) = w & 0xF0F0F0F0u;
