@@ -255,13 +255,15 @@ def run_profile_case(args):
     st = L.current_stream
     if args.profile_case == "gemm":
         M, N, K = 2048, 8192, 8192
-        qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev)
+        x = torch.randn((M, K), device=dev).half()
         qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev)
-        sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
+        a8 = torch.empty((M, K), dtype=torch.int8, device=dev)
+        sa = torch.empty(M, dtype=torch.float16, device=dev); sw = torch.rand(N, device=dev).half()
         y = torch.empty((M, N), dtype=torch.float16, device=dev)
         epi = L.make_epilogue("sym", sa, None, sw)
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         for _ in range(4):
-            L.call("duq4_linear_w4a4", L.ptr(qa), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
+            L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
     elif args.profile_case == "decode":
         M, N, K = 1, 22016, 4096
         W = torch.randint(0, 256, (8, N, K // 2), dtype=torch.uint8, device=dev)  # 8 x 45 MB: cold in L2

@@ -61,7 +61,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         if (acc_out) acc_out += (size_t)b * M * N;
         p = epi_for_batch(p, b);
     }
-    const OutBases ob = out_bases(p, out);
     __shared__ int red[kGemvWarps][16][16 * R + 1];  // [warp][token][row]; +1 pads the row stride
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -169,9 +168,14 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
             ColTerms ct = load_col_terms(p, n);
             __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
             const __half v = dequant_one(p.mode, s, p.s_row[m], zr, ct);
+            const size_t off = (size_t)m * p.ldo + n;
+            if (p.n_peers == 0) {
+                out[off] = v;
+            } else {   // fused all-gather: the same element into every rank's buffer
 #pragma unroll
-            for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                if (pi < ob.n) ob.base[pi][(size_t)m * p.ldo + n] = v;
+                for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
+                    if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+            }
         }
     }
 }
@@ -339,10 +343,14 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
                     ColTerms ct = load_col_terms(p, n);
                     __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
                     const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, ct);
-                    const OutBases ob = out_bases(p, out0);
+                    const size_t off = ((size_t)b * M + m) * p.ldo + n;
+                    if (p.n_peers == 0) {
+                        out0[off] = v;
+                    } else {
 #pragma unroll
-                    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                        if (pi < ob.n) ob.base[pi][((size_t)b * M + m) * p.ldo + n] = v;
+                        for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
+                            if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+                    }
                 }
             }
         }
