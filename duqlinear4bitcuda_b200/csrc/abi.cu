@@ -12,6 +12,7 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
+int tc2_status_read(int32_t *out);
 extern int g_static_weights;
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
                             void *z1, void *s2, void *z2, cudaStream_t st, bool out8);
@@ -263,7 +264,11 @@ int duq4_last_device_status(void *stream, int32_t *status_out) {
     if (rc) return rc;
     rc = gemv_status_read(&b);
     if (rc) return rc;
-    *status_out = a ? a : (b ? 100 + b : 0);   // 1..9: tensor-core GEMM wait, 101..: small-M kernel wait
+    int32_t c = 0;
+    rc = tc2_status_read(&c);
+    if (rc) return rc;
+    // 1..9: tensor-core GEMM wait, 101..: small-M kernel wait, 201..: CTA-pair GEMM wait
+    *status_out = a ? a : (b ? 100 + b : (c ? 200 + c : 0));
     return DUQ4_OK;
 }
 

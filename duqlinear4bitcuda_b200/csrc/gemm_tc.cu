@@ -28,6 +28,7 @@
 
 #include "duq_common.cuh"
 #include "duq_ptx.cuh"
+#include "gemm_tc_shared.cuh"
 
 namespace duq4 {
 
@@ -39,7 +40,6 @@ using namespace ptx;
 
 constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // K elements per pipeline stage (= one 128-byte swizzle row of int8)
-constexpr int kEpiWarps = 4;
 // Operand formats of one launch.
 constexpr int MODE_I8 = 0;     // A and B int8: TMA writes the swizzled tiles, no unpack
 constexpr int MODE_I4 = 1;     // A and B packed int4: both unpacked in shared memory
@@ -48,69 +48,6 @@ constexpr int MODE_A8B4 = 2;   // A already unpacked in HBM (int8 = 16*s4, K per
 // warps: 0 TMA producer, 1 MMA issuer, 2..5 epilogue, 6..6+UW-1 unpack, last: second TMA producer (A of MODE_A8B4)
 __host__ __device__ constexpr int threads_for(int uw) { return 32 * (2 + kEpiWarps + uw + 1); }
 constexpr uint64_t kWaitLimitNs = kPtxWaitLimitNs;
-
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128-byte-swizzled operand descriptor: rows of 128 bytes, 8-row groups 1024 bytes
-// apart (stride byte offset), version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;               // leading byte offset (unused for swizzled K-major): 1
-    d |= (uint64_t)(1024u >> 4) << 32;    // stride byte offset
-    d |= (uint64_t)1 << 46;               // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;               // SWIZZLE_128B
-    return d;
-}
-// kind::i8 instruction descriptor: D = s32, A = B = signed int8, both K-major, no saturation.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
-__device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return w & 0xF0F0F0F0u; }
 
 template <int MODE, int BN, int UW_, int NPK_, int NUP_>
 struct Cfg {
@@ -130,14 +67,6 @@ struct Cfg {
     static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kStageOut + 256 /*barriers*/;
     static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
     static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
-};
-
-struct Args {
-    uint32_t M, N, K, batch;  // K in elements
-    uint32_t tiles_m, tiles_n;
-    EpiParams epi;
-    __half *out;
-    int32_t *acc_out;
 };
 
 template <int MODE, int BN, int UW, int NPK_, int NUP_>
@@ -292,8 +221,6 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
     } else if (warp < 2 + kEpiWarps) {
         // ---------------- epilogue ----------------
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-        const uint32_t row_in_tile = quad * 32 + lane;
-        const int mode = a.epi.mode;
         const uint32_t shift = INT4 ? 8 : 0;
         uint32_t lt = 0;
         bool ok = true;
@@ -304,128 +231,13 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
             uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
             const uint32_t n0 = tn * BN;
             EpiParams pb = a.epi;
-            // Each epilogue warp keeps its own copy of the tile's column terms, so the four
-            // warps never have to meet at a barrier (a barrier a warp could miss when the CTA
-            // is leaving early).
             __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
-            __syncwarp();  // previous tile's readers are done
-            if (mode != DUQ4_MODE_NONE) {
-                size_t co = (size_t)b * pb.col_vec_stride;
-                if (pb.s_col1) pb.s_col1 += co;
-                if (pb.z_col1) pb.z_col1 += co;
-                if (pb.s_col2) pb.s_col2 += co;
-                if (pb.z_col2) pb.z_col2 += co;
-                if (pb.bias) pb.bias += co;
-                for (int c = lane; c < BN; c += 32) {
-                    uint32_t n = n0 + c;
-                    ColTerms t;
-                    t.s = t.z = t.b = __ushort_as_half(0);
-                    if (n < a.N) t = load_col_terms(pb, n);
-                    cs[c] = t.s;
-                    cz[c] = t.z;
-                    cb[c] = t.b;
-                }
-            }
-            __syncwarp();
+            epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
             if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc_status, 4))) break;
             tc_fence_after();
 
-            const uint32_t m = tm * BM + row_in_tile;
-            const bool row_ok = m < a.M;
-            __half sr = __ushort_as_half(0), zr = __ushort_as_half(0);
-            if (row_ok && mode != DUQ4_MODE_NONE) {
-                sr = pb.s_row[(size_t)b * pb.row_vec_stride + m];
-                if (pb.z_row) zr = pb.z_row[(size_t)b * pb.row_vec_stride + m];
-            }
-            const bool has_bias = pb.bias != nullptr;
-            const bool asym = mode == DUQ4_MODE_ASYM || mode == DUQ4_MODE_ASYM_DUAL;
-            const size_t ooff = ((size_t)b * a.M + m) * pb.ldo + n0;
-            int32_t *arow = a.acc_out ? a.acc_out + ((size_t)b * a.M + m) * a.N + n0 : nullptr;
-            const OutBases ob = out_bases(pb, a.out);
-            uintptr_t obits = 0;
-#pragma unroll
-            for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
-            const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
-            const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
-            uint8_t *stg = stage_out + (warp - 2) * C::kStageOutWarp;
-#pragma unroll 1
-            for (int ch = 0; ch < BN / 16; ++ch) {
-                uint32_t v[16];
-                __syncwarp();  // tcgen05.ld is warp-collective
-                tmem_ld16(taddr + ch * 16, v);
-                tmem_ld_wait();
-                const uint32_t c0 = ch * 16;
-                const bool col_any = n0 + c0 < a.N;
-                const bool full = n0 + c0 + 16 <= a.N;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> shift);
-                if (arow && row_ok && col_any) {
-                    if (full && avec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 16; j += 4)
-                            *reinterpret_cast<int4 *>(arow + c0 + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 16; ++j)
-                            if (n0 + c0 + j < a.N) arow[c0 + j] = (int)v[j];
-                    }
-                }
-                if (mode == DUQ4_MODE_NONE) continue;
-                __align__(16) __half o[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    __half e = __int2half_rn((int)v[j]);
-                    __half ss = __hmul_rn(sr, cs[c0 + j]);
-                    __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
-                    if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
-                    o[j] = val;
-                }
-                if (!C::kStaged) {
-                    if (!row_ok || !col_any) continue;
-#pragma unroll
-                    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
-                        if (pi >= ob.n) break;
-                        __half *orow = ob.base[pi] + ooff;
-                        if (full && vec_ok) {
-                            *reinterpret_cast<uint4 *>(orow + c0) = *reinterpret_cast<const uint4 *>(&o[0]);
-                            *reinterpret_cast<uint4 *>(orow + c0 + 8) = *reinterpret_cast<const uint4 *>(&o[8]);
-                        } else {
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
-                        }
-                    }
-                    continue;
-                }
-                // staged: lane = row writes its 32 bytes; after four chunks (64 columns) the warp
-                // reads the block back as 128-byte row segments, four rows per store instruction
-                *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
-                *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
-                if ((ch & 3) != 3) continue;
-                __syncwarp();
-                const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first column of this lane's 8 (tile-relative)
-                const bool seg_full = n0 + g0 + 8 <= a.N;
-#pragma unroll
-                for (int it = 0; it < 8; ++it) {
-                    const uint32_t r = it * 4 + (lane >> 3);
-                    const uint32_t mr = tm * BM + quad * 32 + r;
-                    if (mr >= a.M || n0 + g0 >= a.N) continue;
-                    const uint4 seg = *reinterpret_cast<const uint4 *>(stg + r * 144 + (lane & 7) * 16);
-                    const size_t off = ((size_t)b * a.M + mr) * pb.ldo + n0 + g0;
-#pragma unroll
-                    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
-                        if (pi >= ob.n) break;
-                        if (seg_full && vec_ok) {
-                            *reinterpret_cast<uint4 *>(ob.base[pi] + off) = seg;
-                        } else {
-                            const __half *hs = reinterpret_cast<const __half *>(&seg);
-                            for (int j = 0; j < 8; ++j)
-                                if (n0 + g0 + j < a.N) ob.base[pi][off + j] = hs[j];
-                        }
-                    }
-                }
-                __syncwarp();   // the block is free for the next 64 columns
-            }
+            epi_store_tile<BN, C::kStaged>(a, pb, b, tm * BM, n0, tmem_base + buf * BN, quad, lane, shift, cs, cz, cb,
+                                           stage_out + (warp - 2) * C::kStageOutWarp);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
@@ -604,6 +416,19 @@ static int variant() {
 
 }  // namespace tc
 
+int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
+                    void *out, int32_t *acc_out, cudaStream_t st);
+
+// CTA-pair tiles for the pre-unpacked-activation path: DUQ4_TC_PAIR=0/1 overrides the default.
+static bool pair_tiles() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("DUQ4_TC_PAIR");
+        v = e ? (atoi(e) != 0) : 1;
+    }
+    return v != 0;
+}
+
 // A [batch,M,K] x B [batch,N,K]^T. mode: tc::MODE_I8 / MODE_I4 / MODE_A8B4 (see above).
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
@@ -629,6 +454,10 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
         return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
     }
     if (mode == MODE_A8B4) {
+        if (pair_tiles() && (uint64_t)cdiv(M, 256) * cdiv(N, 256) * batch >= 60) {
+            int rc = gemm_tc2_launch(A, B, M, N, K, batch, p, out, acc_out, st);
+            if (rc != DUQ4_ERR_DEVICE) return rc;   // no CTA pairs on this device: single-CTA tiles below
+        }
         if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
         if (v == 0) return launch<MODE_A8B4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
         if (v == 2) return launch<MODE_A8B4, 256, 10, 3, 3>(A, B, a, st, cache_maps);

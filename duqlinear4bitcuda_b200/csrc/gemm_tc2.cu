@@ -1,0 +1,416 @@
+// CTA-pair (cta_group::2) variant of the tensor-core W4A4 GEMM, for pre-unpacked activations
+// (A int8 [M,K] as written by the fused quantizer, W packed int4 [N,K/2]).
+//
+// Two CTAs on neighbouring SMs (a cluster of 2, no multicast loads) compute one 256 x 256 tile:
+// CTA r of the pair holds rows [128r, 128r+128) of A and rows [128r, 128r+128) of the tile's W
+// block. One thread of the even ("leader") CTA issues tcgen05.mma.cta_group::2 with M = 256,
+// N = 256: each SM multiplies its own 128 A rows with the whole W block, half of which it reads
+// from its partner's shared memory. Compared with the single-CTA 128 x 256 tile every CTA
+// unpacks, stores and serves only HALF of the W block per unit of MMA work, which is what the
+// single-CTA kernel is limited by (shared-memory bandwidth shared between the unpack and the
+// MMA operand reads).
+//
+// Synchronisation (all waits bounded, see duq_ptx.cuh):
+//   pk_full/pk_empty[s]  local : TMA of the packed W half  <->  unpack warps
+//   up_full[u]   LEADER's only : 1 arrival + 32 KiB of TMA bytes (both CTAs' A tiles, their copies
+//                                 carry .cta_group::2 and signal the leader's barrier) and one
+//                                 arrival per unpack warp of BOTH CTAs  ->  MMA issuer
+//   up_empty[u]  local, both   : tcgen05.commit by the leader into each CTA's barrier
+//   acc_full[b]  local, both   : tcgen05.commit after a tile's last MMA
+//   acc_empty[b] LEADER's only : one arrival per epilogue warp of BOTH CTAs
+#include <cuda.h>
+
+#include "duq_common.cuh"
+#include "duq_ptx.cuh"
+#include "gemm_tc_shared.cuh"
+
+namespace duq4 {
+
+__device__ int g_tc2_status = 0;
+
+int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
+                     bool swizzle128, CUtensorMap *out);
+
+namespace tc2 {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int BMH = 128;   // A rows per CTA (half of the pair's 256)
+constexpr int BNH = 128;   // W rows per CTA (half of the pair's 256)
+constexpr int BN = 256;    // accumulator columns
+constexpr int BKE = 128;   // K elements per stage
+constexpr int UW = 8;      // unpack warps
+constexpr int NPK = 3, NUP = 5;
+constexpr int kThreads2 = 32 * (2 + kEpiWarps + UW + 1);
+constexpr int kUnpackedStage = (BMH + BNH) * BKE;   // 32 KiB: A tile then W half, both 128B-swizzled int8
+constexpr int kPackedStage = BNH * (BKE / 2);       // 8 KiB
+constexpr int kColTerms = kEpiWarps * 3 * BN * 2;
+constexpr int kStageOutWarp = 32 * 144;
+constexpr int kSmem2 = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_addr`'s counterpart in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait on a barrier that receives arrivals from the partner CTA (cluster-scope acquire).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_cluster(bar, parity)) return true;
+        if ((it & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            uint64_t now = globaltimer();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kPtxWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc2_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on ONE barrier (shared::cluster address, either CTA of the pair) once every MMA issued
+// so far by this thread has completed in both CTAs.
+__device__ __forceinline__ void umma2_commit(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+// A-tile copy of either CTA: data lands in the issuing CTA's shared memory, the byte count is
+// credited to the LEADER's barrier.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads2, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gbase = smem_raw + (base - raw);
+    const uint32_t up0 = base;
+    const uint32_t pk0 = up0 + NUP * kUnpackedStage;
+    const uint32_t ct_off = NUP * kUnpackedStage + NPK * kPackedStage;
+    __half *colterms = reinterpret_cast<__half *>(gbase + ct_off);
+    uint8_t *stage_out = gbase + ct_off + kColTerms;
+    const uint32_t bar0 = base + ct_off + kColTerms + kEpiWarps * kStageOutWarp;
+    auto pk_full = [&](int s) { return bar0 + 8u * s; };
+    auto pk_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+    auto up_full = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto up_empty = [&](int s) { return bar0 + 8u * (14 + s); };
+    auto acc_full = [&](int s) { return bar0 + 8u * (20 + s); };
+    auto acc_empty = [&](int s) { return bar0 + 8u * (22 + s); };
+    const uint32_t drain_bar = bar0 + 8u * 24;
+    static_assert(NPK <= 4 && NUP <= 6, "barrier map");
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const uint32_t num_tiles = a.tiles_m * a.tiles_n * a.batch;   // tiles of 256 x 256
+    const uint32_t ksteps = (a.K + BKE - 1) / BKE;
+    constexpr int kLastWarp = 2 + kEpiWarps + UW;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(pk_full(s), 1);
+            mbar_init(pk_empty(s), UW);
+        }
+        for (int s = 0; s < 6; ++s) {
+            mbar_init(up_full(s), 1 + 2 * UW);
+            mbar_init(up_empty(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(acc_full(s), 1);
+            mbar_init(acc_empty(s), 2 * kEpiWarps);
+        }
+        mbar_init(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs performs the paired allocation
+        tmem_alloc2(smem_u32(&tmem_base_slot), 512);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers are initialised before anyone arrives remotely
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    auto tile_coords = [&](uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
+        const uint32_t per_b = a.tiles_m * a.tiles_n;
+        b = tile / per_b;
+        const uint32_t r = tile % per_b;
+        tn = r / a.tiles_m;
+        tm = r % a.tiles_m;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: this CTA's half of the packed W block ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
+                uint32_t b, tm, tn;
+                tile_coords(tile, b, tm, tn);
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    const uint32_t s = it % NPK, ph = (it / NPK) & 1;
+                    if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc2_status, 1))) break;
+                    mbar_expect_tx(pk_full(s), kPackedStage);
+                    tma_load_3d(pk0 + s * kPackedStage, &tmB, pk_full(s), ks * (BKE / 2), tn * BN + rank * BNH, b);
+                }
+            }
+            if (!ok) {
+                uint64_t t0 = globaltimer();
+                while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+            }
+        }
+    } else if (warp == kLastWarp) {
+        // ---------------- TMA producer: this CTA's 128 rows of A, credited to the leader ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
+                uint32_t b, tm, tn;
+                tile_coords(tile, b, tm, tn);
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    const uint32_t u = it % NUP, uph = (it / NUP) & 1;
+                    if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 7))) break;
+                    if (rank == 0) mbar_expect_tx(up_full(u), 2 * BMH * BKE);   // both CTAs' A tiles
+                    tma_load_3d_pair(up0 + u * kUnpackedStage, &tmA, mapa(up_full(u), 0), ks * BKE, tm * 256 + rank * BMH, b);
+                }
+            }
+            if (!ok) {
+                uint64_t t0 = globaltimer();
+                while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(256, BN);
+            uint32_t it = 0, lt = 0;
+            bool ok = true, issued = false;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs, ++lt) {
+                const uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
+                if (!(ok = mbar_wait_cluster(acc_empty(buf), aph ^ 1, abortp, 2))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    const uint32_t u = it % NUP, ph = (it / NUP) & 1;
+                    if (!(ok = mbar_wait_cluster(up_full(u), ph, abortp, 3))) break;
+                    tc_fence_after();
+                    const uint32_t sa = up0 + u * kUnpackedStage, sb = sa + BMH * BKE;
+                    const uint64_t da = make_desc(sa), db = make_desc(sb);
+#pragma unroll
+                    for (int kk = 0; kk < BKE / 32; ++kk)
+                        umma2_i8(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (ks | kk) != 0);
+                    issued = true;
+                    umma2_commit(up_empty(u));            // this CTA's stage ...
+                    umma2_commit(mapa(up_empty(u), 1));   // ... and the partner's
+                }
+                if (ok) {
+                    umma2_commit(acc_full(buf));
+                    umma2_commit(mapa(acc_full(buf), 1));
+                }
+            }
+            if (!ok && issued) {
+                umma2_commit(drain_bar);
+                uint64_t t0 = globaltimer();
+                while (!mbar_try(drain_bar, 0) && globaltimer() - t0 < kPtxWaitLimitNs) __nanosleep(1000);
+            }
+        }
+    } else if (warp < 2 + kEpiWarps) {
+        // ---------------- epilogue: this CTA's 128 rows of the tile ----------------
+        const int quad = warp & 3;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs, ++lt) {
+            uint32_t b, tm, tn;
+            tile_coords(tile, b, tm, tn);
+            const uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
+            const uint32_t n0 = tn * BN;
+            EpiParams pb = a.epi;
+            __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
+            epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
+            if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc2_status, 4))) break;
+            tc_fence_after();
+            epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                                     stage_out + (warp - 2) * kStageOutWarp);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
+        }
+    } else {
+        // ---------------- unpack warps: this CTA's packed W half -> swizzled int8 ----------------
+        const int ut = (warp - 2 - kEpiWarps) * 32 + lane;
+        constexpr int kChunks = BNH * 4;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t s = it % NPK, ph = (it / NPK) & 1;
+                const uint32_t u = it % NUP, uph = (it / NUP) & 1;
+                if (!(ok = mbar_wait(pk_full(s), ph, abortp, &g_tc2_status, 5))) break;
+                if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 6))) break;
+                const uint32_t src = pk0 + s * kPackedStage, dst = up0 + u * kUnpackedStage + BMH * BKE;
+#pragma unroll
+                for (int idx = ut; idx < kChunks; idx += UW * 32) {
+                    uint32_t w0, w1, w2, w3;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                                 : "r"(src + idx * 16));
+                    const uint32_t row = idx >> 2, c = idx & 3, sw = row & 7;
+                    const uint32_t rowaddr = dst + row * 128;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowaddr + (((2 * c) ^ sw) << 4)),
+                                 "r"(nib_lo(w0)), "r"(nib_lo(w1)), "r"(nib_lo(w2)), "r"(nib_lo(w3))
+                                 : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowaddr + (((2 * c + 1) ^ sw) << 4)),
+                                 "r"(nib_hi(w0)), "r"(nib_hi(w1)), "r"(nib_hi(w2)), "r"(nib_hi(w3))
+                                 : "memory");
+                }
+                fence_proxy_async();   // generic-proxy writes -> the pair's MMA (async proxy); the cluster-scope release of the arrive below publishes them to the partner
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(pk_empty(s));
+                    mbar_arrive_cluster(mapa(up_full(u), 0));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the partner has finished with this CTA's shared memory and its own TMEM
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, 512);
+    }
+}
+
+}  // namespace tc2
+
+// A int8 pre-unpacked [batch, M, K], W packed [batch, N, K/2]. Returns DUQ4_ERR_DEVICE when the
+// device cannot co-schedule CTA pairs (the caller then uses the single-CTA kernel).
+int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
+                    void *out, int32_t *acc_out, cudaStream_t st) {
+    using namespace tc2;
+    if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    if (K >= 131072u) return DUQ4_ERR_SHAPE;
+    static int max_pairs = -1;
+    if (max_pairs < 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+        if (e != cudaSuccess) return (int)e;
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(2 * 148);
+        q.blockDim = dim3(kThreads2);
+        q.dynamicSmemBytes = kSmem2;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        q.attrs = at;
+        q.numAttrs = 1;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel, &q);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        max_pairs = n;
+    }
+    if (max_pairs < 1) return DUQ4_ERR_DEVICE;
+    tc::Args a{};
+    a.M = M; a.N = N; a.K = K; a.batch = batch;
+    a.epi = p;
+    a.out = (__half *)out;
+    a.acc_out = acc_out;
+    a.tiles_m = cdiv(M, 256);
+    a.tiles_n = cdiv(N, 256);
+    CUtensorMap ma, mb;
+    int rc = tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
+    if (rc) return rc;
+    rc = tma_map_bytes_3d(B, K / 2, N, batch, BKE / 2, BNH, false, &mb);
+    if (rc) return rc;
+    const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
+    const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kThreads2);
+    cfg.dynamicSmemBytes = kSmem2;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mb, a);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)e;
+    }
+    return launch_status();
+}
+
+int tc2_status_read(int32_t *out) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc2_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    *out = v;
+    if (v != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc2_status, &zero, sizeof(int));
+    }
+    return DUQ4_OK;
+}
+
+}  // namespace duq4

@@ -457,9 +457,8 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
     // busy when N is small.
     const bool r2 = (uint64_t)(N / 32) * batch >= 2 * 148;
     const uint32_t rows_per_cta = r2 ? 32 : 16;
-    dim3 grid(cdiv(N, rows_per_cta), batch), block(kGemvWarps * 32);
+    dim3 grid(cdiv(N, rows_per_cta), batch);
     __half *o = (__half *)out;
-    (void)block;
     if (M <= 8) return r2 ? launch_reg<2, 1>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 1>(grid, A, W, M, N, K, p, o, acc_out, st);
     return r2 ? launch_reg<2, 2>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 2>(grid, A, W, M, N, K, p, o, acc_out, st);
 }
