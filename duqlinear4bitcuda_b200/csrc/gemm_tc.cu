@@ -416,10 +416,10 @@ static int variant() {
 
 }  // namespace tc
 
-int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
-                    void *out, int32_t *acc_out, cudaStream_t st);
+int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
 
-// CTA-pair tiles for the pre-unpacked-activation path: DUQ4_TC_PAIR=0/1 overrides the default.
+// CTA-pair tiles for large int4 problems: DUQ4_TC_PAIR=0/1 overrides the default (on).
 static bool pair_tiles() {
     static int v = -1;
     if (v < 0) {
@@ -447,15 +447,20 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     a.tiles_n = cdiv(N, wide ? 256 : 128);
     const int v = variant();
     if (mode == MODE_I8) return wide ? launch<MODE_I8, 256, 4, 1, 4>(A, B, a, st, cache_maps) : launch<MODE_I8, 128, 4, 1, 6>(A, B, a, st, cache_maps);
+    const bool pair_ok = pair_tiles() && (uint64_t)cdiv(M, 256) * cdiv(N, 256) * batch >= 60;
     if (mode == MODE_I4) {
+        if (pair_ok) {
+            int rc = gemm_tc2_launch(true, A, B, M, N, K, batch, p, out, acc_out, st);
+            if (rc != DUQ4_ERR_DEVICE) return rc;   // no CTA pairs on this device: single-CTA tiles below
+        }
         if (!wide) return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
         if (v == 0) return launch<MODE_I4, 256, 4, 4, 2>(A, B, a, st, cache_maps);
         if (v == 2) return launch<MODE_I4, 256, 8, 4, 2>(A, B, a, st, cache_maps);
         return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
     }
     if (mode == MODE_A8B4) {
-        if (pair_tiles() && (uint64_t)cdiv(M, 256) * cdiv(N, 256) * batch >= 60) {
-            int rc = gemm_tc2_launch(A, B, M, N, K, batch, p, out, acc_out, st);
+        if (pair_ok) {
+            int rc = gemm_tc2_launch(false, A, B, M, N, K, batch, p, out, acc_out, st);
             if (rc != DUQ4_ERR_DEVICE) return rc;   // no CTA pairs on this device: single-CTA tiles below
         }
         if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st, cache_maps);

@@ -41,13 +41,20 @@ constexpr int BNH = 128;   // W rows per CTA (half of the pair's 256)
 constexpr int BN = 256;    // accumulator columns
 constexpr int BKE = 128;   // K elements per stage
 constexpr int UW = 8;      // unpack warps
-constexpr int NPK = 3, NUP = 5;
 constexpr int kThreads2 = 32 * (2 + kEpiWarps + UW + 1);
 constexpr int kUnpackedStage = (BMH + BNH) * BKE;   // 32 KiB: A tile then W half, both 128B-swizzled int8
-constexpr int kPackedStage = BNH * (BKE / 2);       // 8 KiB
 constexpr int kColTerms = kEpiWarps * 3 * BN * 2;
 constexpr int kStageOutWarp = 32 * 144;
-constexpr int kSmem2 = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 256;
+// APK = activations arrive packed (int4, the reference's format) and are unpacked here too;
+// otherwise they arrive as the quantizer's tensor-core-ready int8 and go straight into the MMA ring.
+template <bool APK>
+struct Cfg2 {
+    static constexpr int NPK = 3;
+    static constexpr int NUP = APK ? 4 : 5;
+    static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
+    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 256;
+    static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -123,8 +130,11 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+template <bool APK>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
+    using C2 = Cfg2<APK>;
+    constexpr int NPK = C2::NPK, NUP = C2::NUP, kPackedStage = C2::kPackedStage;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -161,7 +171,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(pk_empty(s), UW);
         }
         for (int s = 0; s < 6; ++s) {
-            mbar_init(up_full(s), 1 + 2 * UW);
+            mbar_init(up_full(s), (APK ? 0 : 1) + 2 * UW);
             mbar_init(up_empty(s), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -202,7 +212,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint32_t s = it % NPK, ph = (it / NPK) & 1;
                     if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc2_status, 1))) break;
                     mbar_expect_tx(pk_full(s), kPackedStage);
-                    tma_load_3d(pk0 + s * kPackedStage, &tmB, pk_full(s), ks * (BKE / 2), tn * BN + rank * BNH, b);
+                    uint32_t dst = pk0 + s * kPackedStage;
+                    if (APK) {
+                        tma_load_3d(dst, &tmA, pk_full(s), ks * (BKE / 2), tm * 256 + rank * BMH, b);
+                        dst += BMH * (BKE / 2);
+                    }
+                    tma_load_3d(dst, &tmB, pk_full(s), ks * (BKE / 2), tn * BN + rank * BNH, b);
                 }
             }
             if (!ok) {
@@ -210,7 +225,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
             }
         }
-    } else if (warp == kLastWarp) {
+    } else if (!APK && warp == kLastWarp) {
         // ---------------- TMA producer: this CTA's 128 rows of A, credited to the leader ----------------
         if (lane == 0) {
             uint32_t it = 0;
@@ -286,10 +301,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
         }
-    } else {
-        // ---------------- unpack warps: this CTA's packed W half -> swizzled int8 ----------------
+    } else if (warp < kLastWarp) {
+        // ---------------- unpack warps: this CTA's packed W half (and packed A rows) -> swizzled int8 ----------------
         const int ut = (warp - 2 - kEpiWarps) * 32 + lane;
-        constexpr int kChunks = BNH * 4;
+        constexpr int kChunks = (APK ? BMH + BNH : BNH) * 4;
+        constexpr uint32_t kDstOff = APK ? 0 : BMH * BKE;
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
@@ -298,7 +314,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                 if (!(ok = mbar_wait(pk_full(s), ph, abortp, &g_tc2_status, 5))) break;
                 if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 6))) break;
-                const uint32_t src = pk0 + s * kPackedStage, dst = up0 + u * kUnpackedStage + BMH * BKE;
+                const uint32_t src = pk0 + s * kPackedStage, dst = up0 + u * kUnpackedStage + kDstOff;
 #pragma unroll
                 for (int idx = ut; idx < kChunks; idx += UW * 32) {
                     uint32_t w0, w1, w2, w3;
@@ -336,16 +352,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
 }  // namespace tc2
 
-// A int8 pre-unpacked [batch, M, K], W packed [batch, N, K/2]. Returns DUQ4_ERR_DEVICE when the
-// device cannot co-schedule CTA pairs (the caller then uses the single-CTA kernel).
-int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
-                    void *out, int32_t *acc_out, cudaStream_t st) {
+template <bool APK>
+static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
+                   void *out, int32_t *acc_out, cudaStream_t st) {
     using namespace tc2;
+    constexpr int kSmem2 = Cfg2<APK>::kSmem;
+    auto *kernel = gemm_tc2_kernel<APK>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
     static int max_pairs = -1;
     if (max_pairs < 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
         if (e != cudaSuccess) return (int)e;
         cudaLaunchConfig_t q = {};
         q.gridDim = dim3(2 * 148);
@@ -359,7 +376,7 @@ int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32
         q.attrs = at;
         q.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel, &q);
+        e = cudaOccupancyMaxActiveClusters(&n, kernel, &q);
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
             n = 0;
@@ -375,7 +392,7 @@ int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32
     a.tiles_m = cdiv(M, 256);
     a.tiles_n = cdiv(N, 256);
     CUtensorMap ma, mb;
-    int rc = tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
+    int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma) : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
     if (rc) return rc;
     rc = tma_map_bytes_3d(B, K / 2, N, batch, BKE / 2, BNH, false, &mb);
     if (rc) return rc;
@@ -393,12 +410,21 @@ int gemm_tc2_launch(const void *A, const void *B, uint32_t M, uint32_t N, uint32
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mb, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, a);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)e;
     }
     return launch_status();
+}
+
+// A: int8 pre-unpacked [batch, M, K] (a_packed = false) or packed int4 [batch, M, K/2]; W packed
+// [batch, N, K/2]. Returns DUQ4_ERR_DEVICE when the device cannot co-schedule CTA pairs (the
+// caller then uses the single-CTA kernel).
+int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+    return a_packed ? launch2<true>(A, B, M, N, K, batch, p, out, acc_out, st)
+                    : launch2<false>(A, B, M, N, K, batch, p, out, acc_out, st);
 }
 
 int tc2_status_read(int32_t *out) {

@@ -356,3 +356,23 @@ def test_decode_static_weights_overlap_keeps_stream_order(env, K):
     for i in range(6):
         _, want = o.linear_w4a4("sym", srcs[i].cpu().numpy(), qw, sa.cpu().numpy(), None, sw, None, None, None)
         assert U.f16_equal_nan(outs[i].cpu().numpy(), want), i
+
+
+@pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
+def test_pair_kernel_shapes(env, mode):
+    """Problems with at least 60 tiles of 256x256 run on CTA pairs (cta_group::2): ragged M and N,
+    K with a partial last stage, every epilogue mode, int32 accumulators, packed activations."""
+    torch, L, o = env
+    run_linear(torch, L, o, mode, 2000, 2100, 448, seed=71, col0=5)
+
+
+def test_pair_kernel_batched(env):
+    torch, L, o = env
+    B, M, N, K = 8, 512, 1024, 256   # 8 x 2 x 4 = 64 pair tiles
+    qa = U.rand_codes(B * M, K, 9).reshape(B, M, K // 2); qw = U.rand_codes(B * N, K, 10).reshape(B, N, K // 2)
+    da, dw = dev(torch, qa), dev(torch, qw)
+    C = torch.zeros((B, M, N), dtype=torch.int32, device="cuda")
+    L.call("duq4_batch_matmul_4bit", L.ptr(da), L.ptr(dw), M, N, K, L.ptr(C), B, L.current_stream())
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert np.array_equal(C.cpu().numpy(), o.batch_matmul_4bit(qa, qw))
