@@ -229,6 +229,70 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
     return out
 
 
+def time_mlp_block(torch, L, device):
+    """Quantized SiLU-gated MLP block of a random-init Llama-2-7B layer (hidden 4096, intermediate
+    11008) on 32 x 512 = 16384 tokens: quantize -> fused gate/up GEMM (N = 22016) -> fused
+    SiLU*mul + requantize -> down GEMM. Four launches; the fp16 gate/up tensor is the only
+    intermediate that goes through HBM at full width."""
+    T, H, I = 32 * 512, 4096, 11008
+    st = L.current_stream
+    x = synth_activations(torch, T, H, seed=3, pinned=False).to(device)
+    w_gu, s_gu = synth_weights(torch, 2 * I, H, seed=11, device=device)
+    w_dn, s_dn = synth_weights(torch, H, I, seed=12, device=device)
+    a8 = torch.empty((T, H), dtype=torch.int8, device=device); sa = torch.empty(T, dtype=torch.float16, device=device)
+    gu = torch.empty((T, 2 * I), dtype=torch.float16, device=device)
+    h8 = torch.empty((T, I), dtype=torch.int8, device=device); sh = torch.empty(T, dtype=torch.float16, device=device)
+    y = torch.empty((T, H), dtype=torch.float16, device=device)
+    e1 = L.make_epilogue("sym", sa, None, s_gu)
+    e2 = L.make_epilogue("sym", sh, None, s_dn)
+
+    def block():
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), T, H, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
+        L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(w_gu), T, 2 * I, H, ctypes.byref(e1), L.ptr(gu), None, st())
+        L.call("duq4_silu_mul_quantize_fused", L.MODE_SYM, L.ptr(gu), T, I, 2 * I, I, 1.0, L.ptr(h8), 1, L.ptr(sh), None, st())
+        L.call("duq4_linear_w4a4_preunpacked", L.ptr(h8), L.ptr(w_dn), T, H, I, ctypes.byref(e2), L.ptr(y), None, st())
+
+    for _ in range(3):
+        block()
+    torch.cuda.synchronize()
+    e0, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        block()
+    e1_.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1_) / reps
+    ops = 2.0 * T * H * 2 * I + 2.0 * T * I * H
+    return {"tokens": T, "hidden": H, "intermediate": I, "ms_per_block": round(ms, 4), "tops": round(ops / (ms * 1e-3) / 1e12, 1),
+            "launches_per_block": 4}
+
+
+def time_batched(torch, L, device):
+    """B = 8 independent 4096 x 4096 weight sets over M = 256 tokens each, one batched launch with
+    the asymmetric dequant in the epilogue."""
+    B, M, N, K = 8, 256, 4096, 4096
+    qa = torch.randint(0, 256, (B, M, K // 2), dtype=torch.uint8, device=device)
+    qw = torch.randint(0, 256, (B, N, K // 2), dtype=torch.uint8, device=device)
+    sr = torch.rand((B, M), device=device).half(); zr = torch.randint(0, 16, (B, M), device=device).half()
+    sc = torch.rand((B, N), device=device).half(); zc = torch.randint(0, 16, (B, N), device=device).half()
+    out = torch.empty((B, M, N), dtype=torch.float16, device=device)
+    epi = L.make_epilogue("asym", sr, zr, sc, zc)
+    fn = lambda: L.call("duq4_linear_w4a4_batched", L.ptr(qa), L.ptr(qw), M, N, K, B, ctypes.byref(epi), L.ptr(out), None,
+                        L.current_stream())
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    return {"batch": B, "M": M, "N": N, "K": K, "us": round(ms * 1e3, 2), "tops": round(2.0 * B * M * N * K / (ms * 1e-3) / 1e12, 1)}
+
+
 def int8_cublas_tops(torch, device):
     """cuBLASLt int8 GEMM (torch._int_mm) at 8192^3, best of 5: context for the tensor-pipe peak."""
     try:
@@ -441,6 +505,8 @@ def run_ours(args):
         line["roofline"]["cublaslt_int8_8192cubed_tops"] = int8_cublas_tops(torch, device)
         if not args.no_decode:
             line["decode"] = time_decode(torch, L, device, peaks)
+            line["mlp_block"] = time_mlp_block(torch, L, device)
+            line["batched"] = time_batched(torch, L, device)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()[0]
     if world > 1:

@@ -17,7 +17,7 @@ __all__ = [
     "matmul", "matmul_8bit", "batched_matmul", "sym_quant", "sym_dual_quant", "sym_dequant", "sym_dual_dequant",
     "asym_quant", "asym_quant_8bit", "asym_batch_dequant", "asym_dequant", "asym_dequant_hprec", "asym_dual_quant",
     "asym_dual_dequant", "get_dual_quant_col_k", "quantize_sym_fused", "quantize_asym_fused",
-    "quantize_sym_dual_fused", "quantize_asym_dual_fused", "linear_w4a4", "linear_w4a4_batched",
+    "quantize_sym_dual_fused", "quantize_asym_dual_fused", "silu_mul_quantize_fused", "linear_w4a4", "linear_w4a4_batched",
 ]
 
 
@@ -182,6 +182,26 @@ def quantize_asym_dual_fused(x):
     z1, s2, z2 = torch.empty_like(s1), torch.empty_like(s1), torch.empty_like(s1)
     _run("duq4_quantize_asym_dual_fused", x, _p(x), rows, cols, _p(q), _p(s1), _p(z1), _p(s2), _p(z2))
     return q, s1, z1, s2, z2
+
+
+def silu_mul_quantize_fused(gate_up, mode="sym", clip_ratio=1.0, tensor_core_ready=False):
+    """(new) SiLU-gated MLP glue in one kernel: gate_up fp16 [rows, 2*I] holds the gate projection in
+    columns [0, I) and the up projection in [I, 2I); returns the per-token quantization of
+    h = F.silu(gate) * up (the fp16 tensor those torch ops would produce) without storing h:
+    (codes, scales) for mode "sym", (codes, scales, zeros) for "asym". Codes are packed uint8
+    [rows, I/2], or int8 [rows, I] in the GEMM's tensor-core-ready layout when requested."""
+    _check("silu_mul_quantize_fused", gate_up=gate_up)
+    rows, ld = gate_up.size(0), gate_up.size(1)
+    inter = ld // 2
+    if ld % 2 or gate_up.dtype != torch.float16:
+        raise RuntimeError("silu_mul_quantize_fused: expected fp16 [rows, 2*I]")
+    q = torch.empty((rows, inter) if tensor_core_ready else (rows, inter // 2),
+                    dtype=torch.int8 if tensor_core_ready else torch.uint8, device=gate_up.device)
+    s = torch.empty((rows,), dtype=torch.float16, device=gate_up.device)
+    z = torch.empty_like(s) if mode == "asym" else None
+    _run("duq4_silu_mul_quantize_fused", gate_up, _L.MODES[mode], _p(gate_up), rows, inter, ld, inter, float(clip_ratio), _p(q),
+         1 if tensor_core_ready else 0, _p(s), _p(z))
+    return (q, s) if z is None else (q, s, z)
 
 
 # ---- dequantize ---------------------------------------------------------------------------

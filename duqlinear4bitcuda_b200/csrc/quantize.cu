@@ -289,21 +289,43 @@ __device__ __forceinline__ void store_rowq(const RowQ &r, uint32_t row, __half *
 
 // One CTA (256 threads) per token; the token lives in VPT uint4 registers per thread.
 // Requires cols % 8 == 0, cols <= 256*8*VPT, x 16-byte aligned.
-template <int MODE, int VPT>
+// SiLU-gated MLP glue: h = half(half(silu(g)) * u), each step rounded to fp16 the way the torch
+// composition `F.silu(gate) * up` rounds it (silu(x) = x / (1 + exp(-x)) evaluated in fp32).
+__device__ __forceinline__ uint4 silu_mul8(const uint4 &g, const uint4 &u) {
+    uint4 r;
+    const __half *hg = reinterpret_cast<const __half *>(&g), *hu = reinterpret_cast<const __half *>(&u);
+    __half *hr = reinterpret_cast<__half *>(&r);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float x = __half2float(hg[k]);
+        const __half s = __float2half_rn(__fdiv_rn(x, 1.0f + expf(-x)));
+        hr[k] = __hmul_rn(s, hu[k]);
+    }
+    return r;
+}
+
+// SILU = false: the token is x[row, 0:cols] (in_stride = cols). SILU = true: the token is
+// silu(x[row, 0:cols]) * x[row, up_off : up_off+cols] of a [rows, in_stride] gate/up tensor, i.e. the
+// activation of a SiLU-gated MLP is formed, measured and quantized without ever being stored in fp16.
+template <int MODE, int VPT, bool SILU = false>
 __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__restrict__ x, uint32_t rows, uint32_t cols,
                                                               float clip, uint8_t *__restrict__ q, __half *s1o,
-                                                              __half *z1o, __half *s2o, __half *z2o, bool out8) {
+                                                              __half *z1o, __half *s2o, __half *z2o, bool out8,
+                                                              uint32_t in_stride = 0, uint32_t up_off = 0) {
     __shared__ float sm[8][4];
     const uint32_t nvec = cols >> 3;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
+        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * (SILU ? in_stride : cols));
         uint4 d[VPT];
         Stats st;
         stats_init<MODE>(st);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             uint32_t v = threadIdx.x + i * 256;
-            if (v < nvec) d[i] = __ldg(xr + v);
+            if (v < nvec) {
+                d[i] = __ldg(xr + v);
+                if (SILU) d[i] = silu_mul8(d[i], __ldg(xr + (up_off >> 3) + v));
+            }
         }
         // Row statistics on the raw bit patterns: for symmetric schemes the integer maximum of
         // (bits & 0x7FFF) IS max|x|; asymmetric ones use fp16x2 min/max. The same integer maximum
@@ -493,6 +515,30 @@ static int launch_fused(const void *x, uint32_t rows, uint32_t cols, float clip,
     return launch_status();
 }
 
+// SiLU-gated variant (symmetric / asymmetric single-scale activations).
+template <int MODE>
+static int launch_silu(const void *gate_up, uint32_t rows, uint32_t inter, uint32_t ld, uint32_t up_off, float clip,
+                       uint8_t *q, void *s1, void *z1, cudaStream_t st, bool out8) {
+    if (!gate_up || !q || !s1 || (MODE == QASYM && !z1)) return DUQ4_ERR_NULL;
+    if (rows == 0) return DUQ4_OK;
+    if (inter == 0 || inter % 8 != 0 || ld % 8 != 0 || up_off % 8 != 0 || up_off + inter > ld || inter > 256u * 8u * 16u)
+        return DUQ4_ERR_SHAPE;
+    if (out8 && inter % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (!aligned16(gate_up) || (reinterpret_cast<uintptr_t>(q) & 3) != 0) return DUQ4_ERR_ALIGN;
+    const __half *hx = (const __half *)gate_up;
+    __half *a = (__half *)s1, *b = (__half *)z1;
+    uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    if (inter <= 256u * 8u * 2u)
+        quant_fused_vec_kernel<MODE, 2, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    else if (inter <= 256u * 8u * 4u)
+        quant_fused_vec_kernel<MODE, 4, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    else if (inter <= 256u * 8u * 8u)
+        quant_fused_vec_kernel<MODE, 8, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    else
+        quant_fused_vec_kernel<MODE, 16, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    return launch_status();
+}
+
 // Used by the fused linear entry point (abi.cu).
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
                             void *z1, void *s2, void *z2, cudaStream_t st, bool out8) {
@@ -540,6 +586,17 @@ int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols
                            void *scale_1_out, void *zeros_1_out, void *scale_2_out, void *zeros_2_out, void *stream) {
     return quantize_fused_dispatch(mode, x, rows, cols, clip_ratio, (uint8_t *)q_i8, scale_1_out, zeros_1_out, scale_2_out,
                                    zeros_2_out, (cudaStream_t)stream, true);
+}
+
+int duq4_silu_mul_quantize_fused(int mode, const void *gate_up, uint32_t rows, uint32_t inter, uint32_t ld,
+                                 uint32_t up_offset, float clip_ratio, void *q, int q_is_int8, void *scale_out,
+                                 void *zeros_out, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (mode == QSYM)
+        return launch_silu<QSYM>(gate_up, rows, inter, ld, up_offset, clip_ratio, (uint8_t *)q, scale_out, nullptr, st, q_is_int8 != 0);
+    if (mode == QASYM)
+        return launch_silu<QASYM>(gate_up, rows, inter, ld, up_offset, clip_ratio, (uint8_t *)q, scale_out, zeros_out, st, q_is_int8 != 0);
+    return DUQ4_ERR_MODE;
 }
 
 int duq4_quantize_sym_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q, void *scale_out,

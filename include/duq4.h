@@ -121,6 +121,19 @@ int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols
                            int8_t *q_i8, void *scale_1_out, void *zeros_1_out, void *scale_2_out,
                            void *zeros_2_out, void *stream);
 
+/* Glue of a SiLU-gated MLP block (gate/up GEMM -> SiLU(gate)*up -> requantize -> down GEMM), no
+ * reference counterpart (the reference has no MLP module; a user composes its Linear modules with
+ * torch's silu and multiply). gate_up is fp16 [rows, ld]; the token fed to the quantizer is
+ *     h[r, j] = half( half(silu(gate_up[r, j])) * gate_up[r, up_offset + j] ),   j in [0, inter),
+ * with silu evaluated in fp32 -- bit for bit what `F.silu(gate) * up` yields in fp16 -- and is
+ * quantized per token exactly as duq4_quantize_{sym,asym}_fused would quantize a stored h, but h
+ * never goes to memory. mode: DUQ4_MODE_SYM or DUQ4_MODE_ASYM. q receives packed codes
+ * [rows, inter/2] (q_is_int8 = 0) or tensor-core-ready int8 [rows, inter] (q_is_int8 != 0, see
+ * duq4_quantize_fused_i8). inter, ld and up_offset must be multiples of 8 (64 for int8 output). */
+int duq4_silu_mul_quantize_fused(int mode, const void *gate_up, uint32_t rows, uint32_t inter, uint32_t ld,
+                                 uint32_t up_offset, float clip_ratio, void *q, int q_is_int8,
+                                 void *scale_out, void *zeros_out, void *stream);
+
 /* ---- dequantize an int32 accumulator tensor ------------------------------------------- */
 
 /* ref: include/quant.h:19-26 sym_dequant_host -> src/kernels/quant.cu:64-97.

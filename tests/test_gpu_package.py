@@ -165,3 +165,31 @@ def test_operator_argument_checks(env):
         tu.matmul(torch.zeros((4, 24), dtype=torch.uint8, device="cuda"), torch.zeros((4, 24), dtype=torch.uint8, device="cuda"))
     q = ops.asym_dual_quant(x, s, s, s, s)           # returns its tensor (the reference's binding does not)
     assert q.dtype == torch.uint8 and tuple(q.shape) == (4, 32)
+
+
+@pytest.mark.parametrize("rows,inter", [(5, 64), (33, 11008), (300, 1024)])
+def test_silu_mul_quantize_fused_equals_torch_composition(env, rows, inter):
+    """SiLU-gated MLP glue: the fused kernel's scales and codes equal quantizing the fp16 tensor
+    F.silu(gate) * up that torch produces (the composition a user of the reference writes)."""
+    torch, qnn, tu, o = env
+    import qlinear4bit._CUDA as ops
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    gate_up = (torch.randn((rows, 2 * inter), device="cuda", generator=g) * 3).half()
+    h = (torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]).contiguous()
+    q_ref, s_ref = ops.quantize_sym_fused(h, 0.95)
+    q, s = ops.silu_mul_quantize_fused(gate_up, "sym", 0.95)
+    assert torch.equal(s.view(torch.int16), s_ref.view(torch.int16))
+    assert torch.equal(q, q_ref)
+    qa_ref, sa_ref, za_ref = ops.quantize_asym_fused(h)
+    qa, sa, za = ops.silu_mul_quantize_fused(gate_up, "asym")
+    assert torch.equal(sa.view(torch.int16), sa_ref.view(torch.int16)) and torch.equal(za.view(torch.int16), za_ref.view(torch.int16))
+    assert torch.equal(qa, qa_ref)
+    # and against the CPU oracle on the stored h
+    hn = h.cpu().numpy()
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), o.sym_scales(hn, 0.95).view(np.uint16))
+    if inter % 64 == 0:   # tensor-core-ready int8 output feeds the GEMM directly
+        q8, s8 = ops.silu_mul_quantize_fused(gate_up, "sym", 0.95, tensor_core_ready=True)
+        codes = o.unpack_s4(q.cpu().numpy()).astype(np.int16)
+        pos = np.arange(inter); blk, r = pos // 128, pos % 128
+        src = blk * 128 + 32 * (r // 32) + 2 * (r % 16) + ((r % 32) // 16)
+        assert np.array_equal(q8.cpu().numpy().astype(np.int16), 16 * codes[:, src])
