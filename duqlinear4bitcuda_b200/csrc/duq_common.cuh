@@ -25,6 +25,14 @@ inline int launch_status() {
     return (int)e;
 }
 
+// Per-device one-time launch set-up (function attributes are per device): `done[dev]` flags for
+// up to 64 devices, one array per kernel instantiation. Returns the current device or -1.
+inline int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    return dev;
+}
+
 __device__ __forceinline__ int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }
 
 // One symmetric code: clamp(rn(x / s), -8, 6). __hdiv is the same intrinsic the reference

@@ -384,7 +384,10 @@ static int sm_count() {
 template <int MODE, int BN, int UW, int NPK_, int NUP_>
 static int launch(const void *A, const void *B, const Args &args, cudaStream_t st, bool cache_maps) {
     using C = Cfg<MODE, BN, UW, NPK_, NUP_>;
-    static bool attr_set = false;
+    static bool attr_done[64] = {};
+    const int dev = current_device_slot();
+    if (dev < 0) return DUQ4_ERR_DEVICE;
+    bool &attr_set = attr_done[dev];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, UW, NPK_, NUP_>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);

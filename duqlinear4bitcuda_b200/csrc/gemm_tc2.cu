@@ -360,8 +360,13 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     auto *kernel = gemm_tc2_kernel<APK>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
-    static int max_pairs = -1;
-    if (max_pairs < 0) {
+    static int pairs_of[64];
+    static bool pairs_known[64] = {};
+    const int dev = current_device_slot();
+    if (dev < 0) return DUQ4_ERR_DEVICE;
+    int &max_pairs = pairs_of[dev];
+    if (!pairs_known[dev]) {
+        pairs_known[dev] = true;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
         if (e != cudaSuccess) return (int)e;
         cudaLaunchConfig_t q = {};

@@ -389,7 +389,10 @@ template <int R, int TH>
 static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                       const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms) {
     using S = GemvSmem<R>;
-    static bool attr_set = false;
+    static bool attr_done[64] = {};
+    const int dev = current_device_slot();
+    if (dev < 0) return DUQ4_ERR_DEVICE;
+    bool &attr_set = attr_done[dev];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
         if (e != cudaSuccess) return (int)e;
