@@ -433,6 +433,159 @@ int gemv_status_read(int32_t *out) {
     return DUQ4_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent, double-buffered variant of gemv_w4a4_kernel. Same arithmetic and the same K-split
+// over eight warps, but a CTA walks over many 16-row blocks (grid = CTAs that fit on the device
+// at once) and keeps TWO batches of weight loads per thread in registers: the loads of batch
+// f+1 are issued before batch f is consumed, so the memory pipe never drains at a block
+// boundary -- the reduction, barrier and epilogue of one block overlap the next block's loads.
+template <int TH, int U>
+struct GemvBuf {
+    uint4 w[U][2];    // rows g and g+8 of the block, U consecutive k-steps of this warp
+    uint4 a[U][TH];   // matching token chunks
+};
+
+template <int TH, int U>
+__global__ void __launch_bounds__(kGemvWarps * 32, 2)
+gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ W, uint32_t M, uint32_t N, uint32_t K,
+                         uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0) {
+    __shared__ int red[2][kGemvWarps][16][17];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t kb = K >> 1, nchunk = kb >> 4, nstep = (nchunk + 3) >> 2;
+    const uint32_t nb = (nstep + kGemvWarps * U - 1) / (kGemvWarps * U);   // batches per row block
+    const uint32_t blocks_per_b = (N + 15) / 16, units = blocks_per_b * batch;
+    const uint32_t my_units = blockIdx.x < units ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t total = my_units * nb;
+
+    auto unit_of = [&](uint32_t f) { return blockIdx.x + (f / nb) * gridDim.x; };
+    auto issue_w = [&](GemvBuf<TH, U> &buf, uint32_t f) {
+        const uint32_t unit = unit_of(f), bi = f % nb;
+        const uint32_t b = unit / blocks_per_b, row0 = (unit % blocks_per_b) * 16;
+        const uint8_t *Wb = W + (size_t)b * N * kb;
+        const uint4 *r0 = reinterpret_cast<const uint4 *>(Wb + (size_t)min(row0 + g, N - 1) * kb);
+        const uint4 *r1 = reinterpret_cast<const uint4 *>(Wb + (size_t)min(row0 + g + 8, N - 1) * kb);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t ch = ((bi * kGemvWarps + warp) * U + u) * 4 + t;
+            const bool ok = ch < nchunk;
+            buf.w[u][0] = ok ? ldg_stream(r0 + ch) : make_uint4(0, 0, 0, 0);
+            buf.w[u][1] = ok ? ldg_stream(r1 + ch) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto issue_a = [&](GemvBuf<TH, U> &buf, uint32_t f) {
+        const uint32_t unit = unit_of(f), bi = f % nb;
+        const uint8_t *Ab = A + (size_t)(unit / blocks_per_b) * M * kb;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t ch = ((bi * kGemvWarps + warp) * U + u) * 4 + t;
+#pragma unroll
+            for (int h = 0; h < TH; ++h) {
+                const uint32_t m = g + 8 * h;
+                const bool ok = ch < nchunk && m < M;
+                buf.a[u][h] = ok ? __ldg(reinterpret_cast<const uint4 *>(Ab + (size_t)m * kb) + ch) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    int acc[TH][4];
+#pragma unroll
+    for (int h = 0; h < TH; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h][i] = 0;
+
+    auto consume = [&](const GemvBuf<TH, U> &buf, uint32_t f) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&buf.w[u][0]);
+            const uint32_t *w1 = reinterpret_cast<const uint32_t *>(&buf.w[u][1]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t a0 = nib_lo(w0[j]), a1 = nib_lo(w1[j]), a2 = nib_hi(w0[j]), a3 = nib_hi(w1[j]);
+#pragma unroll
+                for (int h = 0; h < TH; ++h) {
+                    const uint32_t tw = reinterpret_cast<const uint32_t *>(&buf.a[u][h])[j];
+                    mma_s8(acc[h], a0, a1, a2, a3, nib_lo(tw), nib_hi(tw));
+                }
+            }
+        }
+        if (f % nb != nb - 1) return;
+        // last batch of a row block: split-K reduction over the eight warps, dequant, store
+        const uint32_t ui = f / nb, unit = unit_of(f);
+        const uint32_t b = unit / blocks_per_b, row0 = (unit % blocks_per_b) * 16;
+        int(*rd)[16][17] = red[ui & 1];
+#pragma unroll
+        for (int h = 0; h < TH; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                rd[warp][8 * h + 2 * t + (i & 1)][g + 8 * (i >> 1)] = acc[h][i];
+                acc[h][i] = 0;
+            }
+        __syncthreads();   // one barrier per block; red[] alternates so the next block's writers cannot overtake readers
+        const uint32_t o = threadIdx.x;
+        if (o < 16u * 8u * TH) {
+            const uint32_t nl = o & 15, m = o >> 4, n = row0 + nl;
+            if (m < M && n < N) {
+                int sum = 0;
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) sum += rd[w][m][nl];
+                sum >>= 8;   // exact: a multiple of 256
+                const EpiParams p = epi_for_batch(p0, b);
+                if (acc0) acc0[((size_t)b * M + m) * N + n] = sum;
+                if (p.mode != DUQ4_MODE_NONE) {
+                    ColTerms ct = load_col_terms(p, n);
+                    __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
+                    const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, ct);
+                    const size_t off = ((size_t)b * M + m) * p.ldo + n;
+                    if (p.n_peers == 0) {
+                        out0[off] = v;
+                    } else {
+#pragma unroll
+                        for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
+                            if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+                    }
+                }
+            }
+        }
+    };
+
+    pdl_launch_dependents();
+    GemvBuf<TH, U> b0, b1;
+    if (total > 0) issue_w(b0, 0);   // weights are parameters: fetched before the previous grid has finished
+    pdl_wait();                      // activations / outputs belong to the stream's earlier work
+    if (total > 0) issue_a(b0, 0);
+    for (uint32_t f = 0; f < total; f += 2) {
+        if (f + 1 < total) { issue_w(b1, f + 1); issue_a(b1, f + 1); }
+        consume(b0, f);
+        if (f + 1 >= total) break;
+        if (f + 2 < total) { issue_w(b0, f + 2); issue_a(b0, f + 2); }
+        consume(b1, f + 1);
+    }
+}
+
+template <int TH, int U>
+static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                          const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms) {
+    const uint32_t units = cdiv(N, 16) * batch;
+    uint32_t grid = 2u * (uint32_t)sms;
+    if (grid > units) grid = units;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemvWarps * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_persist_kernel<TH, U>, A, W, M, N, K, batch, p, (__half *)out, acc_out);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)e;
+    }
+    return launch_status();
+}
+
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) != 0) return DUQ4_ERR_ALIGN;
@@ -442,13 +595,22 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        const char *e = getenv("DUQ4_GEMV_VARIANT");   // debug: 0 = register-streamed kernel, 1 = TMA-streamed kernel
+        const char *e = getenv("DUQ4_GEMV_VARIANT");   // debug: 0 = one-shot register kernel, 1 = TMA-streamed kernel, 3 = persistent register kernel
         force = e ? atoi(e) : -1;
     }
-    // Measured on B200 (cold weights, CUDA-graph chain): the TMA-streamed kernel wins once there
-    // are at least two 32-row blocks per SM and more than 8 tokens; the register-streamed one
-    // has the shorter start-up and wins elsewhere.
-    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && M > 8 && (uint64_t)cdiv(N, 32) * batch >= 2ull * sms);
+    // Measured on B200 (cold weights, CUDA-graph chain of layers, us per layer; one-shot / persistent / TMA):
+    //   4096->22016: M=1 10.9/10.8/10.4, M=16 16.9/15.6/14.3     4096->4096: M=1 2.9/2.9/3.7, M=16 4.8/4.1/5.0
+    //   11008->4096: M=1 7.1/6.3/7.1,   M=16 10.0/8.2/9.8
+    // -> TMA-streamed for > 8 tokens on layers with >= 2 32-row blocks per SM; persistent when a row block
+    //    needs more than one batch of loads per warp (long K) or for > 8 tokens; one-shot otherwise.
+    const bool big_n = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
+    const bool long_k = (K / 2 / 64) > (uint32_t)(kGemvWarps * 4);
+    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && M > 8 && big_n);
+    const bool persist = force >= 0 ? force == 3 : (!use_tma && (long_k || M > 8));
+    if (persist) {
+        if (M <= 8) return launch_persist<1, 4>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+        return launch_persist<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+    }
     if (use_tma) {
         const bool two = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
         if (M <= 8) return two ? launch_tma<2, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms)

@@ -89,7 +89,7 @@ def test_decode_streaming_kernel_modes(env, mode, M, N, K):
     run_linear(torch, L, o, mode, M, N, K, seed=M + N, bias=(M != 7), col0=(6 if M == 16 else 0))
 
 
-@pytest.mark.parametrize("variant", ["0", "1"])
+@pytest.mark.parametrize("variant", ["0", "1", "3"])
 def test_decode_both_kernels_pinned(variant):
     """Each small-M kernel forced for every shape, in a fresh process (the choice is read once)."""
     import os, subprocess, sys
