@@ -307,12 +307,12 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4 &g, const uint4 &u) {
 // SILU = false: the token is x[row, 0:cols] (in_stride = cols). SILU = true: the token is
 // silu(x[row, 0:cols]) * x[row, up_off : up_off+cols] of a [rows, in_stride] gate/up tensor, i.e. the
 // activation of a SiLU-gated MLP is formed, measured and quantized without ever being stored in fp16.
-template <int MODE, int VPT, bool SILU = false>
-__global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__restrict__ x, uint32_t rows, uint32_t cols,
+template <int MODE, int VPT, bool SILU = false, int NT = 256>
+__global__ void __launch_bounds__(NT) quant_fused_vec_kernel(const __half *__restrict__ x, uint32_t rows, uint32_t cols,
                                                               float clip, uint8_t *__restrict__ q, __half *s1o,
                                                               __half *z1o, __half *s2o, __half *z2o, bool out8,
                                                               uint32_t in_stride = 0, uint32_t up_off = 0) {
-    __shared__ float sm[8][4];
+    __shared__ float sm[NT / 32][4];
     const uint32_t nvec = cols >> 3;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * (SILU ? in_stride : cols));
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
         stats_init<MODE>(st);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            uint32_t v = threadIdx.x + i * 256;
+            uint32_t v = threadIdx.x + i * NT;
             if (v < nvec) {
                 d[i] = __ldg(xr + v);
                 if (SILU) d[i] = silu_mul8(d[i], __ldg(xr + (up_off >> 3) + v));
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
         __half2 hmx = __float2half2_rn(-INFINITY), hmn = __float2half2_rn(INFINITY);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            uint32_t v = threadIdx.x + i * 256;
+            uint32_t v = threadIdx.x + i * NT;
             if (v < nvec) {
                 const uint32_t w[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
                 if (kDual && v < 2) {   // columns 0..15 straddle the split at column 10: per element
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
             stats_init<MODE>(st);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                uint32_t v = threadIdx.x + i * 256;
+                uint32_t v = threadIdx.x + i * NT;
                 if (v < nvec) {
                     const __half *h = reinterpret_cast<const __half *>(&d[i]);
 #pragma unroll
@@ -391,7 +391,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
             uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                uint32_t v = threadIdx.x + i * 256;
+                uint32_t v = threadIdx.x + i * NT;
                 if (v < nvec) qr[v] = code(d[i], v);
             }
         } else {
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(256) quant_fused_vec_kernel(const __half *__re
             uint8_t *qr = q + (size_t)row * cols;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                uint32_t v = threadIdx.x + i * 256;
+                uint32_t v = threadIdx.x + i * NT;
                 if (v < nvec) {
                     uint32_t w = code(d[i], v);
                     uint32_t off = (v >> 4) * 128 + ((v & 15) >> 2) * 32 + (v & 3) * 4;
@@ -528,14 +528,15 @@ static int launch_silu(const void *gate_up, uint32_t rows, uint32_t inter, uint3
     const __half *hx = (const __half *)gate_up;
     __half *a = (__half *)s1, *b = (__half *)z1;
     uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
-    if (inter <= 256u * 8u * 2u)
-        quant_fused_vec_kernel<MODE, 2, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
-    else if (inter <= 256u * 8u * 4u)
-        quant_fused_vec_kernel<MODE, 4, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
-    else if (inter <= 256u * 8u * 8u)
-        quant_fused_vec_kernel<MODE, 8, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    // 512 threads per token: the SiLU evaluation is ALU-heavy, more warps per SM hide it better
+    if (inter <= 512u * 8u * 1u)
+        quant_fused_vec_kernel<MODE, 1, true, 512><<<grid, 512, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    else if (inter <= 512u * 8u * 2u)
+        quant_fused_vec_kernel<MODE, 2, true, 512><<<grid, 512, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+    else if (inter <= 512u * 8u * 4u)
+        quant_fused_vec_kernel<MODE, 4, true, 512><<<grid, 512, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
     else
-        quant_fused_vec_kernel<MODE, 16, true><<<grid, 256, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
+        quant_fused_vec_kernel<MODE, 8, true, 512><<<grid, 512, 0, st>>>(hx, rows, inter, clip, q, a, b, nullptr, nullptr, out8, ld, up_off);
     return launch_status();
 }
 
