@@ -17,7 +17,7 @@ __all__ = [
     "matmul", "matmul_8bit", "batched_matmul", "sym_quant", "sym_dual_quant", "sym_dequant", "sym_dual_dequant",
     "asym_quant", "asym_quant_8bit", "asym_batch_dequant", "asym_dequant", "asym_dequant_hprec", "asym_dual_quant",
     "asym_dual_dequant", "get_dual_quant_col_k", "quantize_sym_fused", "quantize_asym_fused",
-    "quantize_sym_dual_fused", "quantize_asym_dual_fused", "silu_mul_quantize_fused", "linear_w4a4", "linear_w4a4_batched",
+    "quantize_sym_dual_fused", "quantize_asym_dual_fused", "silu_mul_quantize_fused", "linear_w4a4", "linear_w4a4_from_fp16", "linear_w4a4_batched",
 ]
 
 
@@ -302,6 +302,36 @@ def linear_w4a4(mode, A, W, scale_row, zeros_row=None, scale_col_1=None, zeros_c
                            col_offset, out.stride(0) if M > 1 else max(out.stride(0), N))
     _run("duq4_linear_w4a4", A, _p(A), _p(W), M, N, K, ctypes.byref(epi), _p(out), _p(acc))
     return (out, acc) if return_acc else out
+
+
+_WS = {}   # per-device scratch for linear_w4a4_from_fp16, grown on demand
+
+
+def linear_w4a4_from_fp16(mode, x, W, scale_col_1, zeros_col_1=None, scale_col_2=None, zeros_col_2=None, bias=None,
+                          clip_ratio=1.0, act_mode=None):
+    """(new) fp16 activations [M,K] -> per-token quantize -> GEMM -> dequant (+bias) in one library call
+    (two launches, the quantized activations stay in an internal scratch tensor in the GEMM's
+    tensor-core-ready layout). Same result as quantizer module + linear_w4a4. `act_mode` defaults to
+    the single-scale quantizer of the epilogue's family ("sym" for sym/sym_dual, "asym" otherwise),
+    which is what the reference modules pair with each linear variant."""
+    _check("linear_w4a4_from_fp16", x=x, W=W, scale_col_1=scale_col_1, zeros_col_1=zeros_col_1, scale_col_2=scale_col_2,
+           zeros_col_2=zeros_col_2, bias=bias)
+    if x.dtype != torch.float16 or x.dim() != 2:
+        raise RuntimeError("linear_w4a4_from_fp16: x must be fp16 [M, K]")
+    M, K, N = x.size(0), x.size(1), W.size(0)
+    if W.size(1) * 2 != K:
+        raise RuntimeError("linear_w4a4_from_fp16: x and W disagree on K")
+    if act_mode is None:
+        act_mode = "sym" if mode in ("sym", "sym_dual") else "asym"
+    need = _L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+    ws = _WS.get(x.device)
+    if ws is None or ws.numel() < need:
+        ws = _WS[x.device] = torch.empty(need, dtype=torch.uint8, device=x.device)
+    out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    epi = _L.make_epilogue(mode, None, None, scale_col_1, zeros_col_1, scale_col_2, zeros_col_2, bias)
+    _run("duq4_linear_w4a4_from_fp16", x, _p(x), _p(W), M, N, K, _L.MODES[act_mode], float(clip_ratio), ctypes.byref(epi),
+         _p(out), _p(ws), ws.numel())
+    return out
 
 
 def linear_w4a4_batched(mode, A, W, scale_row, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,

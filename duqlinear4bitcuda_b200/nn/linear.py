@@ -34,6 +34,19 @@ class _PackedLinearBase(torch.nn.Module):
     def _vec(self, name):
         return getattr(self, name, None) if name in self._vectors else None
 
+    def _fused_fp16(self, x):
+        """fp16 input of a module that owns its quantizer: quantize + GEMM + dequant in one library
+        call; the activations never exist as packed codes in HBM."""
+        from .. import _CUDA as ops
+        if not x.is_contiguous():
+            x = x.contiguous()
+        flat = lambda t: None if t is None else t.reshape(-1)
+        first = lambda a, b: self._vec(a) if a in self._vectors else self._vec(b)
+        y = ops.linear_w4a4_from_fp16(self._mode, x.view(-1, x.shape[-1]), self.weight,
+                                      flat(first("weight_scales", "weight_scales_1")), flat(first("weight_zeros", "weight_zeros_1")),
+                                      flat(self._vec("weight_scales_2")), flat(self._vec("weight_zeros_2")), self.bias)
+        return y.view(*x.shape[:-1], -1)
+
     def _fused(self, packed):
         if type(packed) is not PackedQuantizedTensor:
             raise AssertionError("Input should be quantized tensor, or require_quantizer should be passed as initial argument")
@@ -123,6 +136,8 @@ class Linear4bitASQ(_PackedLinearBase):
 
     def forward(self, x):
         if self.require_quantizer:
+            if isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float16 and x.shape[-1] % 64 == 0:
+                return self._fused_fp16(x)   # same result as self.quantizer(x) followed by the fused linear
             x = self.quantizer(x)
         return self._fused(x)
 
@@ -154,6 +169,8 @@ class LinearQuant4bitDUASQ(_PackedLinearBase):
 
     def forward(self, x):
         if self.require_quantizer:
+            if isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float16 and x.shape[-1] % 64 == 0:
+                return self._fused_fp16(x)   # same result as self.quantizer(x) followed by the fused linear
             x = self.quantizer(x)
         return self._fused(x)
 

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own Python code.
 
-Run once, in a container that has the reference checkout (default /root/reference):
+Run once, in a container that has a checkout of the reference project:
 
-    python tests/golden/make_golden.py [--ref /path/to/DUQLinear4bitCUDA]
+    python tests/golden/make_golden.py --ref /path/to/DUQLinear4bitCUDA
 
 The reference's quantizer modules (qlinear4bit/nn/quantizer.py) and its pure-torch tools
 (qlinear4bit/tools/quantization.py) run on CPU; its compiled extension `qlinear4bit._CUDA`

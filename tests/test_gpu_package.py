@@ -193,3 +193,18 @@ def test_silu_mul_quantize_fused_equals_torch_composition(env, rows, inter):
         pos = np.arange(inter); blk, r = pos // 128, pos % 128
         src = blk * 128 + 32 * (r // 32) + 2 * (r % 16) + ((r % 32) // 16)
         assert np.array_equal(q8.cpu().numpy().astype(np.int16), 16 * codes[:, src])
+
+
+def test_owned_quantizer_modules_fp16_path_equals_two_step_path(env):
+    """Linear4bitASQ / LinearQuant4bitDUASQ given fp16 input run quantize+GEMM+dequant in one call;
+    the result equals quantizer module -> linear on the packed tensor, bit for bit."""
+    torch, qnn, tu, o = env
+    lin = _lin(torch, 512, 264, 21)
+    x = torch.from_numpy(U.acts(2 * 150, 512, 22, mean=0.1)).view(2, 150, 512).cuda()
+    for cls in (qnn.Linear4bitASQ, qnn.LinearQuant4bitDUASQ):
+        mod = cls.from_linear(lin, require_quantizer=True).cuda()
+        y = mod(x)
+        packed = mod.quantizer(x)
+        y2 = mod._fused(packed)
+        assert tuple(y.shape) == (2, 150, 264)
+        assert torch.equal(y.view(torch.int16), y2.view(torch.int16)), cls.__name__
