@@ -100,6 +100,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
     // activations (and every write) wait for the previous grid. Without the attribute both
     // instructions do nothing.
     pdl_launch_dependents();
+    // Per-channel terms of the column this thread will finish (all of a thread's outputs share it):
+    // fetched now, so that their DRAM latency runs in parallel with the weight stream instead of
+    // extending the CTA's tail. They are parameters like the weights (see duq4_set_static_weights).
+    ColTerms ct_mine;
+    ct_mine.s = ct_mine.z = ct_mine.b = __ushort_as_half(0);
+    ct_mine.has_bias = false;
+    {
+        const uint32_t n_mine = row0 + (threadIdx.x % (16 * R));
+        if (p.mode != DUQ4_MODE_NONE && n_mine < N) ct_mine = load_col_terms(p, n_mine);
+    }
     bool waited = false;
     constexpr int U = 4;  // k-steps in flight per warp
     for (uint32_t s0 = warp * U; s0 < nstep; s0 += kGemvWarps * U) {
@@ -165,9 +175,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         s >>= 8;  // exact: s is a multiple of 256
         if (acc_out) acc_out[(size_t)m * N + n] = s;
         if (p.mode != DUQ4_MODE_NONE) {
-            ColTerms ct = load_col_terms(p, n);
             __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
-            const __half v = dequant_one(p.mode, s, p.s_row[m], zr, ct);
+            const __half v = dequant_one(p.mode, s, p.s_row[m], zr, ct_mine);   // nl == threadIdx.x % (16*R) for every o of this thread
             const size_t off = (size_t)m * p.ldo + n;
             if (p.n_peers == 0) {
                 out[off] = v;
@@ -443,6 +452,7 @@ template <int TH, int U>
 struct GemvBuf {
     uint4 w[U][2];    // rows g and g+8 of the block, U consecutive k-steps of this warp
     uint4 a[U][TH];   // matching token chunks
+    ColTerms ct;      // per-channel terms of this thread's output column (valid in a block's last batch)
 };
 
 template <int TH, int U>
@@ -472,6 +482,10 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
             buf.w[u][0] = ok ? ldg_stream(r0 + ch) : make_uint4(0, 0, 0, 0);
             buf.w[u][1] = ok ? ldg_stream(r1 + ch) : make_uint4(0, 0, 0, 0);
         }
+        // The epilogue's per-channel terms ride with the block's last batch of weight loads, so that
+        // their DRAM latency is hidden like the weights' (they are parameters too).
+        const uint32_t n_mine = row0 + (threadIdx.x & 15);
+        if (bi == nb - 1 && p0.mode != DUQ4_MODE_NONE && n_mine < N) buf.ct = load_col_terms(epi_for_batch(p0, b), n_mine);
     };
     auto issue_a = [&](GemvBuf<TH, U> &buf, uint32_t f) {
         const uint32_t unit = unit_of(f), bi = f % nb;
@@ -533,9 +547,8 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
                 const EpiParams p = epi_for_batch(p0, b);
                 if (acc0) acc0[((size_t)b * M + m) * N + n] = sum;
                 if (p.mode != DUQ4_MODE_NONE) {
-                    ColTerms ct = load_col_terms(p, n);
                     __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
-                    const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, ct);
+                    const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, buf.ct);   // nl == threadIdx.x & 15
                     const size_t off = ((size_t)b * M + m) * p.ldo + n;
                     if (p.n_peers == 0) {
                         out0[off] = v;

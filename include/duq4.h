@@ -58,12 +58,13 @@ const char *duq4_error_string(int status);
  * (ref: src/export/bindings.cpp:471-473). */
 int duq4_dual_quant_col_k(void);
 
-/* Process-wide promise about WEIGHT operands (the second matrix of the linear / matmul entry
- * points): on != 0 states that they are never written by earlier work queued on the same
- * stream (they are parameters, uploaded and synchronised before use). The small-M (M <= 16)
- * kernels are then launched with programmatic stream serialization and start streaming weights
- * while the preceding kernel of the stream is still finishing; activations, scales and all
- * outputs still wait for it. Off by default (full stream ordering). Returns the previous value.
+/* Process-wide promise about WEIGHT-side operands (the second matrix of the linear / matmul entry
+ * points and the per-output-channel vectors of the epilogue: scale_col_*, zeros_col_*, bias):
+ * on != 0 states that they are never written by earlier work queued on the same stream (they
+ * are parameters, uploaded and synchronised before use). The small-M (M <= 16) kernels are then
+ * launched with programmatic stream serialization and start streaming weights and per-channel
+ * vectors while the preceding kernel of the stream is still finishing; activations, per-token
+ * scales and all outputs still wait for it. Off by default (full stream ordering). Returns the previous value.
  * No reference counterpart. */
 int duq4_set_static_weights(int on);
 
