@@ -416,7 +416,16 @@ def run_ours(args):
             dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
             out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
 
+    staging = None
+    if world == 1:   # host-buffer entry point: upload, quantize + GEMM, download pipelined over row chunks
+        staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, N, K, 0)
+        staging = torch.empty(staging_bytes, dtype=torch.uint8, device=device)
+
     def step_e2e():
+        if staging is not None:
+            L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(qw), M, N, K, L.MODE_SYM, 1.0,
+                   ctypes.byref(epi_e2e), out_host.data_ptr(), 0, L.ptr(staging), staging_bytes, st())
+            return
         x.copy_(x_host, non_blocking=True)
         if peer is not None:
             peer.barrier()
@@ -487,7 +496,9 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": round(e2e_tops, 2), "unit": "TOPS", "ms_per_step": round(e2e_ms / args.steps, 4),
                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
-                    "api": "duq4_linear_w4a4_from_fp16 (C ABI), activations from pinned host memory, output back to pinned host memory"},
+                    "api": ("duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, copies pipelined with the arithmetic over row chunks)"
+                            if world == 1 else
+                            "duq4_linear_w4a4_from_fp16 (C ABI) between a copy from pinned host memory and a copy of the gathered result back to it")},
             "gpu_launches": args.steps * 2,
             "roofline": {"kernel": "gemm_tc2_kernel (CTA pairs, 256x256x128 tiles, tcgen05.mma.cta_group::2.kind::i8; A int8 pre-unpacked by the quantizer, W int4 unpacked in smem)" if (M >= 256 * 8 and Ns >= 256 * 8) else "gemm_tc_kernel<MODE_A8B4> (tcgen05.mma kind::i8)", "bound": "tensor",
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",

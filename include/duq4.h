@@ -282,6 +282,25 @@ int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t 
                                       uint32_t K, int act_mode, float clip_ratio,
                                       const duq4_epilogue *epi, void *out, void *stream);
 
+/* The same layer with the activations and the result in HOST memory (what a caller holds when
+ * the reference module is fed from the CPU side; ref: src/nn/linear.cpp:102-127 moves nothing
+ * itself, torch's .to(device) / .cpu() around it do). x_host [M, K] fp16 and out_host
+ * [M, epi->ldo or N] fp16 are host pointers -- page-locked memory lets the copies overlap the
+ * arithmetic, pageable memory works but serialises. W and the per-channel vectors of `epi` are
+ * device pointers as everywhere else; epi->n_out_peers must be 0. The tokens are cut into chunks
+ * of `chunk_rows` rows (0 = about a sixteenth of M; rounded up to a multiple of 256, at most 64
+ * chunks) and upload, quantize + GEMM + dequant, and download of successive chunks run on three
+ * streams; the helper streams fork from `stream` at entry and join it at the end, so later work
+ * on `stream` sees out_host complete. `staging` is DEVICE memory, 256-byte aligned, of at least
+ * duq4_linear_host_staging_bytes(M, N, K, chunk_rows) bytes (device copies of x and of the
+ * result plus one chunk's quantizer scratch). Results equal duq4_linear_w4a4_from_fp16 bit for
+ * bit (chunking by rows changes nothing: every stage is per token). No reference counterpart. */
+size_t duq4_linear_host_staging_bytes(uint32_t M, uint32_t N, uint32_t K, uint32_t chunk_rows);
+int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32_t M, uint32_t N,
+                                    uint32_t K, int act_mode, float clip_ratio,
+                                    const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows,
+                                    void *staging, size_t staging_bytes, void *stream);
+
 /* Device-side status word of the most recent tensor-core GEMM on the current device:
  * 0 = no bounded wait expired. Reads back 4 bytes (synchronises the stream given). */
 int duq4_last_device_status(void *stream, int32_t *status_out /* host pointer */);

@@ -249,6 +249,50 @@ def test_linear_from_fp16(env, M, mode):
                                              L.ptr(ws), nbytes - 1, L.current_stream()) == -4
 
 
+@pytest.mark.parametrize("M,chunk_rows,pinned,pitch", [(4, 0, True, 0), (300, 0, True, 0), (1300, 256, True, 0),
+                                                      (1300, 512, False, 0), (777, 256, True, 24), (2048, 0, True, 0)])
+def test_linear_from_fp16_host_entry_equals_device_entry(env, M, chunk_rows, pinned, pitch):
+    """Host-buffer entry (chunked, three streams) == device-buffer entry bit for bit: every stage is
+    per token, so cutting the tokens into row chunks changes nothing. Covers ragged last chunks (20 rows
+    of 1300: tensor-core kernel; 9 rows of 777: small-M kernel), an output row pitch, pageable host
+    memory, and two calls in a row on the same staging area."""
+    torch, L, o = env
+    N, K = 776, 1024
+    x = U.acts(M, K, 15, mean=0.05)
+    w = (np.random.default_rng(16).standard_normal((N, K)) * 0.02).astype(np.float16)
+    qw, sw = o.weight_sym_quant_pack(w)
+    zc = U.rand_zeros(N, 17)
+    b = np.random.default_rng(18).standard_normal(N).astype(np.float16)
+    dx, dw, dsw, dzc, db = (dev(torch, v) for v in (x, qw, sw, zc, b))
+    ldo = N + pitch
+    for mode in ("sym", "asym"):
+        epi = L.make_epilogue(mode, None, None, dsw, dzc if mode == "asym" else None, None, None, db)
+        nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        want = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi),
+               L.ptr(want), L.ptr(ws), nbytes, L.current_stream())
+        xh = torch.from_numpy(x.copy())
+        oh = torch.full((M, ldo), -3.0, dtype=torch.float16)
+        if pinned:
+            xh, oh = xh.pin_memory(), oh.pin_memory()
+        sbytes = L.cdll.duq4_linear_host_staging_bytes(M, N, K, chunk_rows)
+        staging = torch.zeros(sbytes, dtype=torch.uint8, device="cuda")
+        epi_h = L.make_epilogue(mode, None, None, dsw, dzc if mode == "asym" else None, None, None, db, ldo=ldo)
+        for _ in range(2):
+            L.call("duq4_linear_w4a4_from_fp16_host", xh.data_ptr(), L.ptr(dw), M, N, K, L.MODES[mode], 1.0,
+                   ctypes.byref(epi_h), oh.data_ptr(), chunk_rows, L.ptr(staging), sbytes, L.current_stream())
+        torch.cuda.synchronize()   # the helper streams joined the caller's stream before the call returned
+        assert tc_status(L) == 0
+        got = oh.numpy()
+        assert U.f16_equal_nan(got[:, :N], want.cpu().numpy()), f"{mode}: host entry differs from device entry"
+        if pitch:
+            assert np.all(got[:, N:] == np.float16(-3.0)), "padding columns of the host result were written"
+        assert L.cdll.duq4_linear_w4a4_from_fp16_host(xh.data_ptr(), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi_h),
+                                                      oh.data_ptr(), chunk_rows, L.ptr(staging), sbytes - 1,
+                                                      L.current_stream()) == -4
+
+
 def test_full_size_property_prefill(env):
     """Benchmark-size prefill layer (M=4096, K=8192, N=28672): row sums of the int32 result must
     equal A * (sum of weight rows), and sampled rows must match the oracle exactly."""
