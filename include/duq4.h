@@ -15,8 +15,10 @@
  *     what every launch of the reference uses);
  *   - return value: 0 = ok, < 0 = argument rejected before any launch (DUQ4_ERR_*),
  *     > 0 = a cudaError_t reported by the launch.
- *   - all functions are re-entrant; the only process-wide state is a mutex-guarded
- *     cache of TMA descriptors keyed by (pointer, shape).
+ *   - all functions are re-entrant; the process-wide state is a mutex-guarded cache of TMA
+ *     descriptors keyed by (pointer, shape), the duq4_set_static_weights flag, the scratch
+ *     array of the _static entry point, and two helper streams per device that the _host entry
+ *     point creates on first use.
  */
 #ifndef DUQ4_H_
 #define DUQ4_H_
@@ -64,8 +66,8 @@ int duq4_dual_quant_col_k(void);
  * are parameters, uploaded and synchronised before use). The small-M (M <= 16) kernels are then
  * launched with programmatic stream serialization and start streaming weights and per-channel
  * vectors while the preceding kernel of the stream is still finishing; activations, per-token
- * scales and all outputs still wait for it. Off by default (full stream ordering). Returns the previous value.
- * No reference counterpart. */
+ * scales and all outputs still wait for it. Off by default (full stream ordering). Returns the
+ * previous value. No reference counterpart. */
 int duq4_set_static_weights(int on);
 
 /* ---- quantize, scales (and zero-points) supplied by the caller ------------------------ */
