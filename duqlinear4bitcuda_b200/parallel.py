@@ -165,3 +165,138 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         else:
             full = gather_columns(self.local_forward(x2d), self.n_out, self.group)
         return full.view(*x.shape[:-1], self.n_out)
+
+
+# ---------------------------------------------------------------------------------------------
+# Row-parallel (K-sharded) layer: the companion of the column-parallel layer for a tensor-parallel
+# MLP. The column-parallel gate/up projection leaves every rank with its own block of the hidden
+# activations, which is exactly the K-slice the down projection needs: no gather in between.
+#
+# Bit-exactness with the unsharded layer rests on two facts. (1) Per-token quantizer statistics
+# are exact reductions (max / min of fp16 values), so an all-reduce of the per-rank row statistics
+# gives every rank the scale (and zero-point) the unsharded quantizer would compute, and each rank
+# quantizes its slice with it. (2) The GEMM is an exact integer contraction, so the int32 partial
+# accumulators of the K-slices add up to the unsharded accumulators; they are summed across ranks
+# BEFORE the fp16 dequant, which then runs once on the totals.
+
+
+def k_shard_bounds(k_in: int, world: int, rank: int):
+    """[begin, end) of the input channels (K) owned by `rank`: contiguous, multiples of 64 channels
+    (the GEMM's K granularity) except that trailing ranks may be empty."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    if k_in % 64 != 0:
+        raise ValueError(f"K = {k_in} is not a multiple of 64")
+    per = -(-(k_in // 64) // world) * 64
+    b = min(k_in, rank * per)
+    return b, min(k_in, b + per)
+
+
+def _all_reduce_f16(t: torch.Tensor, op, group=None):
+    """all-reduce of fp16 values; carried as fp32 (exact for max/min) where the backend has no fp16."""
+    if dist.get_backend(group) == "gloo":
+        w = t.to(torch.float32)
+        dist.all_reduce(w, op=op, group=group)
+        return w.to(torch.float16)
+    dist.all_reduce(t, op=op, group=group)
+    return t
+
+
+def global_sym_scale(local_absmax: torch.Tensor, clip_ratio: float = 1.0, group=None):
+    """Per-token symmetric scale of the FULL row from per-rank abs-max values [M] fp16: the formula of
+    the reference's SymQuantizer (qlinear4bit/nn/quantizer.py:10-16) applied to the all-reduced max."""
+    amax = _all_reduce_f16(local_absmax.clone(), dist.ReduceOp.MAX, group)
+    return (amax / 7).to(torch.float16) * clip_ratio
+
+
+def global_asym_scale_zeros(local_min: torch.Tensor, local_max: torch.Tensor, group=None):
+    """Per-token asymmetric scale and zero-point of the FULL row from per-rank min / max [M] fp16:
+    the formula of the reference's AsymQuantizer (qlinear4bit/nn/quantizer.py:24-35)."""
+    mn = _all_reduce_f16(local_min.clone(), dist.ReduceOp.MIN, group)
+    mx = _all_reduce_f16(local_max.clone(), dist.ReduceOp.MAX, group)
+    scale = ((mx - mn) / 15).to(torch.float16)
+    zeros = torch.round(-mn / scale).to(torch.float16)
+    return scale, zeros
+
+
+def reduce_partial_accumulators(acc: torch.Tensor, group=None):
+    """Sum of the ranks' int32 partial accumulators [M, N], in place on every rank (exact)."""
+    dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+    return acc
+
+
+class RowParallelLinear4bit(torch.nn.Module):
+    """One W4A4 layer whose INPUT channels are split over a process group. Holds weight[:, K-slice]
+    (packed, [N, Ks/2]) and the full per-output-channel vectors; forward takes this rank's fp16
+    activation slice [.., Ks] and returns the full fp16 [.., N] on every rank, bit-identical to the
+    unsharded layer.
+
+    mode: "sym" or "asym" (the dual-uniform schemes split the first 10 input channels off, which
+    does not commute with a K split; they are rejected)."""
+
+    def __init__(self, mode, k_in, weight, scales, zeros=None, bias=None, clip_ratio=1.0, group=None):
+        super().__init__()
+        if mode not in ("sym", "asym"):
+            raise ValueError(f"row-parallel layer supports 'sym' and 'asym', not {mode!r}")
+        if mode == "asym" and zeros is None:
+            raise ValueError("asym mode needs weight zero-points")
+        self.mode, self.k_in, self.clip_ratio, self.group = mode, k_in, clip_ratio, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.k_begin, self.k_end = k_shard_bounds(k_in, self.world, self.rank)
+        if weight.shape[1] * 2 != self.k_end - self.k_begin:
+            raise ValueError(f"weight: expected {(self.k_end - self.k_begin) // 2} packed columns, got {weight.shape[1]}")
+        self.register_buffer("weight", weight.contiguous())
+        self.register_buffer("scales", scales.reshape(-1).contiguous())
+        self.register_buffer("zeros", None if zeros is None else zeros.reshape(-1).contiguous())
+        self.register_buffer("bias", None if bias is None else bias.contiguous())
+
+    @classmethod
+    def from_full(cls, mode, weight, scales, zeros=None, bias=None, clip_ratio=1.0, group=None):
+        """Build from the unsharded packed weight [N, K/2]; each rank keeps its packed K-slice."""
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        k_in = weight.shape[1] * 2
+        b, e = k_shard_bounds(k_in, world, rank)
+        return cls(mode, k_in, weight[:, b // 2: e // 2].contiguous(), scales, zeros, bias, clip_ratio, group)
+
+    def forward(self, x_slice: torch.Tensor):
+        from . import _CUDA
+        x2d = x_slice.reshape(-1, x_slice.shape[-1]).contiguous()
+        M, ks = x2d.shape
+        if ks != self.k_end - self.k_begin:
+            raise ValueError(f"activation slice has {ks} channels, this rank owns {self.k_end - self.k_begin}")
+        n_out = self.weight.shape[0]
+        multi = self.world > 1
+        if self.mode == "sym":
+            if ks:
+                amax = torch.max(torch.abs(x2d), dim=-1)[0]
+            else:
+                amax = torch.zeros(M, dtype=torch.float16, device=x2d.device)
+            scale = global_sym_scale(amax, self.clip_ratio, self.group) if multi else (amax / 7).to(torch.float16) * self.clip_ratio
+            zeros = None
+        else:
+            if ks:
+                mn, mx = torch.min(x2d, dim=-1)[0], torch.max(x2d, dim=-1)[0]
+            else:   # an empty slice must not move the global statistics
+                mn = torch.full((M,), float("inf"), dtype=torch.float16, device=x2d.device)
+                mx = -mn
+            if multi:
+                scale, zeros = global_asym_scale_zeros(mn, mx, self.group)
+            else:
+                scale = ((mx - mn) / 15).to(torch.float16)
+                zeros = torch.round(-mn / scale).to(torch.float16)
+        if ks:
+            q = _CUDA.sym_quant(x2d, scale) if self.mode == "sym" else _CUDA.asym_quant(x2d, scale, zeros)
+            acc = _CUDA.matmul(q, self.weight)
+        else:
+            acc = torch.zeros((M, n_out), dtype=torch.int32, device=x2d.device)
+        if multi:
+            reduce_partial_accumulators(acc, self.group)
+        if self.mode == "sym":
+            out = _CUDA.sym_dequant(acc, scale, self.scales, 32)
+        else:
+            out = _CUDA.asym_dequant(acc, scale, zeros, self.scales, self.zeros, 32)
+        if self.bias is not None:
+            out = out + self.bias
+        return out.view(*x_slice.shape[:-1], n_out)

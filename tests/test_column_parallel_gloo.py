@@ -65,3 +65,78 @@ def test_two_rank_gather_matches_unsharded(tmp_path, n_out, mode):
         assert ok == "1", f"rank {r}: gathered result differs from the unsharded layer"
         if mode != "sym":
             assert differs == "1"
+
+
+# ---- row-parallel (K-sharded) host logic -------------------------------------------------------
+def test_k_shard_bounds_cover_and_align():
+    from duqlinear4bitcuda_b200.parallel import k_shard_bounds
+    for k in (64, 128, 4096, 11008, 8192, 28672):
+        for w in (1, 2, 3, 4, 8):
+            spans = [k_shard_bounds(k, w, r) for r in range(w)]
+            assert spans[0][0] == 0 and spans[-1][1] == k
+            for (b0, e0), (b1, e1) in zip(spans, spans[1:]):
+                assert e0 == b1 and b0 <= e0
+            assert all(b % 64 == 0 and e % 64 == 0 for b, e in spans)
+    assert k_shard_bounds(11008, 8, 7) == (9856, 11008)
+    assert k_shard_bounds(128, 4, 3) == (128, 128)   # more ranks than 64-channel blocks: trailing ranks are empty
+    with pytest.raises(ValueError):
+        k_shard_bounds(100, 2, 0)
+
+
+def _row_worker(rank, world, port, mode, k_in, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as o
+        from duqlinear4bitcuda_b200.parallel import (global_asym_scale_zeros, global_sym_scale, k_shard_bounds,
+                                                     reduce_partial_accumulators)
+        M, N = 6, 40
+        x = U.acts(M, k_in, 21, mean=0.2 if mode == "asym" else 0.0)
+        qw = U.rand_codes(N, k_in, 22)
+        sc = U.rand_scales(N, 23); zc = U.rand_zeros(N, 24)
+        b, e = k_shard_bounds(k_in, world, rank)
+        xs = x[:, b:e]
+        # per-rank statistics of the slice -> all-reduce -> the unsharded quantizer's scale (and zero-point)
+        if mode == "sym":
+            amax = np.abs(xs).max(axis=1) if e > b else np.zeros(M, np.float16)
+            s = global_sym_scale(torch.from_numpy(amax.astype(np.float16)), 1.0).numpy()
+            z = None
+            s_want = o.sym_scales(x, 1.0)
+        else:
+            mn = xs.min(axis=1) if e > b else np.full(M, np.inf, np.float16)
+            mx = xs.max(axis=1) if e > b else np.full(M, -np.inf, np.float16)
+            s, z = (t.numpy() for t in global_asym_scale_zeros(torch.from_numpy(mn.astype(np.float16)),
+                                                               torch.from_numpy(mx.astype(np.float16))))
+            s_want, z_want = o.asym_scales_zeros(x)
+        ok_stats = U.bits_equal(s, s_want) and (z is None or U.bits_equal(z, z_want))
+        # slice codes with the global scale, partial int32 GEMM, exact sum over ranks, one dequant
+        if e > b:
+            q = o.sym_quant(np.ascontiguousarray(xs), s) if mode == "sym" else o.asym_quant(np.ascontiguousarray(xs), s, z)
+            acc = o.matmul_4bit(q, np.ascontiguousarray(qw[:, b // 2: e // 2]))
+        else:
+            acc = np.zeros((M, N), np.int32)
+        acc = reduce_partial_accumulators(torch.from_numpy(acc.copy())).numpy()
+        got = o.sym_dequant(acc, s, sc) if mode == "sym" else o.asym_dequant(acc, s, z, sc, zc)
+        # the unsharded layer
+        if mode == "sym":
+            qa = o.sym_quant(x, s_want); _, want = o.linear_w4a4("sym", qa, qw, s_want, None, sc, None, None, None)
+        else:
+            qa = o.asym_quant(x, s_want, z_want); _, want = o.linear_w4a4("asym", qa, qw, s_want, z_want, sc, zc, None, None)
+        ok = U.f16_equal_nan(got, want)
+        open(os.path.join(tmp, f"r{rank}"), "w").write(f"{int(ok_stats)} {int(ok)}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode,k_in,world", [("sym", 256, 2), ("asym", 192, 2), ("sym", 128, 3)])
+def test_row_parallel_partial_sums_match_unsharded(tmp_path, mode, k_in, world):
+    """K-sharded layer on gloo ranks (per-shard arithmetic by the CPU oracle): all-reduced row statistics
+    reproduce the unsharded quantizer's scale / zero-point bit for bit, and int32 partial accumulators
+    summed before the dequant reproduce the unsharded output bit for bit (ragged and empty K-slices
+    included: 192 = 128 + 64; 128 over 3 ranks leaves rank 2 empty)."""
+    port = _free_port()
+    mp.spawn(_row_worker, args=(world, port, mode, k_in, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        ok_stats, ok = open(tmp_path / f"r{r}").read().split()
+        assert ok_stats == "1", f"rank {r}: all-reduced statistics differ from the unsharded quantizer"
+        assert ok == "1", f"rank {r}: row-parallel result differs from the unsharded layer"

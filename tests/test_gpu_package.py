@@ -208,3 +208,25 @@ def test_owned_quantizer_modules_fp16_path_equals_two_step_path(env):
         y2 = mod._fused(packed)
         assert tuple(y.shape) == (2, 150, 264)
         assert torch.equal(y.view(torch.int16), y2.view(torch.int16)), cls.__name__
+
+
+@pytest.mark.parametrize("mode,M", [("sym", 5), ("sym", 300), ("asym", 40)])
+def test_row_parallel_layer_single_rank_equals_fused_layer(mode, M):
+    """RowParallelLinear4bit without a process group (one K-slice = the whole K): its piecewise path
+    (torch statistics, quantize with a given scale, int32 GEMM, dequant) must equal the one-call
+    fused layer bit for bit -- the same identity the multi-rank form relies on."""
+    import torch
+    from duqlinear4bitcuda_b200.parallel import ColumnParallelLinear4bit, RowParallelLinear4bit
+    N, K = 520, 1024
+    x = torch.from_numpy(U.acts(M, K, 31, mean=0.1 if mode == "asym" else 0.0)).cuda()
+    t = lambda a: torch.from_numpy(a).cuda()
+    qw = t(U.rand_codes(N, K, 32)); sc = t(U.rand_scales(N, 33)); zc = t(U.rand_zeros(N, 34))
+    bias = t(np.random.default_rng(35).standard_normal(N).astype(np.float16))
+    row = RowParallelLinear4bit.from_full(mode, qw, sc, zc if mode == "asym" else None, bias)
+    col = ColumnParallelLinear4bit(mode, N, qw, sc, zc if mode == "asym" else None, None, None, bias, unsharded=True)
+    y_row, y_col = row(x), col(x)
+    torch.cuda.synchronize()
+    assert tuple(y_row.shape) == (M, N)
+    assert torch.equal(y_row.view(torch.int16), y_col.view(torch.int16))
+    with pytest.raises(ValueError):
+        RowParallelLinear4bit.from_full("sym_dual", qw, sc)
