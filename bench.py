@@ -268,6 +268,45 @@ def time_mlp_block(torch, L, device):
             "launches_per_block": 4}
 
 
+def time_prefill_sweep(torch, L, device, Ms=(512, 2048, 4096, 8192)):
+    """Whole layer (fused per-token quantizer + GEMM with the dequant in its epilogue, one C-ABI call)
+    on the Llama-2-70B MLP shapes with the asymmetric dual-uniform scheme: activations ~N(0.1, 1) with
+    0.5 % of the channels x30, per-channel asymmetric weights (codes as signed nibbles, zero-points as
+    per-channel vectors)."""
+    rows = []
+    for K, N in ((8192, 28672), (28672, 8192)):
+        g = torch.Generator().manual_seed(100 + K % 97)
+        qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g).to(device)
+        sc1 = (torch.rand(N, generator=g) * 0.01 + 0.002).half().to(device); zc1 = torch.randint(0, 16, (N,), generator=g).half().to(device)
+        sc2 = (torch.rand(N, generator=g) * 0.01 + 0.002).half().to(device); zc2 = torch.randint(0, 16, (N,), generator=g).half().to(device)
+        epi = L.make_epilogue("asym_dual", None, None, sc1, zc1, sc2, zc2)
+        for M in Ms:
+            gd = torch.Generator(device=device).manual_seed(1000 + M)   # seeded on the device: 235 M values at the largest size
+            x = torch.randn((M, K), generator=gd, dtype=torch.float32, device=device) + 0.1
+            x[:, torch.randperm(K, generator=g)[: K // 200].to(device)] *= 30.0
+            x = x.half()
+            out = torch.empty((M, N), dtype=torch.float16, device=device)
+            nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            fn = lambda: L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, N, K, L.MODES["asym_dual"], 1.0,
+                                ctypes.byref(epi), L.ptr(out), L.ptr(ws), nbytes, L.current_stream())
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            rows.append({"K": K, "N": N, "M": M, "ms_per_layer": round(ms, 4), "tops": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1),
+                         "frac_of_nominal_4500": round(2.0 * M * N * K / (ms * 1e-3) / 1e12 / 4500.0, 3)})
+            del x, out, ws
+    return rows
+
+
 def time_batched(torch, L, device):
     """B = 8 independent 4096 x 4096 weight sets over M = 256 tokens each, one batched launch with
     the asymmetric dequant in the epilogue."""
@@ -518,6 +557,7 @@ def run_ours(args):
             line["decode"] = time_decode(torch, L, device, peaks)
             line["mlp_block"] = time_mlp_block(torch, L, device)
             line["batched"] = time_batched(torch, L, device)
+            line["prefill_sweep"] = time_prefill_sweep(torch, L, device)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()[0]
     if world > 1:

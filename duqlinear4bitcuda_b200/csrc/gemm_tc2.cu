@@ -33,12 +33,17 @@ int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t b
 
 namespace tc2 {
 
+#ifndef DUQ4_TC2_NPK
+#define DUQ4_TC2_NPK 5   // packed-W ring depth for int8 activations (build-time knob for experiments)
+#endif
+
 using namespace ptx;
 using namespace tc;
 
 constexpr int BMH = 128;   // A rows per CTA (half of the pair's 256)
-constexpr int BNH = 128;   // W rows per CTA (half of the pair's 256)
-constexpr int BN = 256;    // accumulator columns
+constexpr int BNH = 128;   // W rows per CTA at the full tile width (half of the pair's 256)
+constexpr int BN = 256;    // accumulator columns at the full tile width; a launch may use narrower tiles
+                           // (Args::bn, a multiple of 32) when that fills the last wave of tiles better
 constexpr int BKE = 128;   // K elements per stage
 constexpr int UW = 8;      // unpack warps
 constexpr int kThreads2 = 32 * (2 + kEpiWarps + UW + 1);
@@ -49,10 +54,14 @@ constexpr int kStageOutWarp = 32 * 144;
 // otherwise they arrive as the quantizer's tensor-core-ready int8 and go straight into the MMA ring.
 template <bool APK>
 struct Cfg2 {
-    static constexpr int NPK = 3;
+    // Ring depths. A packed stage is refilled by a TMA copy that takes about a microsecond to land
+    // (L2 / HBM latency) while a k-step of MMA work takes 0.3-0.4 us, so the packed ring has to
+    // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
+    // (copy latency / 3) per k-step whatever the tile width.
+    static constexpr int NPK = APK ? 4 : DUQ4_TC2_NPK;
     static constexpr int NUP = APK ? 4 : 5;
     static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
-    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 256;
+    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
 };
 
@@ -149,24 +158,25 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t *stage_out = gbase + ct_off + kColTerms;
     const uint32_t bar0 = base + ct_off + kColTerms + kEpiWarps * kStageOutWarp;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
-    auto pk_empty = [&](int s) { return bar0 + 8u * (4 + s); };
-    auto up_full = [&](int s) { return bar0 + 8u * (8 + s); };
-    auto up_empty = [&](int s) { return bar0 + 8u * (14 + s); };
-    auto acc_full = [&](int s) { return bar0 + 8u * (20 + s); };
-    auto acc_empty = [&](int s) { return bar0 + 8u * (22 + s); };
-    const uint32_t drain_bar = bar0 + 8u * 24;
-    static_assert(NPK <= 4 && NUP <= 6, "barrier map");
+    auto pk_empty = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto up_full = [&](int s) { return bar0 + 8u * (16 + s); };
+    auto up_empty = [&](int s) { return bar0 + 8u * (22 + s); };
+    auto acc_full = [&](int s) { return bar0 + 8u * (28 + s); };
+    auto acc_empty = [&](int s) { return bar0 + 8u * (30 + s); };
+    const uint32_t drain_bar = bar0 + 8u * 32;
+    static_assert(NPK <= 8 && NUP <= 6, "barrier map");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const uint32_t num_tiles = a.tiles_m * a.tiles_n * a.batch;   // tiles of 256 x 256
     const uint32_t ksteps = (a.K + BKE - 1) / BKE;
+    const uint32_t bn = a.bn, bnh = bn >> 1;   // this launch's tile width and each CTA's share of the W block
     constexpr int kLastWarp = 2 + kEpiWarps + UW;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < 8; ++s) {
             mbar_init(pk_full(s), 1);
             mbar_init(pk_empty(s), UW);
         }
@@ -211,13 +221,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                     const uint32_t s = it % NPK, ph = (it / NPK) & 1;
                     if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc2_status, 1))) break;
-                    mbar_expect_tx(pk_full(s), kPackedStage);
+                    mbar_expect_tx(pk_full(s), ((APK ? BMH : 0) + bnh) * (BKE / 2));
                     uint32_t dst = pk0 + s * kPackedStage;
                     if (APK) {
                         tma_load_3d(dst, &tmA, pk_full(s), ks * (BKE / 2), tm * 256 + rank * BMH, b);
                         dst += BMH * (BKE / 2);
                     }
-                    tma_load_3d(dst, &tmB, pk_full(s), ks * (BKE / 2), tn * BN + rank * BNH, b);
+                    tma_load_3d(dst, &tmB, pk_full(s), ks * (BKE / 2), tn * bn + rank * bnh, b);
                 }
             }
             if (!ok) {
@@ -248,7 +258,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc(256, BN);
+            const uint32_t idesc = make_idesc(256, (int)bn);
             uint32_t it = 0, lt = 0;
             bool ok = true, issued = false;
             for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs, ++lt) {
@@ -289,14 +299,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t b, tm, tn;
             tile_coords(tile, b, tm, tn);
             const uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
-            const uint32_t n0 = tn * BN;
+            const uint32_t n0 = tn * bn;
             EpiParams pb = a.epi;
             __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
             epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
             if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc2_status, 4))) break;
             tc_fence_after();
             epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                     stage_out + (warp - 2) * kStageOutWarp);
+                                     stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
@@ -304,7 +314,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp < kLastWarp) {
         // ---------------- unpack warps: this CTA's packed W half (and packed A rows) -> swizzled int8 ----------------
         const int ut = (warp - 2 - kEpiWarps) * 32 + lane;
-        constexpr int kChunks = (APK ? BMH + BNH : BNH) * 4;
+        const int kChunks = (int)((APK ? BMH + bnh : bnh) * 4);   // 16-byte chunks of packed rows in a stage
         constexpr uint32_t kDstOff = APK ? 0 : BMH * BKE;
         uint32_t it = 0;
         bool ok = true;
@@ -315,7 +325,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!(ok = mbar_wait(pk_full(s), ph, abortp, &g_tc2_status, 5))) break;
                 if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 6))) break;
                 const uint32_t src = pk0 + s * kPackedStage, dst = up0 + u * kUnpackedStage + kDstOff;
-#pragma unroll
+#pragma unroll 2
                 for (int idx = ut; idx < kChunks; idx += UW * 32) {
                     uint32_t w0, w1, w2, w3;
                     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -351,6 +361,25 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 }  // namespace tc2
+
+// Tile width for a launch. Tiles are handed out round-robin to a fixed number of CTA pairs, so the
+// launch takes ceil(tiles / pairs) rounds. Measured on B200, a round of 224-wide tiles takes 0.98 of
+// a round of 256-wide tiles and 192-wide ones 0.94 (the MMA time hardly shrinks with the width), so
+// a narrower tile only pays where it does not add a round: it then trims the round time a little
+// and spreads a nearly empty last round over more pairs (e.g. N = 8192: 32 -> 37 tile columns,
+// M = 2048: 256 tiles = 3.46 rounds -> 296 tiles = exactly 4 rounds of cheaper tiles).
+// DUQ4_TC_BN pins a width (multiple of 32; tests and experiments).
+static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, uint32_t pairs) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *e = getenv("DUQ4_TC_BN");
+        forced = e ? atoi(e) : 0;
+        if (forced < 32 || forced > 256 || forced % 32 != 0) forced = 0;
+    }
+    if (forced) return (uint32_t)forced;
+    auto rounds = [&](uint32_t bn) { return ((uint64_t)tiles_m * cdiv(N, bn) * batch + pairs - 1) / pairs; };
+    return rounds(224) <= rounds(256) ? 224u : 256u;
+}
 
 template <bool APK>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
@@ -395,11 +424,12 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     a.out = (__half *)out;
     a.acc_out = acc_out;
     a.tiles_m = cdiv(M, 256);
-    a.tiles_n = cdiv(N, 256);
+    a.bn = pick_tile_width(a.tiles_m, N, batch, (uint32_t)max_pairs);
+    a.tiles_n = cdiv(N, a.bn);
     CUtensorMap ma, mb;
     int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma) : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
     if (rc) return rc;
-    rc = tma_map_bytes_3d(B, K / 2, N, batch, BKE / 2, BNH, false, &mb);
+    rc = tma_map_bytes_3d(B, K / 2, N, batch, BKE / 2, a.bn / 2, false, &mb);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
     const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;

@@ -78,6 +78,7 @@ __device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return w & 0xF0F0F0F0u;
 struct Args {
     uint32_t M, N, K, batch;  // K in elements
     uint32_t tiles_m, tiles_n;
+    uint32_t bn;              // CTA-pair kernel only: accumulator columns per tile (multiple of 32, <= 256)
     EpiParams epi;
     __half *out;
     int32_t *acc_out;
@@ -119,7 +120,9 @@ __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb,
 template <int BN, bool STAGED>
 __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &pb, uint32_t b, uint32_t m_base, uint32_t n0,
                                    uint32_t tmem_acc, int quad, int lane, uint32_t shift, const __half *cs,
-                                   const __half *cz, const __half *cb, uint8_t *stg) {
+                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16) {
+    // nch: 16-column chunks of the accumulator that belong to this tile (tiles narrower than BN)
+    const uint32_t n_end = min(a.N, n0 + 16u * (uint32_t)nch);   // first column not written by this tile
     const int mode = a.epi.mode;
     const uint32_t m = m_base + quad * 32 + lane;
     const bool row_ok = m < a.M;
@@ -141,14 +144,14 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
     const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-    for (int ch = 0; ch < BN / 16; ++ch) {
+    for (int ch = 0; ch < nch; ++ch) {
         uint32_t v[16];
         __syncwarp();  // tcgen05.ld is warp-collective
         tmem_ld16(taddr + ch * 16, v);
         tmem_ld_wait();
         const uint32_t c0 = ch * 16;
-        const bool col_any = n0 + c0 < a.N;
-        const bool full = n0 + c0 + 16 <= a.N;
+        const bool col_any = n0 + c0 < n_end;
+        const bool full = n0 + c0 + 16 <= n_end;
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> shift);
         if (arow && row_ok && col_any) {
@@ -158,7 +161,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
                     *reinterpret_cast<int4 *>(arow + c0 + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
             } else {
                 for (int j = 0; j < 16; ++j)
-                    if (n0 + c0 + j < a.N) arow[c0 + j] = (int)v[j];
+                    if (n0 + c0 + j < n_end) arow[c0 + j] = (int)v[j];
             }
         }
         if (mode == DUQ4_MODE_NONE) continue;
@@ -182,7 +185,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
                     *reinterpret_cast<uint4 *>(orow + c0 + 8) = *reinterpret_cast<const uint4 *>(&o[8]);
                 } else {
                     for (int j = 0; j < 16; ++j)
-                        if (n0 + c0 + j < a.N) orow[c0 + j] = o[j];
+                        if (n0 + c0 + j < n_end) orow[c0 + j] = o[j];
                 }
             }
             continue;
@@ -191,15 +194,15 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         // reads the block back as 128-byte row segments, four rows per store instruction
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
-        if ((ch & 3) != 3) continue;
+        if ((ch & 3) != 3 && ch != nch - 1) continue;   // flush every 64 columns and at the tile's end
         __syncwarp();
         const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first column of this lane's 8 (tile-relative)
-        const bool seg_full = n0 + g0 + 8 <= a.N;
+        const bool seg_full = n0 + g0 + 8 <= n_end;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const uint32_t r = it * 4 + (lane >> 3);
             const uint32_t mr = m_base + quad * 32 + r;
-            if (mr >= a.M || n0 + g0 >= a.N) continue;
+            if (mr >= a.M || n0 + g0 >= n_end) continue;
             const uint4 seg = *reinterpret_cast<const uint4 *>(stg + r * 144 + (lane & 7) * 16);
             const size_t off = ((size_t)b * a.M + mr) * pb.ldo + n0 + g0;
 #pragma unroll
@@ -210,7 +213,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
                 } else {
                     const __half *hs = reinterpret_cast<const __half *>(&seg);
                     for (int j = 0; j < 8; ++j)
-                        if (n0 + g0 + j < a.N) ob.base[pi][off + j] = hs[j];
+                        if (n0 + g0 + j < n_end) ob.base[pi][off + j] = hs[j];
                 }
             }
         }

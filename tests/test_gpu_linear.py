@@ -410,6 +410,20 @@ def test_pair_kernel_shapes(env, mode):
     run_linear(torch, L, o, mode, 2000, 2100, 448, seed=71, col0=5)
 
 
+@pytest.mark.parametrize("width", ["160", "192", "224", "32"])
+def test_pair_kernel_tile_widths_pinned(width):
+    """The CTA-pair kernel picks its tile width per launch (narrower tiles when they fill the last
+    round of tiles better); each width forced for the pair-kernel cases, in a fresh process (the
+    choice is read once). Covers packed and pre-unpacked activations, ragged N against every width,
+    int32 accumulators and all epilogue modes."""
+    import os, subprocess, sys
+    env2 = dict(os.environ, DUQ4_TC_BN=width)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", os.path.abspath(__file__), "-k",
+                        "pair_kernel_shapes or pair_kernel_batched or preunpacked_activations_match_packed_path or full_size_property"],
+                       env=env2, capture_output=True, text=True, cwd=U.ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_pair_kernel_batched(env):
     torch, L, o = env
     B, M, N, K = 8, 512, 1024, 256   # 8 x 2 x 4 = 64 pair tiles
