@@ -231,9 +231,13 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
 
 def time_mlp_block(torch, L, device):
     """Quantized SiLU-gated MLP block of a random-init Llama-2-7B layer (hidden 4096, intermediate
-    11008) on 32 x 512 = 16384 tokens: quantize -> fused gate/up GEMM (N = 22016) -> fused
-    SiLU*mul + requantize -> down GEMM. Four launches; the fp16 gate/up tensor is the only
-    intermediate that goes through HBM at full width."""
+    11008) on 32 x 512 = 16384 tokens, four launches either way:
+      fused epilogue : quantize -> gate/up GEMM whose epilogue forms h = silu(g) * u (fp16 [T, I]; the
+                       [T, 2I] gate/up tensor is never written) -> quantize h -> down GEMM
+      glue kernel    : quantize -> gate/up GEMM (fp16 [T, 2I]) -> fused SiLU*mul + requantize -> down GEMM
+    Both give bit-identical results. The glue-kernel pipeline is the faster one (the SiLU arithmetic,
+    exp + IEEE divide per element, overloads the GEMM's four epilogue warps) and is reported as
+    ms_per_block; the other is reported beside it."""
     T, H, I = 32 * 512, 4096, 11008
     st = L.current_stream
     x = synth_activations(torch, T, H, seed=3, pinned=False).to(device)
@@ -241,31 +245,45 @@ def time_mlp_block(torch, L, device):
     w_dn, s_dn = synth_weights(torch, H, I, seed=12, device=device)
     a8 = torch.empty((T, H), dtype=torch.int8, device=device); sa = torch.empty(T, dtype=torch.float16, device=device)
     gu = torch.empty((T, 2 * I), dtype=torch.float16, device=device)
+    h = torch.empty((T, I), dtype=torch.float16, device=device)
     h8 = torch.empty((T, I), dtype=torch.int8, device=device); sh = torch.empty(T, dtype=torch.float16, device=device)
     y = torch.empty((T, H), dtype=torch.float16, device=device)
     e1 = L.make_epilogue("sym", sa, None, s_gu)
     e2 = L.make_epilogue("sym", sh, None, s_dn)
 
-    def block():
+    def block_fused_epilogue():
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), T, H, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
+        L.call("duq4_linear_w4a4_gate_up_silu", L.ptr(a8), 1, L.ptr(w_gu), T, I, H, ctypes.byref(e1), L.ptr(h), st())
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(h), T, I, 1.0, L.ptr(h8), L.ptr(sh), None, None, None, st())
+        L.call("duq4_linear_w4a4_preunpacked", L.ptr(h8), L.ptr(w_dn), T, H, I, ctypes.byref(e2), L.ptr(y), None, st())
+
+    def block_glue_kernel():
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), T, H, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(w_gu), T, 2 * I, H, ctypes.byref(e1), L.ptr(gu), None, st())
         L.call("duq4_silu_mul_quantize_fused", L.MODE_SYM, L.ptr(gu), T, I, 2 * I, I, 1.0, L.ptr(h8), 1, L.ptr(sh), None, st())
         L.call("duq4_linear_w4a4_preunpacked", L.ptr(h8), L.ptr(w_dn), T, H, I, ctypes.byref(e2), L.ptr(y), None, st())
 
-    for _ in range(3):
-        block()
-    torch.cuda.synchronize()
-    e0, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 10
-    e0.record()
-    for _ in range(reps):
-        block()
-    e1_.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1_) / reps
+    def run(block):
+        for _ in range(3):
+            block()
+        torch.cuda.synchronize()
+        e0, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            block()
+        e1_.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1_) / reps
+
+    ms_fused = run(block_fused_epilogue)
+    y_fused = y.clone()
+    ms = run(block_glue_kernel)
+    same = bool(torch.equal(y.view(torch.int16), y_fused.view(torch.int16)))
     ops = 2.0 * T * H * 2 * I + 2.0 * T * I * H
     return {"tokens": T, "hidden": H, "intermediate": I, "ms_per_block": round(ms, 4), "tops": round(ops / (ms * 1e-3) / 1e12, 1),
-            "launches_per_block": 4}
+            "launches_per_block": 4, "pipeline": "quantize, gate/up GEMM, fused SiLU*mul+requantize, down GEMM",
+            "ms_per_block_silu_in_gemm_epilogue_variant": round(ms_fused, 4), "variants_bit_identical": same}
 
 
 def time_prefill_sweep(torch, L, device, Ms=(512, 2048, 4096, 8192)):
@@ -382,6 +400,12 @@ def run_profile_case(args):
         q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev); s = torch.empty(M, dtype=torch.float16, device=dev)
         for x in xs:
             L.call("duq4_quantize_sym_fused", L.ptr(x), M, K, 1.0, L.ptr(q), L.ptr(s), st())
+    elif args.profile_case == "silu":
+        T, I = 4096, 11008   # 180 MB of fp16 gate/up per launch (> L2)
+        gu = (torch.randn((T, 2 * I), device=dev) * 2).half()
+        h8 = torch.empty((T, I), dtype=torch.int8, device=dev); sh = torch.empty(T, dtype=torch.float16, device=dev)
+        for _ in range(4):
+            L.call("duq4_silu_mul_quantize_fused", L.MODE_SYM, L.ptr(gu), T, I, 2 * I, I, 1.0, L.ptr(h8), 1, L.ptr(sh), None, st())
     else:
         raise SystemExit("unknown --profile-case")
     torch.cuda.synchronize()
@@ -576,7 +600,7 @@ def main():
                     help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize", "silu"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.warmup < 3:

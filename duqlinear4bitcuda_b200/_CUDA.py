@@ -334,6 +334,29 @@ def linear_w4a4_from_fp16(mode, x, W, scale_col_1, zeros_col_1=None, scale_col_2
     return out
 
 
+def linear_w4a4_gate_up_silu(mode, A, W, scale_row, zeros_row=None, scale_col=None, zeros_col=None, bias=None):
+    """(new) SiLU-gated gate/up projection in one launch: W packed [2*I, K/2] = gate rows then up rows,
+    `scale_col` / `zeros_col` / `bias` with 2*I entries; returns h fp16 [M, I] equal to
+    `F.silu(y[:, :I]) * y[:, I:]` for y = linear_w4a4(mode, A, W, ...), without writing y. A is either
+    packed int4 activations uint8 [M, K/2] or the tensor-core-ready int8 [M, K] of
+    silu_mul_quantize_fused / duq4_quantize_fused_i8. mode: "sym" or "asym"."""
+    _check("linear_w4a4_gate_up_silu", A=A, W=W, scale_row=scale_row, zeros_row=zeros_row, scale_col=scale_col,
+           zeros_col=zeros_col, bias=bias)
+    if mode not in ("sym", "asym"):
+        raise RuntimeError("linear_w4a4_gate_up_silu: mode must be 'sym' or 'asym'")
+    a_is_int8 = A.dtype == torch.int8
+    M, K = A.size(0), (A.size(1) if a_is_int8 else A.size(1) * 2)
+    if W.size(0) % 2 != 0 or W.size(1) * 2 != K:
+        raise RuntimeError("linear_w4a4_gate_up_silu: W must be [2*I, K/2]")
+    inter = W.size(0) // 2
+    _size0("linear_w4a4_gate_up_silu", "scale_row", scale_row, M)
+    _size0("linear_w4a4_gate_up_silu", "scale_col", scale_col, 2 * inter)
+    h = torch.empty((M, inter), dtype=torch.float16, device=A.device)
+    epi = _L.make_epilogue(mode, scale_row, zeros_row, scale_col, zeros_col, None, None, bias)
+    _run("duq4_linear_w4a4_gate_up_silu", A, _p(A), 1 if a_is_int8 else 0, _p(W), M, inter, K, ctypes.byref(epi), _p(h))
+    return h
+
+
 def linear_w4a4_batched(mode, A, W, scale_row, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
                         zeros_col_2=None):
     """(new) batched form: A [b,M,K/2], W [b,N,K/2], row vectors [b,M], column vectors [b,N]."""

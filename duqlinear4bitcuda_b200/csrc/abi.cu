@@ -10,6 +10,8 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
+int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_t M, uint32_t inter, uint32_t K,
+                            const EpiParams &p, void *h_out, cudaStream_t st);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
 int tc2_status_read(int32_t *out);
@@ -153,6 +155,19 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, A_i8, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
+}
+
+int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W, uint32_t M, uint32_t inter, uint32_t K,
+                                  const duq4_epilogue *epi, void *h_out, void *stream) {
+    if (!A || !W || !epi) return DUQ4_ERR_NULL;
+    if (epi->mode != DUQ4_MODE_SYM && epi->mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;   // the dual selectors go by output column
+    EpiParams p;
+    int rc = check_epi(epi, inter, true, &p);   // ldo defaults to the width of h
+    if (rc) return rc;
+    if (!h_out && !p.n_peers) return DUQ4_ERR_NULL;
+    if (M == 0 || inter == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0 || inter > 0x7FFFFFFFu) return DUQ4_ERR_SHAPE;
+    return gemm_tc2_launch_gate_up(a_is_int8 == 0, A, W, M, inter, K, p, h_out, (cudaStream_t)stream);
 }
 
 // Scratch layout of duq4_linear_w4a4_from_fp16: activation codes, then four fp16 vectors [M]

@@ -124,6 +124,14 @@ __device__ __forceinline__ ColTerms load_col_terms(const EpiParams &p, uint32_t 
     return t;
 }
 
+// SiLU-gated MLP glue for one element: h = half(half(silu(g)) * u), each step rounded to fp16 the way
+// the torch composition `F.silu(gate) * up` rounds it (silu(x) = x / (1 + exp(-x)) evaluated in fp32).
+__device__ __forceinline__ __half silu_mul_one(__half g, __half u) {
+    const float x = __half2float(g);
+    const __half s = __float2half_rn(__fdiv_rn(x, 1.0f + expf(-x)));
+    return __hmul_rn(s, u);
+}
+
 // The reference dequant arithmetic, one rounding per fp16 operation, explicit .rn forms so
 // that no multiply is contracted into an fma with the bias add:
 //   sym : (s_row * s_col) * half(acc)

@@ -139,6 +139,80 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// Epilogue of the SiLU-gated gate/up projection. The tile's accumulator holds, for the same 128
+// hidden channels j = j0 .. j0+127, the gate pre-activations in columns [0,128) and the up
+// projections in columns [128,256) (the two CTAs of the pair loaded their W halves from the gate
+// rows and from the up rows). One warp's 32 rows: both halves are dequantized to fp16 exactly as the
+// plain epilogue would write them, h = half(half(silu(g)) * u) is formed in registers and only h
+// [M, I] goes to memory -- the fp16 gate/up tensor never exists.
+__device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiParams &pb, uint32_t m_base, uint32_t j0,
+                                                       uint32_t tmem_acc, int quad, int lane, const __half *cs,
+                                                       const __half *cz, const __half *cb, uint8_t *stg) {
+    const int mode = a.epi.mode;
+    const uint32_t inter = a.gate_up;
+    const uint32_t m = m_base + quad * 32 + lane;
+    const bool row_ok = m < a.M;
+    __half sr = __ushort_as_half(0), zr = __ushort_as_half(0);
+    if (row_ok) {
+        sr = pb.s_row[m];
+        if (pb.z_row) zr = pb.z_row[m];
+    }
+    const bool has_bias = pb.bias != nullptr;
+    const bool asym = mode == DUQ4_MODE_ASYM;
+    const OutBases ob = out_bases(pb, a.out);
+    uintptr_t obits = 0;
+#pragma unroll
+    for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
+        if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
+    const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
+    const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
+    auto deq = [&](uint32_t raw, int c) {
+        const __half e = __int2half_rn(((int)raw) >> 8);   // accumulators are 256 x the true sums
+        const __half ss = __hmul_rn(sr, cs[c]);
+        __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c])) : __hmul_rn(ss, e);
+        if (has_bias) val = __hadd_rn(val, cb[c]);
+        return val;
+    };
+#pragma unroll 1
+    for (int ch = 0; ch < 8; ++ch) {
+        uint32_t vg[16], vu[16];
+        __syncwarp();  // tcgen05.ld is warp-collective
+        tmem_ld16(taddr + ch * 16, vg);
+        tmem_ld16(taddr + 128 + ch * 16, vu);
+        tmem_ld_wait();
+        const int c0 = ch * 16;
+        __align__(16) __half o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = silu_mul_one(deq(vg[j], c0 + j), deq(vu[j], 128 + c0 + j));
+        *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
+        *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
+        if ((ch & 3) != 3) continue;
+        __syncwarp();
+        const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first hidden channel of this lane's 8 (tile-relative)
+        const bool seg_full = j0 + g0 + 8 <= inter;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const uint32_t r = it * 4 + (lane >> 3);
+            const uint32_t mr = m_base + quad * 32 + r;
+            if (mr >= a.M || j0 + g0 >= inter) continue;
+            const uint4 seg = *reinterpret_cast<const uint4 *>(stg + r * 144 + (lane & 7) * 16);
+            const size_t off = (size_t)mr * pb.ldo + j0 + g0;
+#pragma unroll
+            for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
+                if (pi >= ob.n) break;
+                if (seg_full && vec_ok) {
+                    *reinterpret_cast<uint4 *>(ob.base[pi] + off) = seg;
+                } else {
+                    const __half *hs = reinterpret_cast<const __half *>(&seg);
+                    for (int j = 0; j < 8; ++j)
+                        if (j0 + g0 + j < inter) ob.base[pi][off + j] = hs[j];
+                }
+            }
+        }
+        __syncwarp();   // the block is free for the next 64 channels
+    }
+}
+
 template <bool APK>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
@@ -227,7 +301,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         tma_load_3d(dst, &tmA, pk_full(s), ks * (BKE / 2), tm * 256 + rank * BMH, b);
                         dst += BMH * (BKE / 2);
                     }
-                    tma_load_3d(dst, &tmB, pk_full(s), ks * (BKE / 2), tn * bn + rank * bnh, b);
+                    // gate/up mode: the leader's half comes from the gate rows, the partner's from the up rows
+                    const uint32_t wrow = a.gate_up ? (rank ? a.gate_up : 0u) + tn * 128u : tn * bn + rank * bnh;
+                    tma_load_3d(dst, &tmB, pk_full(s), ks * (BKE / 2), wrow, b);
                 }
             }
             if (!ok) {
@@ -302,11 +378,30 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t n0 = tn * bn;
             EpiParams pb = a.epi;
             __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
-            epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
+            if (a.gate_up) {
+                // per-channel terms of the tile's 128 gate columns, then of its 128 up columns
+                __syncwarp();
+                for (int c = lane; c < BN; c += 32) {
+                    const uint32_t j = tn * 128u + (uint32_t)(c & 127);
+                    ColTerms t;
+                    t.s = t.z = t.b = __ushort_as_half(0);
+                    if (j < a.gate_up) t = load_col_terms(pb, (c < 128 ? 0u : a.gate_up) + j);
+                    cs[c] = t.s;
+                    cz[c] = t.z;
+                    cb[c] = t.b;
+                }
+                __syncwarp();
+            } else {
+                epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
+            }
             if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc2_status, 4))) break;
             tc_fence_after();
-            epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                     stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
+            if (a.gate_up)
+                epi_store_tile_gate_up(a, pb, tm * 256 + rank * BMH, tn * 128u, tmem_base + buf * BN, quad, lane, cs, cz, cb,
+                                       stage_out + (warp - 2) * kStageOutWarp);
+            else
+                epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                                         stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
@@ -383,7 +478,7 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
 
 template <bool APK>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
-                   void *out, int32_t *acc_out, cudaStream_t st) {
+                   void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0) {
     using namespace tc2;
     constexpr int kSmem2 = Cfg2<APK>::kSmem;
     auto *kernel = gemm_tc2_kernel<APK>;
@@ -424,12 +519,13 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     a.out = (__half *)out;
     a.acc_out = acc_out;
     a.tiles_m = cdiv(M, 256);
-    a.bn = pick_tile_width(a.tiles_m, N, batch, (uint32_t)max_pairs);
-    a.tiles_n = cdiv(N, a.bn);
+    a.gate_up = gate_up;   // N is then the width I of h; W has 2*I rows, tiles are 256 rows x 128 hidden channels
+    a.bn = gate_up ? 256u : pick_tile_width(a.tiles_m, N, batch, (uint32_t)max_pairs);
+    a.tiles_n = gate_up ? cdiv(N, 128) : cdiv(N, a.bn);
     CUtensorMap ma, mb;
     int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma) : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
     if (rc) return rc;
-    rc = tma_map_bytes_3d(B, K / 2, N, batch, BKE / 2, a.bn / 2, false, &mb);
+    rc = tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
     const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
@@ -460,6 +556,14 @@ int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uin
                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
     return a_packed ? launch2<true>(A, B, M, N, K, batch, p, out, acc_out, st)
                     : launch2<false>(A, B, M, N, K, batch, p, out, acc_out, st);
+}
+
+// SiLU-gated gate/up projection: W packed [2*I, K/2] (gate rows, then up rows), per-channel vectors of
+// length 2*I, h_out fp16 [M, I] = silu(gate) * up of the dequantized projections.
+int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_t M, uint32_t inter, uint32_t K,
+                            const EpiParams &p, void *h_out, cudaStream_t st) {
+    return a_packed ? launch2<true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter)
+                    : launch2<false>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter);
 }
 
 int tc2_status_read(int32_t *out) {

@@ -296,11 +296,7 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4 &g, const uint4 &u) {
     const __half *hg = reinterpret_cast<const __half *>(&g), *hu = reinterpret_cast<const __half *>(&u);
     __half *hr = reinterpret_cast<__half *>(&r);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float x = __half2float(hg[k]);
-        const __half s = __float2half_rn(__fdiv_rn(x, 1.0f + expf(-x)));
-        hr[k] = __hmul_rn(s, hu[k]);
-    }
+    for (int k = 0; k < 8; ++k) hr[k] = silu_mul_one(hg[k], hu[k]);
     return r;
 }
 

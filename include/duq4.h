@@ -284,6 +284,23 @@ int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t 
                                       uint32_t K, int act_mode, float clip_ratio,
                                       const duq4_epilogue *epi, void *out, void *stream);
 
+/* SiLU-gated gate/up projection of an MLP in one launch: W packed [2*inter, K/2] holds the gate rows
+ * followed by the up rows (the fused weight a user of the reference builds by concatenating the two
+ * Linear4bit weights), per-channel vectors of `epi` have 2*inter entries in the same order, and
+ *     h_out[m, j] = half( half(silu(g[m, j])) * u[m, j] ),   g = layer output column j, u = column inter + j,
+ * i.e. exactly what `F.silu(y[:, :inter]) * y[:, inter:]` gives on the fp16 output y of
+ * duq4_linear_w4a4 -- but y is never written: the CTA pair computing a tile loads one half of its
+ * W block from the gate rows and the other from the up rows, and the epilogue combines them.
+ * A: activations, packed int4 [M, K/2] (a_is_int8 = 0) or the tensor-core-ready int8 [M, K] of
+ * duq4_quantize_fused_i8 (a_is_int8 = 1). epi->mode: DUQ4_MODE_SYM or DUQ4_MODE_ASYM (the dual
+ * schemes select by output column and are rejected); epi->scale_row (/zeros_row) per token;
+ * epi->ldo = row pitch of h_out (0 = inter). Needs a device that co-schedules CTA pairs
+ * (DUQ4_ERR_DEVICE otherwise). No reference counterpart: the reference has Linear modules only
+ * (qlinear4bit/nn/linear.py), an MLP is composed by its user. */
+int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W, uint32_t M,
+                                  uint32_t inter, uint32_t K, const duq4_epilogue *epi,
+                                  void *h_out, void *stream);
+
 /* The same layer with the activations and the result in HOST memory (what a caller holds when
  * the reference module is fed from the CPU side; ref: src/nn/linear.cpp:102-127 moves nothing
  * itself, torch's .to(device) / .cpu() around it do). x_host [M, K] fp16 and out_host

@@ -230,3 +230,39 @@ def test_row_parallel_layer_single_rank_equals_fused_layer(mode, M):
     assert torch.equal(y_row.view(torch.int16), y_col.view(torch.int16))
     with pytest.raises(ValueError):
         RowParallelLinear4bit.from_full("sym_dual", qw, sc)
+
+
+@pytest.mark.parametrize("mode,M,inter,K,int8_acts", [("sym", 300, 1408, 512, True), ("asym", 64, 200, 448, False),
+                                                      ("sym", 2048, 2816, 1024, True), ("asym", 520, 1408, 512, True)])
+def test_gate_up_silu_epilogue_equals_unfused_composition(mode, M, inter, K, int8_acts):
+    """One-launch SiLU-gated gate/up projection == linear_w4a4 on the fused [2*I, K] weight followed by
+    torch's F.silu(gate) * up, bit for bit (ragged M, I not a multiple of the 128-channel tile, bias,
+    both activation formats, asymmetric epilogue)."""
+    import torch
+    import qlinear4bit._CUDA as ops
+    import duqlinear4bitcuda_b200.lib as L
+    t = lambda a: torch.from_numpy(a).cuda()
+    x = t(U.acts(M, K, 51, mean=0.1 if mode == "asym" else 0.0))
+    qw = t(U.rand_codes(2 * inter, K, 52))
+    sc = t(U.rand_scales(2 * inter, 53, 0.002, 0.02)); zc = t(U.rand_zeros(2 * inter, 54))
+    bias = t((np.random.default_rng(55).standard_normal(2 * inter) * 0.5).astype(np.float16))
+    if mode == "sym":
+        qa, sa = ops.quantize_sym_fused(x, 1.0); za = None
+    else:
+        qa, sa, za = ops.quantize_asym_fused(x)
+    y = ops.linear_w4a4(mode, qa, qw, sa, za, sc, zc if mode == "asym" else None, None, None, bias)
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    A = qa
+    if int8_acts:   # tensor-core-ready int8 activations from the fused quantizer
+        A = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        s2 = torch.empty(M, dtype=torch.float16, device="cuda"); z2 = torch.empty(M, dtype=torch.float16, device="cuda")
+        L.call("duq4_quantize_fused_i8", L.MODES[mode], L.ptr(x), M, K, 1.0, L.ptr(A), L.ptr(s2), L.ptr(z2) if mode == "asym" else None,
+               None, None, L.current_stream())
+        assert torch.equal(s2.view(torch.int16), sa.reshape(-1).view(torch.int16))
+    h = ops.linear_w4a4_gate_up_silu(mode, A, qw, sa.reshape(-1), None if za is None else za.reshape(-1), sc,
+                                     zc if mode == "asym" else None, bias)
+    torch.cuda.synchronize()
+    assert tuple(h.shape) == (M, inter)
+    assert torch.equal(h.view(torch.int16), want.contiguous().view(torch.int16))
+    with pytest.raises(RuntimeError):
+        ops.linear_w4a4_gate_up_silu("sym_dual", A, qw, sa.reshape(-1), None, sc)
