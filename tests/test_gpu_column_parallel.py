@@ -51,7 +51,8 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 4096), ("sym_dual", 300, 1040, 512), ("asym_dual", 64, 2048, 1024)])
+@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 4096), ("sym_dual", 300, 1040, 512), ("asym_dual", 64, 2048, 1024),
+                                        ("sym", 2048, 4096, 256), ("asym", 2000, 4200, 192)])   # the last two: CTA-pair kernel per rank
 def test_two_gpu_column_parallel_matches_single_gpu(tmp_path, mode, M, N, K):
     import torch
     import torch.multiprocessing as mp
