@@ -631,9 +631,10 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
         return two ? launch_tma<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms)
                    : launch_tma<1, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
     }
-    // Two row groups per CTA halve the token re-reads; one keeps at least ~2 CTAs per SM
-    // busy when N is small.
-    const bool r2 = (uint64_t)(N / 32) * batch >= 2 * 148;
+    // Up to 8 tokens: 16-row CTAs (three per SM) -- more, smaller CTAs keep the weight stream smoother
+    // across CTA boundaries than 32-row ones (4096->22016, M=1: 10.3 vs 10.8 us). 9..16 tokens: two row
+    // groups per CTA halve the token re-reads when there are enough rows to fill the SMs.
+    const bool r2 = M > 8 && (uint64_t)(N / 32) * batch >= 2 * 148;
     const uint32_t rows_per_cta = r2 ? 32 : 16;
     dim3 grid(cdiv(N, rows_per_cta), batch);
     __half *o = (__half *)out;
