@@ -45,23 +45,29 @@ constexpr int BNH = 128;   // W rows per CTA at the full tile width (half of the
 constexpr int BN = 256;    // accumulator columns at the full tile width; a launch may use narrower tiles
                            // (Args::bn, a multiple of 32) when that fills the last wave of tiles better
 constexpr int BKE = 128;   // K elements per stage
-constexpr int UW = 8;      // unpack warps
-constexpr int kThreads2 = 32 * (2 + kEpiWarps + UW + 1);
+// Warp roles: TMA-W producer, MMA issuer, EPI epilogue warps, UWN unpack warps, A producer -- 15 warps.
+// The plain GEMM uses 4 epilogue + 8 unpack warps. The SiLU-gated gate/up variant (GU) turns that
+// around, 8 + 4: its epilogue evaluates exp and an IEEE divide per output and needs the issue
+// slots, while its W unpack (int8 activations need none) is light. Two epilogue warps then share
+// a TMEM lane quadrant and split the tile's hidden channels between them.
+constexpr int kThreads2 = 32 * 15;
 constexpr int kUnpackedStage = (BMH + BNH) * BKE;   // 32 KiB: A tile then W half, both 128B-swizzled int8
-constexpr int kColTerms = kEpiWarps * 3 * BN * 2;
 constexpr int kStageOutWarp = 32 * 144;
 // APK = activations arrive packed (int4, the reference's format) and are unpacked here too;
 // otherwise they arrive as the quantizer's tensor-core-ready int8 and go straight into the MMA ring.
-template <bool APK>
+template <bool APK, bool GU = false>
 struct Cfg2 {
+    static constexpr int EPI = GU ? 8 : 4;    // epilogue warps
+    static constexpr int UWN = GU ? 4 : 8;    // unpack warps
+    static constexpr int kColTerms = EPI * 3 * BN * 2;
     // Ring depths. A packed stage is refilled by a TMA copy that takes about a microsecond to land
     // (L2 / HBM latency) while a k-step of MMA work takes 0.3-0.4 us, so the packed ring has to
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
-    static constexpr int NPK = APK ? 4 : DUQ4_TC2_NPK;
-    static constexpr int NUP = APK ? 4 : 5;
+    static constexpr int NPK = GU ? (APK ? 3 : 5) : (APK ? 4 : DUQ4_TC2_NPK);
+    static constexpr int NUP = (APK || GU) ? 4 : 5;
     static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
-    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kEpiWarps * kStageOutWarp + 512;
+    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
 };
 
@@ -147,7 +153,8 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
 // [M, I] goes to memory -- the fp16 gate/up tensor never exists.
 __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiParams &pb, uint32_t m_base, uint32_t j0,
                                                        uint32_t tmem_acc, int quad, int lane, const __half *cs,
-                                                       const __half *cz, const __half *cb, uint8_t *stg) {
+                                                       const __half *cz, const __half *cb, uint8_t *stg, int ch_begin,
+                                                       int ch_end) {
     const int mode = a.epi.mode;
     const uint32_t inter = a.gate_up;
     const uint32_t m = m_base + quad * 32 + lane;
@@ -166,15 +173,18 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
         if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
     const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
-    auto deq = [&](uint32_t raw, int c) {
-        const __half e = __int2half_rn(((int)raw) >> 8);   // accumulators are 256 x the true sums
-        const __half ss = __hmul_rn(sr, cs[c]);
-        __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c])) : __hmul_rn(ss, e);
-        if (has_bias) val = __hadd_rn(val, cb[c]);
+    // Dequant of two neighbouring columns at a time with the packed fp16 instructions: every lane of
+    // hmul2 / hsub2 / hadd2 rounds like the scalar _rn form, so the values equal the plain epilogue's.
+    const __half2 sr2 = __half2half2(sr), zr2 = __half2half2(zr);
+    auto deq2 = [&](uint32_t raw0, uint32_t raw1, int c) {   // c even
+        const __half2 e = __halves2half2(__int2half_rn(((int)raw0) >> 8), __int2half_rn(((int)raw1) >> 8));   // accumulators are 256 x the true sums
+        const __half2 ss = __hmul2_rn(sr2, *reinterpret_cast<const __half2 *>(cs + c));
+        __half2 val = asym ? __hmul2_rn(ss, __hsub2_rn(__hsub2_rn(e, zr2), *reinterpret_cast<const __half2 *>(cz + c))) : __hmul2_rn(ss, e);
+        if (has_bias) val = __hadd2_rn(val, *reinterpret_cast<const __half2 *>(cb + c));
         return val;
     };
 #pragma unroll 1
-    for (int ch = 0; ch < 8; ++ch) {
+    for (int ch = ch_begin; ch < ch_end; ++ch) {   // 16-channel chunks of the tile's 128 hidden channels (a multiple of 4 of them)
         uint32_t vg[16], vu[16];
         __syncwarp();  // tcgen05.ld is warp-collective
         tmem_ld16(taddr + ch * 16, vg);
@@ -183,7 +193,11 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
         const int c0 = ch * 16;
         __align__(16) __half o[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j] = silu_mul_one(deq(vg[j], c0 + j), deq(vu[j], 128 + c0 + j));
+        for (int j = 0; j < 16; j += 2) {
+            const __half2 g = deq2(vg[j], vg[j + 1], c0 + j), u = deq2(vu[j], vu[j + 1], 128 + c0 + j);
+            o[j] = silu_mul_one(__low2half(g), __low2half(u));
+            o[j + 1] = silu_mul_one(__high2half(g), __high2half(u));
+        }
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
         if ((ch & 3) != 3) continue;
@@ -213,11 +227,12 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
     }
 }
 
-template <bool APK>
+template <bool APK, bool GU>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
-    using C2 = Cfg2<APK>;
+    using C2 = Cfg2<APK, GU>;
     constexpr int NPK = C2::NPK, NUP = C2::NUP, kPackedStage = C2::kPackedStage;
+    constexpr int EPI = C2::EPI, UW = C2::UWN, kColTerms = C2::kColTerms;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -230,7 +245,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t ct_off = NUP * kUnpackedStage + NPK * kPackedStage;
     __half *colterms = reinterpret_cast<__half *>(gbase + ct_off);
     uint8_t *stage_out = gbase + ct_off + kColTerms;
-    const uint32_t bar0 = base + ct_off + kColTerms + kEpiWarps * kStageOutWarp;
+    const uint32_t bar0 = base + ct_off + kColTerms + EPI * kStageOutWarp;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
     auto pk_empty = [&](int s) { return bar0 + 8u * (8 + s); };
     auto up_full = [&](int s) { return bar0 + 8u * (16 + s); };
@@ -246,7 +261,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t num_tiles = a.tiles_m * a.tiles_n * a.batch;   // tiles of 256 x 256
     const uint32_t ksteps = (a.K + BKE - 1) / BKE;
     const uint32_t bn = a.bn, bnh = bn >> 1;   // this launch's tile width and each CTA's share of the W block
-    constexpr int kLastWarp = 2 + kEpiWarps + UW;
+    constexpr int kLastWarp = 2 + EPI + UW;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -260,7 +275,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(acc_full(s), 1);
-            mbar_init(acc_empty(s), 2 * kEpiWarps);
+            mbar_init(acc_empty(s), 2 * EPI);
         }
         mbar_init(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -366,7 +381,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 while (!mbar_try(drain_bar, 0) && globaltimer() - t0 < kPtxWaitLimitNs) __nanosleep(1000);
             }
         }
-    } else if (warp < 2 + kEpiWarps) {
+    } else if (warp < 2 + EPI) {
         // ---------------- epilogue: this CTA's 128 rows of the tile ----------------
         const int quad = warp & 3;
         uint32_t lt = 0;
@@ -378,7 +393,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t n0 = tn * bn;
             EpiParams pb = a.epi;
             __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
-            if (a.gate_up) {
+            if (GU) {
                 // per-channel terms of the tile's 128 gate columns, then of its 128 up columns
                 __syncwarp();
                 for (int c = lane; c < BN; c += 32) {
@@ -396,9 +411,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc2_status, 4))) break;
             tc_fence_after();
-            if (a.gate_up)
+            if (GU)   // warps 2..5 take hidden channels [0,64) of the tile, warps 6..9 [64,128)
                 epi_store_tile_gate_up(a, pb, tm * 256 + rank * BMH, tn * 128u, tmem_base + buf * BN, quad, lane, cs, cz, cb,
-                                       stage_out + (warp - 2) * kStageOutWarp);
+                                       stage_out + (warp - 2) * kStageOutWarp, ((warp - 2) >> 2) * 4, ((warp - 2) >> 2) * 4 + 4);
             else
                 epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                          stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
@@ -408,7 +423,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (warp < kLastWarp) {
         // ---------------- unpack warps: this CTA's packed W half (and packed A rows) -> swizzled int8 ----------------
-        const int ut = (warp - 2 - kEpiWarps) * 32 + lane;
+        const int ut = (warp - 2 - EPI) * 32 + lane;
         const int kChunks = (int)((APK ? BMH + bnh : bnh) * 4);   // 16-byte chunks of packed rows in a stage
         constexpr uint32_t kDstOff = APK ? 0 : BMH * BKE;
         uint32_t it = 0;
@@ -476,12 +491,12 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
     return rounds(224) <= rounds(256) ? 224u : 256u;
 }
 
-template <bool APK>
+template <bool APK, bool GU = false>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
                    void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0) {
     using namespace tc2;
-    constexpr int kSmem2 = Cfg2<APK>::kSmem;
-    auto *kernel = gemm_tc2_kernel<APK>;
+    constexpr int kSmem2 = Cfg2<APK, GU>::kSmem;
+    auto *kernel = gemm_tc2_kernel<APK, GU>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
     static int pairs_of[64];
@@ -562,8 +577,8 @@ int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uin
 // length 2*I, h_out fp16 [M, I] = silu(gate) * up of the dequantized projections.
 int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_t M, uint32_t inter, uint32_t K,
                             const EpiParams &p, void *h_out, cudaStream_t st) {
-    return a_packed ? launch2<true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter)
-                    : launch2<false>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter);
+    return a_packed ? launch2<true, true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter)
+                    : launch2<false, true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter);
 }
 
 int tc2_status_read(int32_t *out) {
