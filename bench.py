@@ -572,7 +572,7 @@ def run_ours(args):
                          "frac": round(gemm_tops / int8_peak, 4),
                          # dram read+write bytes per launch: the ncu capture of the reduced case
                          # (profiles/gemm_tc2_kernel_pair_M2048_K8192_N8192.md: 57.0 MB for 2.75e11 ops) scaled by ops
-                         "traffic": round(57.0e6 * (2.0 * M * Ns * K) / 2.749e11),
+                         "traffic": round(58.5e6 * (2.0 * M * Ns * K) / 2.749e11),
                          "traffic_note": "ncu dram__bytes_read+write of the M=2048,N=8192 capture scaled by ops; algorithmic bytes "
                                          f"{M * K + Ns * K // 2 + 2 * M * Ns} (int8 activations + packed weights + fp16 out)",
                          "avg_launch_ms": round(gemm_avg_ms, 4),
