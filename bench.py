@@ -404,6 +404,15 @@ def run_profile_case(args):
         q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev); s = torch.empty(M, dtype=torch.float16, device=dev)
         for x in xs:
             L.call("duq4_quantize_sym_fused", L.ptr(x), M, K, 1.0, L.ptr(q), L.ptr(s), st())
+    elif args.profile_case == "skinny":
+        M, N, K = 64, 22016, 4096    # up to 128 tokens: narrow tiles, W streamed once (8 x 45 MB of cold weights)
+        W = torch.randint(0, 256, (8, N, K // 2), dtype=torch.uint8, device=dev)
+        a8 = (torch.randint(-8, 8, (M, K), dtype=torch.int8, device=dev) * 16)
+        sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        epi = L.make_epilogue("sym", sa, None, sw)
+        for c in range(8):
+            L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
     elif args.profile_case == "silu":
         T, I = 4096, 11008   # 180 MB of fp16 gate/up per launch (> L2)
         gu = (torch.randn((T, 2 * I), device=dev) * 2).half()
@@ -604,7 +613,7 @@ def main():
                     help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize", "silu"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize", "silu", "skinny"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.warmup < 3:

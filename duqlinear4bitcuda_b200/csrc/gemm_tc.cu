@@ -56,7 +56,7 @@ struct Cfg {
     static constexpr int kUnpackedStage = (BM + BN) * BK;
     static constexpr int NPK = MODE == MODE_I8 ? 1 : NPK_;   // packed-tile ring (TMA -> unpack warps)
     static constexpr int NUP = NUP_;                          // swizzled int8 ring (-> MMA)
-    static_assert(NPK <= 4 && NUP <= 6, "barrier map holds 4 packed and 6 unpacked stages");
+    static_assert(NPK <= 8 && NUP <= 6, "barrier map holds 8 packed and 6 unpacked stages");
     static constexpr int kColTerms = kEpiWarps * 3 * BN * 2;  // per epilogue warp: (scale, zero, bias) x BN halves
     // Output staging (per epilogue warp 32 rows x 64 fp16, rows padded to 144 bytes): lets the
     // epilogue turn its one-row-per-lane registers into 128-byte row segments before they go to
@@ -64,9 +64,10 @@ struct Cfg {
     static constexpr bool kStaged = MODE != MODE_I4;
     static constexpr int kStageOutWarp = 32 * 144;
     static constexpr int kStageOut = kStaged ? kEpiWarps * kStageOutWarp : 0;
-    static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kStageOut + 256 /*barriers*/;
+    static constexpr int kSmem = 1024 /*align slack*/ + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kStageOut + 512 /*barriers*/;
     static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
-    static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
+    // two accumulator buffers; the allocation must be a power of two >= 32 columns
+    static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 };
 
 template <int MODE, int BN, int UW, int NPK_, int NUP_>
@@ -91,12 +92,12 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
     const uint32_t bar0 = base + ct_off + C::kColTerms + C::kStageOut;
     // barrier map (8 bytes each)
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
-    auto pk_empty = [&](int s) { return bar0 + 8u * (4 + s); };
-    auto up_full = [&](int s) { return bar0 + 8u * (8 + s); };
-    auto up_empty = [&](int s) { return bar0 + 8u * (14 + s); };
-    auto acc_full = [&](int s) { return bar0 + 8u * (20 + s); };
-    auto acc_empty = [&](int s) { return bar0 + 8u * (22 + s); };
-    const uint32_t drain_bar = bar0 + 8u * 24;
+    auto pk_empty = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto up_full = [&](int s) { return bar0 + 8u * (16 + s); };
+    auto up_empty = [&](int s) { return bar0 + 8u * (22 + s); };
+    auto acc_full = [&](int s) { return bar0 + 8u * (28 + s); };
+    auto acc_empty = [&](int s) { return bar0 + 8u * (30 + s); };
+    const uint32_t drain_bar = bar0 + 8u * 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t num_tiles = a.tiles_m * a.tiles_n * a.batch;
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(threads_for(UW), 1) gemm_tc_kernel(const __gri
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < 8; ++s) {
             mbar_init(pk_full(s), 1);
             mbar_init(pk_empty(s), kUnpackWarps);
         }
@@ -460,6 +461,36 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
         if (v == 0) return launch<MODE_I4, 256, 4, 4, 2>(A, B, a, st, cache_maps);
         if (v == 2) return launch<MODE_I4, 256, 8, 4, 2>(A, B, a, st, cache_maps);
         return launch<MODE_I4, 256, 8, 3, 3>(A, B, a, st, cache_maps);
+    }
+    if ((mode == MODE_A8B4 || mode == MODE_I4) && a.tiles_m == 1) {
+        // At most 128 tokens: every tile streams its own block of W exactly once and there is one row of
+        // tiles, so 256-wide tiles (pairs or not) would leave SMs idle and take two rounds on the others
+        // (4096 -> 22016 at 64 tokens: 36.8 us). Narrow tiles give (nearly) every SM exactly one; choose the
+        // width that minimises the bytes the busiest SM streams, ties to the wider tile (fewer re-reads of
+        // the activations). Measured 23.2 us for that layer; a packed ring of 256-byte-per-row boxes, 4 or
+        // 12 unpack warps and a deeper or shallower operand ring all measured the same or worse.
+        const uint32_t sms = (uint32_t)sm_count();
+        uint32_t best_bn = 0;
+        uint64_t best = ~0ull;
+        for (uint32_t bn : {160u, 128u, 96u, 64u}) {
+            const uint64_t rounds = ((uint64_t)cdiv(N, bn) * batch + sms - 1) / sms;
+            if (rounds * bn < best) { best = rounds * bn; best_bn = bn; }
+        }
+        a.tiles_n = cdiv(N, best_bn);
+        if (mode == MODE_I4) {   // packed activations (the reference's format): both operands unpacked in the CTA
+            switch (best_bn) {
+                case 160: return launch<MODE_I4, 160, 8, 4, 3>(A, B, a, st, cache_maps);
+                case 128: return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
+                case 96: return launch<MODE_I4, 96, 8, 4, 4>(A, B, a, st, cache_maps);
+                default: return launch<MODE_I4, 64, 8, 4, 4>(A, B, a, st, cache_maps);
+            }
+        }
+        switch (best_bn) {
+            case 160: return launch<MODE_A8B4, 160, 8, 8, 3>(A, B, a, st, cache_maps);
+            case 128: return launch<MODE_A8B4, 128, 8, 8, 4>(A, B, a, st, cache_maps);
+            case 96: return launch<MODE_A8B4, 96, 8, 8, 4>(A, B, a, st, cache_maps);
+            default: return launch<MODE_A8B4, 64, 8, 8, 4>(A, B, a, st, cache_maps);
+        }
     }
     if (mode == MODE_A8B4) {
         if (pair_ok) {

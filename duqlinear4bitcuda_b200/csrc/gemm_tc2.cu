@@ -33,6 +33,9 @@ int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t b
 
 namespace tc2 {
 
+#ifndef DUQ4_TC2_NUP
+#define DUQ4_TC2_NUP 5   // operand ring depth for int8 activations (build-time knob for experiments)
+#endif
 #ifndef DUQ4_TC2_NPK
 #define DUQ4_TC2_NPK 5   // packed-W ring depth for int8 activations (build-time knob for experiments)
 #endif
@@ -65,7 +68,7 @@ struct Cfg2 {
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
     static constexpr int NPK = GU ? (APK ? 3 : 5) : (APK ? 4 : DUQ4_TC2_NPK);
-    static constexpr int NUP = (APK || GU) ? 4 : 5;
+    static constexpr int NUP = (APK || GU) ? 4 : DUQ4_TC2_NUP;
     static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
     static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");

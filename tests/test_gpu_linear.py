@@ -325,7 +325,9 @@ def test_full_size_property_prefill(env):
 
 
 @pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
-@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (130, 264, 192), (512, 1024, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (130, 264, 192), (512, 1024, 2048),
+                                   # up to 128 tokens: narrow-tile launches (tile width picked by N: 160 / 128 / 96 / 64)
+                                   (17, 22016, 256), (64, 1000, 1088), (100, 20000, 192), (128, 4104, 448), (33, 12288, 320)])
 def test_preunpacked_activations_match_packed_path(env, mode, M, N, K):
     """duq4_quantize_fused_i8 + duq4_linear_w4a4_preunpacked give the scales and outputs of
     duq4_quantize_*_fused + duq4_linear_w4a4, and the int32 accumulators of the oracle."""
