@@ -389,8 +389,8 @@ def run_profile_case(args):
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         for _ in range(4):
             L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
-    elif args.profile_case == "decode":
-        M, N, K = 1, 22016, 4096
+    elif args.profile_case in ("decode", "decode16"):
+        M, N, K = (1 if args.profile_case == "decode" else 16), 22016, 4096
         W = torch.randint(0, 256, (8, N, K // 2), dtype=torch.uint8, device=dev)  # 8 x 45 MB: cold in L2
         qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev)
         sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
@@ -613,7 +613,7 @@ def main():
                     help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "quantize", "silu", "skinny"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "decode16", "quantize", "silu", "skinny"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
