@@ -161,7 +161,8 @@ __device__ __forceinline__ uint32_t code2_fast(uint32_t w, float rcp, __half2 z)
         const __half2 c = __hmin2(__hmax2(__hadd2(q, z), __float2half2_rn(0.f)), __float2half2_rn(15.f));
         t = __hadd2(c, __float2half2_rn(1024.f));            // 0x6400 + code
     }
-    return *reinterpret_cast<const uint32_t *>(&t) & 0x000F000Fu;
+    // each half is 0x6400 (or 0x6600) + code: the code is the low BYTE of the half, the high byte is constant
+    return *reinterpret_cast<const uint32_t *>(&t);
 }
 
 // 8 halves -> 8 nibbles, low nibble first. col0 >= 16 for the dual schemes (set 2 only).
@@ -172,10 +173,11 @@ __device__ __forceinline__ uint32_t code8_fast(const uint4 &v, const FastQ &f) {
     const __half2 z = dual ? f.z2 : f.z1;
     const uint32_t a = code2_fast<MODE>(v.x, rcp, z), b = code2_fast<MODE>(v.y, rcp, z);
     const uint32_t c = code2_fast<MODE>(v.z, rcp, z), d = code2_fast<MODE>(v.w, rcp, z);
-    // word -> byte: element 0 in bits 0..3, element 1 (bits 16..19) moved to bits 4..7
-    const uint32_t b0 = (a | (a >> 12)) & 0xFFu, b1 = (b | (b >> 12)) & 0xFFu;
-    const uint32_t b2 = (c | (c >> 12)) & 0xFFu, b3 = (d | (d >> 12)) & 0xFFu;
-    uint32_t out = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    // Each word holds its two codes in bytes 0 and 2. Gather the four code bytes of two words with one byte
+    // permute ([c0, c1, c2, c3], one nibble each), fold odd bytes onto even ones (x | x >> 4 puts c1 into the
+    // high nibble of byte 0 and c3 into that of byte 2), and gather the four finished bytes of the two halves.
+    const uint32_t ab = __byte_perm(a, b, 0x6420), cd = __byte_perm(c, d, 0x6420);
+    uint32_t out = __byte_perm(ab | (ab >> 4), cd | (cd >> 4), 0x6420);
     if (MODE == QSYM || MODE == QSYM_DUAL) out ^= 0x88888888u;   // (code + 8) -> two's complement nibble
     return out;
 }
