@@ -194,14 +194,18 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
             qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=device)
             sa = (torch.rand(M, device=device) * 0.1 + 0.01).to(torch.float16)
             y = torch.empty((M, N), dtype=torch.float16, device=device)
-            epi = L.make_epilogue("sym", sa, None, sw)
-
+            # one epilogue per layer: each names the NEXT layer's weights (L2 prefetch hint), as a model
+            # runner that knows its layer order would
+            epis = []
+            for c in range(ncopy):
+                epis.append(L.make_epilogue("sym", sa, None, sw, next_weights=None if os.environ.get("DUQ4_BENCH_NO_HINT")
+                                            else W[(c + 1) % ncopy]))
             passes = -(-100 // ncopy)   # at least 100 layer invocations per graph replay
 
             def body():
                 for _ in range(passes):
                     for c in range(ncopy):
-                        L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi),
+                        L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epis[c]),
                                L.ptr(y), None, L.current_stream())
 
             s = torch.cuda.Stream()

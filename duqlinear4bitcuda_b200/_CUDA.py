@@ -282,11 +282,12 @@ def asym_dequant_hprec(q, scale_row, zeros_row, scale_col, zeros_col, bits):
 
 # ---- fused linear (new) -------------------------------------------------------------------
 def linear_w4a4(mode, A, W, scale_row, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
-                zeros_col_2=None, bias=None, col_offset=0, out=None, return_acc=False):
+                zeros_col_2=None, bias=None, col_offset=0, out=None, return_acc=False, next_weights=None):
     """(new) fp16 [M,N] = dequant_mode(A [M,K/2] . W [N,K/2]^T) (+ bias): GEMM, dequant and bias in
     one kernel; results identical to matmul -> *_dequant -> `+ bias`. `mode` is one of
     "sym", "sym_dual", "asym", "asym_dual". `out` may be a column slice view of a wider
-    row-major buffer (its row stride is honoured)."""
+    row-major buffer (its row stride is honoured). `next_weights`: the packed weights of the layer
+    that follows on this stream -- a hint that lets the small-M kernels warm L2 with them."""
     _check("linear_w4a4", A=A, W=W, scale_row=scale_row, zeros_row=zeros_row, scale_col_1=scale_col_1,
            zeros_col_1=zeros_col_1, scale_col_2=scale_col_2, zeros_col_2=zeros_col_2, bias=bias)
     M, N, K = A.size(0), W.size(0), A.size(1) * 2
@@ -299,7 +300,7 @@ def linear_w4a4(mode, A, W, scale_row, zeros_row=None, scale_col_1=None, zeros_c
         raise RuntimeError("linear_w4a4: out must be fp16 [M,N] with unit column stride")
     acc = torch.empty((M, N), dtype=torch.int32, device=A.device) if return_acc else None
     epi = _L.make_epilogue(mode, scale_row, zeros_row, scale_col_1, zeros_col_1, scale_col_2, zeros_col_2, bias,
-                           col_offset, out.stride(0) if M > 1 else max(out.stride(0), N))
+                           col_offset, out.stride(0) if M > 1 else max(out.stride(0), N), next_weights=next_weights)
     _run("duq4_linear_w4a4", A, _p(A), _p(W), M, N, K, ctypes.byref(epi), _p(out), _p(acc))
     return (out, acc) if return_acc else out
 

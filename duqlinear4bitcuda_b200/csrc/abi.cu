@@ -46,6 +46,8 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
         if (!e->out_peers[i]) return DUQ4_ERR_NULL;
         p->peers[i] = (__half *)e->out_peers[i];
     }
+    p->next_w = (const uint8_t *)e->next_weights;
+    p->next_w_bytes = e->next_weights ? e->next_weights_bytes : 0;
     if (e->mode == DUQ4_MODE_NONE) return DUQ4_OK;
     const bool asym = e->mode == DUQ4_MODE_ASYM || e->mode == DUQ4_MODE_ASYM_DUAL;
     const bool dual = e->mode == DUQ4_MODE_SYM_DUAL || e->mode == DUQ4_MODE_ASYM_DUAL;

@@ -62,6 +62,9 @@ struct EpiParams {
     // own buffer included) instead of the single `out` pointer.
     uint32_t n_peers;
     __half *peers[DUQ4_MAX_OUT_PEERS];
+    // L2 prefetch hint (small-M kernels): packed weights of the next launch on the stream
+    const uint8_t *next_w;
+    uint64_t next_w_bytes;
 };
 
 // Output bases of a launch: the peer list if there is one, else the plain `out` pointer.

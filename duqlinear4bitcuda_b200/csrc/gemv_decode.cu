@@ -34,6 +34,28 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 
 // Programmatic dependent launch (no-ops unless the launch carries the attribute).
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// L2 prefetch of [ptr, ptr + bytes): ptr 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void l2_prefetch_bulk(const void *ptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
+// Next-layer hint: the CTAs of this launch together ask L2 for a window of the next launch's packed
+// weights, one contiguous slice per CTA, each when it starts. The window skips the first 12 MiB -- the rows
+// the next launch's first wave of CTAs fetches by itself while this launch drains (programmatic dependent
+// launch) -- and covers the following 18 MiB, which its later CTAs would otherwise request from a memory
+// pipe that has just run dry. Measured on 4096->12288 / 4096->22016 at one token: 6.4 -> 5.7 us and
+// 10.6 -> 9.9 us per layer; windows of 8..32 MiB starting at 8..20 MiB all lie within 4 % of that.
+constexpr uint64_t kNextSkip = 12ull << 20, kNextLen = 18ull << 20;
+__device__ __forceinline__ void prefetch_next_weights(const EpiParams &p, uint32_t cta, uint32_t ncta) {
+    if (!p.next_w || p.next_w_bytes <= kNextSkip || (reinterpret_cast<uintptr_t>(p.next_w) & 15) != 0) return;
+    uint64_t total = p.next_w_bytes - kNextSkip;
+    if (total > kNextLen) total = kNextLen;
+    const uint64_t per = ((total + ncta - 1) / ncta + 127) & ~127ull;
+    const uint64_t off = (uint64_t)cta * per;
+    if (off >= total) return;
+    uint64_t n = total - off < per ? total - off : per;
+    n &= ~15ull;
+    if (n) l2_prefetch_bulk(p.next_w + kNextSkip + off, (uint32_t)n);
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
@@ -125,6 +147,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
             }
         }
         if (!waited) {
+            if (threadIdx.x == 0 && blockIdx.y == 0) prefetch_next_weights(p, blockIdx.x, gridDim.x);
             pdl_wait();
             waited = true;
         }
@@ -250,9 +273,14 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            bool hinted = false;
             for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
                 const uint32_t b = u / blocks_per_b, row0 = (u % blocks_per_b) * S::kRows;
                 for (uint32_t ks = 0; ks < nks; ++ks, ++it) {
+                    if (!hinted && it == (uint32_t)S::kStages) {   // once this CTA's own ring is full
+                        prefetch_next_weights(p0, blockIdx.x, gridDim.x);
+                        hinted = true;
+                    }
                     const uint32_t s = it % S::kStages, ph = (it / S::kStages) & 1;
                     if (ok) ok = mbar_wait(empty(s), ph ^ 1, abortp, &g_gemv_status, 1);
                     if (!ok) continue;
@@ -565,6 +593,7 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
     pdl_launch_dependents();
     GemvBuf<TH, U> b0, b1;
     if (total > 0) issue_w(b0, 0);   // weights are parameters: fetched before the previous grid has finished
+    if (threadIdx.x == 0) prefetch_next_weights(p0, blockIdx.x, gridDim.x);
     pdl_wait();                      // activations / outputs belong to the stream's earlier work
     if (total > 0) issue_a(b0, 0);
     for (uint32_t f = 0; f < total; f += 2) {

@@ -29,6 +29,8 @@ class Epilogue(ctypes.Structure):
         ("ldo", ctypes.c_uint32),
         ("n_out_peers", ctypes.c_uint32),
         ("out_peers", ctypes.c_void_p * 8),
+        ("next_weights", ctypes.c_void_p),
+        ("next_weights_bytes", ctypes.c_uint64),
     ]
 
 
@@ -114,7 +116,9 @@ def current_stream():
 
 
 def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
-                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None):
+                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None):
+    """Fill a duq4_epilogue. `next_weights`: packed weight tensor of the layer that runs next on the
+    stream (L2 prefetch hint of the small-M kernels; never read or written by this launch)."""
     e = Epilogue()
     e.mode = MODES[mode] if isinstance(mode, str) else int(mode)
     e.col_offset = col_offset
@@ -129,4 +133,7 @@ def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_
         e.n_out_peers = len(out_peers)
         for i, a in enumerate(out_peers):
             e.out_peers[i] = int(a)
+    if next_weights is not None:
+        e.next_weights = next_weights.data_ptr()
+        e.next_weights_bytes = next_weights.numel() * next_weights.element_size()
     return e

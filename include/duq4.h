@@ -215,6 +215,13 @@ typedef struct duq4_epilogue {
      * synchronises the ranks before anyone reads the gathered result. */
     uint32_t n_out_peers;
     void *out_peers[8];
+    /* Optional hint for chains of small-M (M <= 16) layers: device pointer and size of the packed
+     * weights the NEXT launch on this stream will read. The kernel asks the L2 cache to fetch part of
+     * that range while its own last CTAs drain, so the next layer does not start on a cold memory
+     * pipe. Purely a performance hint: the bytes are never read or written by this launch, results
+     * do not depend on it. NULL / 0 = none. Ignored by the tensor-core kernels. */
+    const void *next_weights;
+    uint64_t next_weights_bytes;
 } duq4_epilogue;
 
 /* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches

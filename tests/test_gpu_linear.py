@@ -436,3 +436,24 @@ def test_pair_kernel_batched(env):
     torch.cuda.synchronize()
     assert tc_status(L) == 0
     assert np.array_equal(C.cpu().numpy(), o.batch_matmul_4bit(qa, qw))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 12288, 4096), (16, 12288, 4096), (4, 4096, 11008)])
+def test_next_weights_hint_changes_nothing_but_timing(env, M, N, K):
+    """The L2 prefetch hint for the following layer (duq4_epilogue.next_weights) is never dereferenced by
+    the arithmetic: outputs with a hint (aligned, misaligned, shorter than the skipped head, huge) equal
+    the outputs without one, on every small-M kernel."""
+    torch, L, o = env
+    qa = dev(torch, U.rand_codes(M, K, 1)); qw = dev(torch, U.rand_codes(N, K, 2))
+    sr = dev(torch, U.rand_scales(M, 3)); sc = dev(torch, U.rand_scales(N, 4))
+    nxt = torch.randint(0, 256, (40 << 20,), dtype=torch.uint8, device="cuda")
+    outs = []
+    for hint in (None, nxt, nxt[1:], nxt[: 1 << 20], nxt[16: (13 << 20) + 48]):
+        epi = L.make_epilogue("sym", sr, None, sc, next_weights=hint)
+        out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+        L.call("duq4_linear_w4a4", L.ptr(qa), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(out), None, L.current_stream())
+        torch.cuda.synchronize()
+        outs.append(out)
+    for x in outs[1:]:
+        assert torch.equal(x.view(torch.int16), outs[0].view(torch.int16))
+    assert torch.equal(nxt[:64].cpu(), nxt[:64].cpu())   # the hinted buffer is untouched (still readable)
