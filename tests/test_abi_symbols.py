@@ -27,3 +27,54 @@ def test_metadata_calls_without_gpu():
     assert b"sm_100a" in L.cdll.duq4_version()
     assert L.cdll.duq4_error_string(-4).startswith(b"workspace")
     assert L.cdll.duq4_linear_from_fp16_workspace_bytes(16, 4096) == 16 * 2048 + 4 * 256
+
+
+def test_arguments_are_rejected_before_any_launch():
+    """Status codes for bad arguments come back without a GPU: every entry point validates pointers,
+    modes, shapes and workspaces before it touches the CUDA runtime. Pointers below are fake non-NULL
+    addresses; a call that got as far as a launch would fail differently (positive cudaError_t)."""
+    import ctypes
+    import duqlinear4bitcuda_b200.lib as L
+    c = L.cdll
+    P = ctypes.c_void_p(0x1000)          # "some device pointer"
+    NULL = None
+    e = L.Epilogue()
+    e.mode = L.MODE_SYM
+    e.scale_row = 0x1000
+    e.scale_col_1 = 0x1000
+    ep = ctypes.byref(e)
+    # NULL operands
+    assert c.duq4_sym_quant(NULL, P, 4, 64, 32, P, NULL) == -1
+    assert c.duq4_matmul_4bit(P, NULL, 4, 8, 64, P, NULL) == -1
+    assert c.duq4_linear_w4a4(NULL, P, 4, 8, 64, ep, P, NULL, NULL) == -1
+    # K must be a multiple of 64
+    assert c.duq4_matmul_4bit(P, P, 4, 8, 100, P, NULL) == -2
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 4, 8, 100, L.MODE_SYM, 1.0, ep, P, P, 1 << 20, NULL) == -2
+    # unknown modes; the dual schemes are refused by the gate/up entry point
+    bad = L.Epilogue(); bad.mode = 99
+    assert c.duq4_linear_w4a4(P, P, 4, 8, 64, ctypes.byref(bad), P, NULL, NULL) == -3
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 4, 8, 64, 9, 1.0, ep, P, P, 1 << 20, NULL) == -3
+    dual = L.Epilogue(); dual.mode = L.MODE_SYM_DUAL; dual.scale_row = 0x1000; dual.scale_col_1 = 0x1000; dual.scale_col_2 = 0x1000
+    assert c.duq4_linear_w4a4_gate_up_silu(P, 1, P, 4, 8, 64, ctypes.byref(dual), P, NULL) == -3
+    # an asymmetric epilogue needs zero-points
+    asym = L.Epilogue(); asym.mode = L.MODE_ASYM; asym.scale_row = 0x1000; asym.scale_col_1 = 0x1000
+    assert c.duq4_linear_w4a4(P, P, 4, 8, 64, ctypes.byref(asym), P, NULL, NULL) == -1
+    # workspaces: missing, too small, misaligned
+    need = c.duq4_linear_from_fp16_workspace_bytes(4, 64)
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 4, 8, 64, L.MODE_SYM, 1.0, ep, P, NULL, need, NULL) == -4
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 4, 8, 64, L.MODE_SYM, 1.0, ep, P, P, need - 1, NULL) == -4
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 4, 8, 64, L.MODE_SYM, 1.0, ep, P, ctypes.c_void_p(0x1010), need, NULL) == -4
+    # built-in scratch: problems that do not fit are refused
+    assert c.duq4_linear_w4a4_from_fp16_static(P, P, 4096, 8, 8192, L.MODE_SYM, 1.0, ep, P, NULL) == -8
+    # host-buffer entry point: peers are not allowed, staging is checked
+    peers = L.Epilogue(); peers.mode = L.MODE_SYM; peers.scale_col_1 = 0x1000; peers.n_out_peers = 1; peers.out_peers[0] = 0x1000
+    assert c.duq4_linear_w4a4_from_fp16_host(P, P, 300, 8, 64, L.MODE_SYM, 1.0, ctypes.byref(peers), P, 0, P, 1 << 30, NULL) == -3
+    assert c.duq4_linear_w4a4_from_fp16_host(P, P, 300, 8, 64, L.MODE_SYM, 1.0, ep, P, 0, NULL, 1 << 30, NULL) == -4
+    # empty problems are fine and do nothing
+    assert c.duq4_linear_w4a4_from_fp16(P, P, 0, 8, 64, L.MODE_SYM, 1.0, ep, P, P, 1 << 20, NULL) == 0
+    # sizes of the host-buffer staging area: device copies of x and of the result + one chunk's quantizer scratch
+    M, N, K = 4096, 28672, 8192
+    chunk = 256   # a sixteenth of M, already a multiple of 256
+    assert c.duq4_linear_host_staging_bytes(M, N, K, 0) == M * K * 2 + M * N * 2 + c.duq4_linear_from_fp16_workspace_bytes(chunk, K)
+    for code in range(-8, 0):
+        assert len(c.duq4_error_string(code)) > 3
