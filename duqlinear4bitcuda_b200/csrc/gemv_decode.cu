@@ -647,7 +647,10 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
     //    needs more than one batch of loads per warp (long K) or for > 8 tokens; one-shot otherwise.
     const bool big_n = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
     const bool long_k = (K / 2 / 64) > (uint32_t)(kGemvWarps * 4);
-    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && M > 8 && big_n);
+    // ... and for any token count on the largest layers (>= 4 32-row blocks per SM; 4096->22016 at M=1 with the
+    //    next-layer hint: 9.8 us TMA-streamed vs 10.1 us one-shot, while 4096->12288 is 6.15 vs 5.8)
+    const bool huge_n = (uint64_t)cdiv(N, 32) * batch >= 4ull * sms;
+    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && big_n && (M > 8 || huge_n));
     const bool persist = force >= 0 ? force == 3 : (!use_tma && (long_k || M > 8));
     if (persist) {
         if (M <= 8) return launch_persist<1, 4>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
