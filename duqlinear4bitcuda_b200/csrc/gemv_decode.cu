@@ -231,7 +231,7 @@ template <int R>
 struct GemvSmem {
     static constexpr int kRows = 16 * R;
     static constexpr int kStageBytes = kRows * kStageKBytes;
-    static constexpr int kStages = R == 2 ? 5 : 8;   // 160 KiB / 128 KiB of weights in flight per SM
+    static constexpr int kStages = R == 2 ? 4 : 8;   // 128 KiB of weights in flight per SM (measured: 3 / 4 / 5 / 6 stages of 32 KiB -> 9.8 / 9.6 / 9.8 / 10.4 us on 4096->22016, M=1)
     static constexpr int kRedInts = 2 * kGemvWarps * 16 * (kRows + 1);
     static constexpr int kBytes = 1024 + kStages * kStageBytes + kRedInts * 4 + 2 * kStages * 8 + 16;
 };
