@@ -230,7 +230,9 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
             out.append({"K": K, "N": N, "M": M, "us_per_layer": round(us, 3), "weight_GBps": round(gbs, 1),
                         "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
                         "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4), "cold_weight_buffers": ncopy,
-                        "layers_per_graph": ncopy * passes})
+                        "layers_per_graph": ncopy * passes,
+                        "static_weights_overlap": not os.environ.get("DUQ4_BENCH_NO_PDL"),
+                        "next_layer_hint": not os.environ.get("DUQ4_BENCH_NO_HINT")})
             del g
         del W
     L.cdll.duq4_set_static_weights(prev)
