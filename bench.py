@@ -508,20 +508,26 @@ def run_ours(args):
             L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(qw), M, N, K, L.MODE_SYM, 1.0,
                    ctypes.byref(epi_e2e), out_host.data_ptr(), 0, L.ptr(staging), staging_bytes, st())
             return
-        x.copy_(x_host, non_blocking=True)
+        # N > 1: the job has ONE host input and ONE host result. Rank 0 uploads the activations and the
+        # ranks receive them over NVLink (broadcast); every rank computes its column block and the blocks are
+        # gathered on the devices; rank 0 alone brings the [M, N] result back to its host buffer.
+        if rank == 0:
+            x.copy_(x_host, non_blocking=True)
+        dist.broadcast(x, src=0)
         if peer is not None:
             peer.barrier()
             L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_f_e2e),
                    None, L.ptr(ws), ws_bytes, st())
             peer.barrier()
-            out_host.copy_(peer.buf, non_blocking=True)
+            if rank == 0:
+                out_host.copy_(peer.buf, non_blocking=True)
             return
         L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_e2e),
                L.ptr(out_shard), L.ptr(ws), ws_bytes, st())
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
-            out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
-        out_host.copy_(out_full, non_blocking=True)
+        dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
+        out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
+        if rank == 0:
+            out_host.copy_(out_full, non_blocking=True)
 
     def barrier():
         if world > 1:
@@ -580,7 +586,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                     "api": ("duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, copies pipelined with the arithmetic over row chunks)"
                             if world == 1 else
-                            "duq4_linear_w4a4_from_fp16 (C ABI) between a copy from pinned host memory and a copy of the gathered result back to it")},
+                            "rank 0 uploads the activations from pinned host memory, NCCL broadcast to the ranks, duq4_linear_w4a4_from_fp16 (C ABI) per rank with the gather on the devices, rank 0 copies the [M, N] result back to pinned host memory")},
             "gpu_launches": args.steps * 2,
             "roofline": {"kernel": "gemm_tc2_kernel (CTA pairs, 256x256x128 tiles, tcgen05.mma.cta_group::2.kind::i8; A int8 pre-unpacked by the quantizer, W int4 unpacked in smem)" if (M >= 256 * 8 and Ns >= 256 * 8) else "gemm_tc_kernel<MODE_A8B4> (tcgen05.mma kind::i8)", "bound": "tensor",
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
