@@ -397,7 +397,7 @@ static int launch(const void *A, const void *B, const Args &args, cudaStream_t s
     }
     const bool a_packed = MODE == MODE_I4, b_packed = MODE != MODE_I8;
     CUtensorMap ma, mb;
-    int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma, cache_maps);
+    int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.a_rows > args.M ? args.a_rows : args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma, cache_maps);
     if (rc) return rc;
     rc = get_map(B, b_packed ? args.K / 2 : args.K, args.N, args.batch, b_packed ? BK / 2 : BK, BN, !b_packed, &mb, cache_maps);
     if (rc) return rc;
@@ -434,13 +434,16 @@ static bool pair_tiles() {
 }
 
 // A [batch,M,K] x B [batch,N,K]^T. mode: tc::MODE_I8 / MODE_I4 / MODE_A8B4 (see above).
+// a_rows: rows the A buffer really has (0 = M). A caller that owns a larger buffer lets the tensor map cover it, so
+// that the A tile of a launch with few tokens is read in-bounds instead of zero-filled (batch must be 1 then).
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
+                   const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps, uint32_t a_rows) {
     using namespace tc;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (mode != MODE_I8 && K >= 131072u) return DUQ4_ERR_SHAPE;  // 256x-scaled accumulators must fit int32
     Args a{};
     a.M = M; a.N = N; a.K = K; a.batch = batch;
+    a.a_rows = (batch == 1 && a_rows > M) ? a_rows : M;
     a.epi = p;
     a.out = (__half *)out;
     a.acc_out = acc_out;

@@ -79,6 +79,7 @@ struct Args {
     uint32_t M, N, K, batch;  // K in elements
     uint32_t tiles_m, tiles_n;
     uint32_t bn;              // CTA-pair kernel only: accumulator columns per tile (multiple of 32, <= 256)
+    uint32_t a_rows;          // rows of the A buffer the tensor map may read (>= M; the extra rows are never stored)
     uint32_t gate_up;         // CTA-pair kernel only: 0, or I = width of a SiLU-gated gate/up projection (W has 2*I rows)
     EpiParams epi;
     __half *out;

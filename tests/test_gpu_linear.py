@@ -216,7 +216,7 @@ def test_batched(env, B, M, N, K):
     assert U.f16_equal_nan(out.cpu().numpy(), o.asym_batch_dequant(want, sr, zr, sc, zc))
 
 
-@pytest.mark.parametrize("M", [4, 300])
+@pytest.mark.parametrize("M", [4, 20, 31, 300])   # 20, 31: the int8 code buffer is padded to 32 rows
 @pytest.mark.parametrize("mode", ["sym", "asym"])
 def test_linear_from_fp16(env, M, mode):
     """quantize -> GEMM -> dequant in one call, scratch supplied by the caller."""
