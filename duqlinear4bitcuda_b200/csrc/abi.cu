@@ -7,7 +7,8 @@
 
 namespace duq4 {
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
+                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
+int tma_map_cache_entries();
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true,
                    uint32_t a_rows = 0);
@@ -16,7 +17,7 @@ int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
 int tc2_status_read(int32_t *out);
-extern int g_static_weights;
+extern std::atomic<int> g_static_weights;
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
                             void *z1, void *s2, void *z2, cudaStream_t st, bool out8);
 
@@ -60,14 +61,14 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
 }
 
 static int linear_dispatch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                           const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+                           const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true) {
     if (!A || !W) return DUQ4_ERR_NULL;
     if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
     if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0 || batch == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
-    if (M <= kSmallM) return gemv_w4a4_launch(A, W, M, N, K, batch, p, out, acc_out, st);
-    return gemm_tc_launch(1 /* both operands packed int4 */, A, W, M, N, K, batch, p, out, acc_out, st);
+    if (M <= kSmallM) return gemv_w4a4_launch(A, W, M, N, K, batch, p, out, acc_out, st, cache_maps);
+    return gemm_tc_launch(1 /* both operands packed int4 */, A, W, M, N, K, batch, p, out, acc_out, st, cache_maps);
 }
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -97,10 +98,10 @@ const char *duq4_error_string(int status) {
 
 int duq4_dual_quant_col_k(void) { return DUQ4_QUANT_COL_K; }
 
+int duq4_tensor_map_cache_entries(void) { return tma_map_cache_entries(); }
+
 int duq4_set_static_weights(int on) {
-    int prev = g_static_weights;
-    g_static_weights = on ? 1 : 0;
-    return prev;
+    return g_static_weights.exchange(on ? 1 : 0);
 }
 
 int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
@@ -274,8 +275,9 @@ int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t 
     if (rc) return rc;
     p.s_row = (const __half *)s1;
     p.z_row = epi_asym ? (const __half *)z1 : nullptr;
-    if (small) return linear_dispatch(ws, W, M, N, K, 1, p, out, nullptr, st);
-    // tensor maps are encoded on the stack for this call: no cache insertion, no host heap use
+    // tensor maps are encoded on the stack for this call (cache_maps = false on every path: small-M TMA kernel,
+    // single-CTA and CTA-pair tensor-core kernels): no cache lookup or insertion, no host heap use
+    if (small) return linear_dispatch(ws, W, M, N, K, 1, p, out, nullptr, st, false);
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, ws, W, M, N, K, 1, p, out, nullptr, st, false, code_rows(M));
 }
 

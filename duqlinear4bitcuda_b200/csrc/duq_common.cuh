@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/duq4.h"
 
 namespace duq4 {
@@ -31,6 +34,37 @@ inline int current_device_slot() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
     return dev;
+}
+
+// Once-per-device host set-up that any number of host threads may reach at the same time (function
+// attributes, occupancy queries): the first caller on a device runs `f` under a lock, later callers see
+// the published flag. `f` returns 0 on success; a failure is returned and the set-up retried next time.
+struct DeviceOnce {
+    std::mutex mu;
+    std::atomic<int> done[64];
+    DeviceOnce() { for (auto &d : done) d.store(0, std::memory_order_relaxed); }
+    template <class F>
+    int run(int dev, F &&f) {
+        if (done[dev].load(std::memory_order_acquire)) return 0;
+        std::lock_guard<std::mutex> g(mu);
+        if (done[dev].load(std::memory_order_relaxed)) return 0;
+        const int rc = f();
+        if (rc == 0) done[dev].store(1, std::memory_order_release);
+        return rc;
+    }
+};
+
+// SM count of the device that is current (queried once per device; 148 if the query fails).
+inline int sm_count_current_device() {
+    static std::atomic<int> n[64];   // zero-initialised
+    const int dev = current_device_slot();
+    if (dev < 0) return 148;
+    int v = n[dev].load(std::memory_order_relaxed);
+    if (v <= 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
 }
 
 __device__ __forceinline__ int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }

@@ -333,6 +333,10 @@ static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t bat
                    bool swizzle128, CUtensorMap *out, bool use_cache = true) {
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    if (!out) {   // diagnostic query: number of cached descriptors
+        std::lock_guard<std::mutex> g(mu);
+        return (int)cache.size();
+    }
     MapKey key{ptr, kbytes, rows, batch, box_k, box_rows, swizzle128 ? 1u : 0u};
     if (use_cache) {
         std::lock_guard<std::mutex> g(mu);
@@ -364,37 +368,31 @@ static int get_map(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t bat
 
 }  // namespace tc
 
+// use_cache = false: the descriptor is encoded into *out for this call only (nothing is looked up or kept,
+// so the host heap is not touched).
 int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
-                      bool swizzle128, CUtensorMap *out) {
-    return tc::get_map(ptr, kbytes, rows, batch, box_k, box_rows, swizzle128, out, true);
+                      bool swizzle128, CUtensorMap *out, bool use_cache) {
+    return tc::get_map(ptr, kbytes, rows, batch, box_k, box_rows, swizzle128, out, use_cache);
 }
+
+// Entries currently held by the descriptor cache (diagnostic).
+int tma_map_cache_entries() { return tc::get_map(nullptr, 0, 0, 0, 0, 0, false, nullptr, true); }
 
 namespace tc {
 
-static int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
+static int sm_count() { return sm_count_current_device(); }
 
 template <int MODE, int BN, int UW, int NPK_, int NUP_>
 static int launch(const void *A, const void *B, const Args &args, cudaStream_t st, bool cache_maps) {
     using C = Cfg<MODE, BN, UW, NPK_, NUP_>;
-    static bool attr_done[64] = {};
+    static DeviceOnce once;
     const int dev = current_device_slot();
     if (dev < 0) return DUQ4_ERR_DEVICE;
-    bool &attr_set = attr_done[dev];
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, UW, NPK_, NUP_>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    int orc = once.run(dev, [] {
+        return (int)cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, UW, NPK_, NUP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmem);
+    });
+    if (orc) return orc;
     const bool a_packed = MODE == MODE_I4, b_packed = MODE != MODE_I8;
     CUtensorMap ma, mb;
     int rc = get_map(A, a_packed ? args.K / 2 : args.K, args.a_rows > args.M ? args.a_rows : args.M, args.batch, a_packed ? BK / 2 : BK, BM, !a_packed, &ma, cache_maps);
@@ -409,28 +407,26 @@ static int launch(const void *A, const void *B, const Args &args, cudaStream_t s
 
 // Debug override of the pipeline shape (DUQ4_TC_VARIANT=0..2); unset = the tuned default.
 static int variant() {
-    static int v = -1;
-    if (v < 0) {
+    static const int v = [] {
         const char *e = getenv("DUQ4_TC_VARIANT");
-        v = e ? atoi(e) : 1;
-        if (v < 0 || v > 2) v = 1;
-    }
+        const int x = e ? atoi(e) : 1;
+        return (x < 0 || x > 2) ? 1 : x;
+    }();
     return v;
 }
 
 }  // namespace tc
 
 int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st);
+                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps);
 
 // CTA-pair tiles for large int4 problems: DUQ4_TC_PAIR=0/1 overrides the default (on).
 static bool pair_tiles() {
-    static int v = -1;
-    if (v < 0) {
+    static const bool v = [] {
         const char *e = getenv("DUQ4_TC_PAIR");
-        v = e ? (atoi(e) != 0) : 1;
-    }
-    return v != 0;
+        return e ? (atoi(e) != 0) : true;
+    }();
+    return v;
 }
 
 // A [batch,M,K] x B [batch,N,K]^T. mode: tc::MODE_I8 / MODE_I4 / MODE_A8B4 (see above).
@@ -457,7 +453,7 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     const bool pair_ok = pair_tiles() && (uint64_t)cdiv(M, 256) * cdiv(N, 256) * batch >= 60;
     if (mode == MODE_I4) {
         if (pair_ok) {
-            int rc = gemm_tc2_launch(true, A, B, M, N, K, batch, p, out, acc_out, st);
+            int rc = gemm_tc2_launch(true, A, B, M, N, K, batch, p, out, acc_out, st, cache_maps);
             if (rc != DUQ4_ERR_DEVICE) return rc;   // no CTA pairs on this device: single-CTA tiles below
         }
         if (!wide) return launch<MODE_I4, 128, 8, 4, 4>(A, B, a, st, cache_maps);
@@ -497,7 +493,7 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     }
     if (mode == MODE_A8B4) {
         if (pair_ok) {
-            int rc = gemm_tc2_launch(false, A, B, M, N, K, batch, p, out, acc_out, st);
+            int rc = gemm_tc2_launch(false, A, B, M, N, K, batch, p, out, acc_out, st, cache_maps);
             if (rc != DUQ4_ERR_DEVICE) return rc;   // no CTA pairs on this device: single-CTA tiles below
         }
         if (!wide) return launch<MODE_A8B4, 128, 8, 4, 4>(A, B, a, st, cache_maps);

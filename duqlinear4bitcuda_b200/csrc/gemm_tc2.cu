@@ -29,16 +29,9 @@ namespace duq4 {
 __device__ int g_tc2_status = 0;
 
 int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
-                     bool swizzle128, CUtensorMap *out);
+                     bool swizzle128, CUtensorMap *out, bool use_cache);
 
 namespace tc2 {
-
-#ifndef DUQ4_TC2_NUP
-#define DUQ4_TC2_NUP 5   // operand ring depth for int8 activations (build-time knob for experiments)
-#endif
-#ifndef DUQ4_TC2_NPK
-#define DUQ4_TC2_NPK 5   // packed-W ring depth for int8 activations (build-time knob for experiments)
-#endif
 
 using namespace ptx;
 using namespace tc;
@@ -67,8 +60,8 @@ struct Cfg2 {
     // (L2 / HBM latency) while a k-step of MMA work takes 0.3-0.4 us, so the packed ring has to
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
-    static constexpr int NPK = GU ? (APK ? 3 : 5) : (APK ? 4 : DUQ4_TC2_NPK);
-    static constexpr int NUP = (APK || GU) ? 4 : DUQ4_TC2_NUP;
+    static constexpr int NPK = GU ? (APK ? 3 : 5) : (APK ? 4 : 5);
+    static constexpr int NUP = (APK || GU) ? 4 : 5;
     static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
     static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
@@ -483,12 +476,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // M = 2048: 256 tiles = 3.46 rounds -> 296 tiles = exactly 4 rounds of cheaper tiles).
 // DUQ4_TC_BN pins a width (multiple of 32; tests and experiments).
 static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, uint32_t pairs) {
-    static int forced = -1;
-    if (forced < 0) {
+    static const int forced = [] {
         const char *e = getenv("DUQ4_TC_BN");
-        forced = e ? atoi(e) : 0;
-        if (forced < 32 || forced > 256 || forced % 32 != 0) forced = 0;
-    }
+        const int v = e ? atoi(e) : 0;
+        return (v < 32 || v > 256 || v % 32 != 0) ? 0 : v;
+    }();
     if (forced) return (uint32_t)forced;
     auto rounds = [&](uint32_t bn) { return ((uint64_t)tiles_m * cdiv(N, bn) * batch + pairs - 1) / pairs; };
     return rounds(224) <= rounds(256) ? 224u : 256u;
@@ -496,19 +488,17 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
 
 template <bool APK, bool GU = false>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
-                   void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0) {
+                   void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0, bool cache_maps = true) {
     using namespace tc2;
     constexpr int kSmem2 = Cfg2<APK, GU>::kSmem;
     auto *kernel = gemm_tc2_kernel<APK, GU>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
-    static int pairs_of[64];
-    static bool pairs_known[64] = {};
+    static DeviceOnce once;
+    static std::atomic<int> pairs_of[64];
     const int dev = current_device_slot();
     if (dev < 0) return DUQ4_ERR_DEVICE;
-    int &max_pairs = pairs_of[dev];
-    if (!pairs_known[dev]) {
-        pairs_known[dev] = true;
+    int orc = once.run(dev, [&] {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
         if (e != cudaSuccess) return (int)e;
         cudaLaunchConfig_t q = {};
@@ -528,8 +518,11 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
             (void)cudaGetLastError();
             n = 0;
         }
-        max_pairs = n;
-    }
+        pairs_of[dev].store(n, std::memory_order_relaxed);
+        return 0;
+    });
+    if (orc) return orc;
+    const int max_pairs = pairs_of[dev].load(std::memory_order_relaxed);
     if (max_pairs < 1) return DUQ4_ERR_DEVICE;
     tc::Args a{};
     a.M = M; a.N = N; a.K = K; a.batch = batch;
@@ -544,9 +537,10 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     a.bn = (gate_up || p.n_peers > 1) ? 256u : pick_tile_width(a.tiles_m, N, batch, (uint32_t)max_pairs);
     a.tiles_n = gate_up ? cdiv(N, 128) : cdiv(N, a.bn);
     CUtensorMap ma, mb;
-    int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma) : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma);
+    int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma, cache_maps)
+                 : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma, cache_maps);
     if (rc) return rc;
-    rc = tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb);
+    rc = tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb, cache_maps);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
     const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
@@ -574,9 +568,9 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
 // [batch, N, K/2]. Returns DUQ4_ERR_DEVICE when the device cannot co-schedule CTA pairs (the
 // caller then uses the single-CTA kernel).
 int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
-    return a_packed ? launch2<true>(A, B, M, N, K, batch, p, out, acc_out, st)
-                    : launch2<false>(A, B, M, N, K, batch, p, out, acc_out, st);
+                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
+    return a_packed ? launch2<true>(A, B, M, N, K, batch, p, out, acc_out, st, 0, cache_maps)
+                    : launch2<false>(A, B, M, N, K, batch, p, out, acc_out, st, 0, cache_maps);
 }
 
 // SiLU-gated gate/up projection: W packed [2*I, K/2] (gate rows, then up rows), per-channel vectors of

@@ -395,12 +395,12 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
 }
 
 int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t batch, uint32_t box_k, uint32_t box_rows,
-                     bool swizzle128, CUtensorMap *out);
+                     bool swizzle128, CUtensorMap *out, bool use_cache);
 
 // Set through duq4_set_static_weights(): the caller promises that weight tensors are not
 // written by earlier work of the same stream, which lets small-M kernels start fetching them
 // while the previous kernel is still finishing.
-int g_static_weights = 0;
+std::atomic<int> g_static_weights{0};
 
 template <int R, int TH>
 static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p,
@@ -413,7 +413,7 @@ static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M,
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_kernel<R, TH>, A, W, M, N, K, p, out, acc_out);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -424,19 +424,17 @@ static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M,
 
 template <int R, int TH>
 static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms) {
+                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms, bool cache_maps) {
     using S = GemvSmem<R>;
-    static bool attr_done[64] = {};
+    static DeviceOnce once;
     const int dev = current_device_slot();
     if (dev < 0) return DUQ4_ERR_DEVICE;
-    bool &attr_set = attr_done[dev];
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    int rc = once.run(dev, [] {
+        return (int)cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    });
+    if (rc) return rc;
     CUtensorMap mw;
-    int rc = tma_map_bytes_3d(W, K / 2, N, batch, 128, S::kRows, true, &mw);
+    rc = tma_map_bytes_3d(W, K / 2, N, batch, 128, S::kRows, true, &mw, cache_maps);
     if (rc) return rc;
     const uint32_t units = cdiv(N, S::kRows) * batch;
     const uint32_t grid = units < (uint32_t)sms ? units : (uint32_t)sms;
@@ -449,7 +447,7 @@ static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_tma_kernel<R, TH>, mw, A, M, N, K, batch, p, (__half *)out, acc_out);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -619,7 +617,7 @@ static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = g_static_weights ? 1 : 0;
+    cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_persist_kernel<TH, U>, A, W, M, N, K, batch, p, (__half *)out, acc_out);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -629,17 +627,13 @@ static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32
 }
 
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st) {
+                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) != 0) return DUQ4_ERR_ALIGN;
-    static int sms = 0, force = -1;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
+    const int sms = sm_count_current_device();
+    static const int force = [] {
         const char *e = getenv("DUQ4_GEMV_VARIANT");   // debug: 0 = one-shot register kernel, 1 = TMA-streamed kernel, 3 = persistent register kernel
-        force = e ? atoi(e) : -1;
-    }
+        return e ? atoi(e) : -1;
+    }();
     // Measured on B200 (cold weights, CUDA-graph chain of layers, us per layer; one-shot / persistent / TMA):
     //   4096->22016: M=1 10.9/10.8/10.4, M=16 16.9/15.6/14.3     4096->4096: M=1 2.9/2.9/3.7, M=16 4.8/4.1/5.0
     //   11008->4096: M=1 7.1/6.3/7.1,   M=16 10.0/8.2/9.8
@@ -658,10 +652,10 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
     }
     if (use_tma) {
         const bool two = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
-        if (M <= 8) return two ? launch_tma<2, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms)
-                               : launch_tma<1, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
-        return two ? launch_tma<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms)
-                   : launch_tma<1, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+        if (M <= 8) return two ? launch_tma<2, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps)
+                               : launch_tma<1, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps);
+        return two ? launch_tma<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps)
+                   : launch_tma<1, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps);
     }
     // Up to 8 tokens: 16-row CTAs (three per SM) -- more, smaller CTAs keep the weight stream smoother
     // across CTA boundaries than 32-row ones (4096->22016, M=1: 10.3 vs 10.8 us). 9..16 tokens: two row

@@ -42,15 +42,29 @@ int pipe_state(PipeState **out) {
     std::lock_guard<std::mutex> g(g_mu);
     PipeState &s = g_state[dev];
     if (!s.ready) {
-        if ((e = cudaStreamCreateWithFlags(&s.up, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
-        if ((e = cudaStreamCreateWithFlags(&s.down, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
-        if ((e = cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-        if ((e = cudaEventCreateWithFlags(&s.join_down, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+        // built in a local copy and published only when complete; a failure destroys what was made
+        PipeState t;
+        auto fail = [&t](cudaError_t err) {
+            if (t.up) cudaStreamDestroy(t.up);
+            if (t.down) cudaStreamDestroy(t.down);
+            if (t.fork) cudaEventDestroy(t.fork);
+            if (t.join_down) cudaEventDestroy(t.join_down);
+            for (uint32_t i = 0; i < kMaxChunks; ++i) {
+                if (t.uploaded[i]) cudaEventDestroy(t.uploaded[i]);
+                if (t.computed[i]) cudaEventDestroy(t.computed[i]);
+            }
+            return (int)err;
+        };
+        if ((e = cudaStreamCreateWithFlags(&t.up, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+        if ((e = cudaStreamCreateWithFlags(&t.down, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+        if ((e = cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
+        if ((e = cudaEventCreateWithFlags(&t.join_down, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
         for (uint32_t i = 0; i < kMaxChunks; ++i) {
-            if ((e = cudaEventCreateWithFlags(&s.uploaded[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-            if ((e = cudaEventCreateWithFlags(&s.computed[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+            if ((e = cudaEventCreateWithFlags(&t.uploaded[i], cudaEventDisableTiming)) != cudaSuccess) return fail(e);
+            if ((e = cudaEventCreateWithFlags(&t.computed[i], cudaEventDisableTiming)) != cudaSuccess) return fail(e);
         }
-        s.ready = true;
+        t.ready = true;
+        s = t;
     }
     *out = &s;
     return DUQ4_OK;

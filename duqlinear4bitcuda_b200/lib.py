@@ -47,6 +47,7 @@ SIGNATURES = {
     "duq4_version": [],
     "duq4_error_string": [_i],
     "duq4_dual_quant_col_k": [],
+    "duq4_tensor_map_cache_entries": [],
     "duq4_set_static_weights": [_i],
     "duq4_sym_quant": [_vp, _vp, _u32, _u32, _u32, _vp, _vp],
     "duq4_sym_dual_quant": [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp],

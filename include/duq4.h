@@ -15,9 +15,11 @@
  *     what every launch of the reference uses);
  *   - return value: 0 = ok, < 0 = argument rejected before any launch (DUQ4_ERR_*),
  *     > 0 = a cudaError_t reported by the launch.
- *   - all functions are re-entrant; the process-wide state is a mutex-guarded cache of TMA
- *     descriptors keyed by (pointer, shape), the duq4_set_static_weights flag, the scratch
- *     array of the _static entry point, and two helper streams per device that the _host entry
+ *   - all functions may be called from several host threads at once (on different streams or
+ *     devices); the process-wide state is a mutex-guarded cache of TMA descriptors keyed by
+ *     (pointer, shape), once-per-device kernel set-up guarded the same way, the atomic
+ *     duq4_set_static_weights flag, the scratch array of the _static entry point (shared by all
+ *     its calls on a GPU -- see there), and two helper streams per device that the _host entry
  *     point creates on first use.
  */
 #ifndef DUQ4_H_
@@ -59,6 +61,10 @@ const char *duq4_error_string(int status);
 /* Value exported by the reference's pybind module as get_dual_quant_col_k()
  * (ref: src/export/bindings.cpp:471-473). */
 int duq4_dual_quant_col_k(void);
+/* Number of TMA descriptors the library's cache holds at the moment (diagnostic; the cache lives on
+ * the host heap, is keyed by (pointer, shape) and is emptied when it passes 4096 entries). No reference
+ * counterpart. */
+int duq4_tensor_map_cache_entries(void);
 
 /* Process-wide promise about WEIGHT-side operands (the second matrix of the linear / matmul entry
  * points and the per-output-channel vectors of the epilogue: scale_col_*, zeros_col_*, bias):
@@ -266,7 +272,9 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
 
 /* duq4_linear_w4a4_from_fp16 for callers that have no device memory to lend and may not
  * allocate any: it takes no workspace argument and makes no allocation of any kind (no
- * cudaMalloc/cudaFree, no pooled or library allocator, no host heap). Typical callers: a
+ * cudaMalloc/cudaFree, no pooled or library allocator, no host heap: the TMA descriptors of the
+ * call are encoded on the stack and the descriptor cache is neither consulted nor extended, on
+ * every kernel the call can route to). Typical callers: a
  * plugin running inside a serving process whose allocator has already claimed the whole GPU
  * (a cudaMalloc there fails or stalls the device), code on a latency path where an allocation's
  * implicit device synchronisation is not acceptable, and small embedders that only own their
@@ -309,7 +317,7 @@ int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W
                                   void *h_out, void *stream);
 
 /* The same layer with the activations and the result in HOST memory (what a caller holds when
- * the reference module is fed from the CPU side; ref: src/nn/linear.cpp:102-127 moves nothing
+ * the reference module is fed from the CPU side; ref: src/module/linear.cu:108-153 moves nothing
  * itself, torch's .to(device) / .cpu() around it do). x_host [M, K] fp16 and out_host
  * [M, epi->ldo or N] fp16 are host pointers -- page-locked memory lets the copies overlap the
  * arithmetic, pageable memory works but serialises. W and the per-channel vectors of `epi` are

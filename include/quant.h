@@ -16,6 +16,10 @@
 #include "duq4.h"
 
 constexpr int QUANT_COL_K = DUQ4_QUANT_COL_K;  // include/quant.h:5 of the reference
+// include/quant.h:7 of the reference: a 128-bit mask with bits 0-4 and 10-14 set. The reference's dual
+// asymmetric dequant tests it as `(QUANT_COL_ST << col) & 1`, which is non-zero for output column 0 only;
+// the library's epilogues reproduce that outcome (DUQ4_MODE_ASYM_DUAL), the constant is kept for callers.
+constexpr __uint128_t QUANT_COL_ST = (((__uint128_t)0x1F) << 0) | (((__uint128_t)0x1F) << 10);
 
 namespace duq4_detail {
 inline void check(const char *fn, int status) {

@@ -24,7 +24,7 @@ def build(force=False):
     for inc in ce.include_paths():
         cmd += ["-isystem", inc]
     cmd += [L.LIB_PATH, "-L", tlib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
-            "-L", "/usr/local/cuda/lib64", "-lcudart",
+            "-L", "/usr/local/cuda/lib64", "-lcudart", "-ldl",
             "-Wl,-rpath," + tlib, "-Wl,-rpath," + os.path.dirname(L.LIB_PATH), "-Wl,--no-as-needed"]
     subprocess.check_call(cmd)
     return EXE

@@ -12,6 +12,8 @@ SRC = r'''
 #include <cstdio>
 int main() {
     static_assert(QUANT_COL_K == 10 && qmax_sym == 6 && kElementsPerVector == 2, "reference constants");
+    static_assert(QUANT_COL_ST == ((((__uint128_t)1 << 5) - 1) | ((((__uint128_t)1 << 5) - 1) << 10)), "bits 0-4 and 10-14");
+    static_assert(((QUANT_COL_ST << 0) & 1) == 1 && ((QUANT_COL_ST << 1) & 1) == 0, "the reference's selector holds for column 0 only");
     int caught = 0;
     try { matmul_host_4bit(nullptr, nullptr, 4, 4, 64, nullptr); } catch (const std::runtime_error &) { ++caught; }
     try { sym_quant_host(nullptr, nullptr, 4, 64, 32, nullptr); } catch (const std::runtime_error &) { ++caught; }

@@ -217,34 +217,36 @@ def test_batched(env, B, M, N, K):
 
 
 @pytest.mark.parametrize("M", [4, 20, 31, 300])   # 20, 31: the int8 code buffer is padded to 32 rows
-@pytest.mark.parametrize("mode", ["sym", "asym"])
+@pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
 def test_linear_from_fp16(env, M, mode):
-    """quantize -> GEMM -> dequant in one call, scratch supplied by the caller."""
+    """quantize -> GEMM -> dequant in one call, scratch supplied by the caller. The codes and per-token
+    vectors the call leaves in its scratch are checked against the oracle (and the reference's quantize
+    kernel) by U.check_gpu_codes; the oracle's GEMM + dequant on exactly those codes must then give every
+    output row bit for bit."""
     torch, L, o = env
     N, K = 520, 1024
-    x = U.acts(M, K, 5, mean=0.1 if mode == "asym" else 0.0)
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    x = U.acts(M, K, 5, mean=0.1 if asym else 0.0)
     w = (np.random.default_rng(6).standard_normal((N, K)) * 0.02).astype(np.float16)
     qw, sw = o.weight_sym_quant_pack(w)
-    zc = U.rand_zeros(N, 7)
-    if mode == "sym":
-        s = o.sym_scales(x, 1.0); qa = o.sym_quant(x, s); z = None
-    else:
-        s, z = o.asym_scales_zeros(x); qa = o.asym_quant(x, s, z)
-    _, want = o.linear_w4a4(mode, qa, qw, s, z, sw, zc, None, None)
-    dx, dw, dsw, dzc = (dev(torch, v) for v in (x, qw, sw, zc))
+    zc = U.rand_zeros(N, 7); sw2 = U.rand_scales(N, 8); zc2 = U.rand_zeros(N, 9)
+    dx, dw, dsw, dzc, dsw2, dzc2 = (dev(torch, v) for v in (x, qw, sw, zc, sw2, zc2))
     nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
     ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
-    epi = L.make_epilogue(mode, None, None, dsw, dzc if mode == "asym" else None)
+    epi = L.make_epilogue(mode, None, None, dsw, dzc if asym else None, dsw2 if dual else None, dzc2 if mode == "asym_dual" else None)
     out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
     for _ in range(2):  # the scratch is reused between calls
         L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), L.ptr(out),
                L.ptr(ws), nbytes, L.current_stream())
     torch.cuda.synchronize()
-    got = out.cpu().numpy()
-    # codes may differ from the exact-division oracle at rare near-ties of the GPU divide; such a
-    # token's row then differs, so compare row-wise and allow a handful of such rows
-    bad_rows = [r for r in range(M) if not U.f16_equal_nan(got[r], want[r])]
-    assert len(bad_rows) <= max(1, M // 100), bad_rows
+    if M > 16:
+        assert tc_status(L) == 0
+    qa, s1, z1, s2, z2 = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
+    U.check_gpu_codes(torch, L, mode, x, qa, s1, z1 if asym else None, s2 if dual else None, z2 if mode == "asym_dual" else None)
+    # the epilogue uses set 1 of the per-token vectors (the reference modules carry one row-scale vector)
+    _, want = o.linear_w4a4(mode, qa, qw, s1, z1 if asym else None, sw, zc if asym else None, sw2 if dual else None,
+                            zc2 if mode == "asym_dual" else None)
+    assert U.f16_equal_nan(out.cpu().numpy(), want), f"{mode} M={M}: fp16 outputs differ from the oracle on the call's own codes"
     assert L.cdll.duq4_linear_w4a4_from_fp16(L.ptr(dx), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), L.ptr(out),
                                              L.ptr(ws), nbytes - 1, L.current_stream()) == -4
 

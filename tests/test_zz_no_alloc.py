@@ -5,7 +5,11 @@ path that must not trigger an allocation's device synchronisation). Its scratch 
 
   * two calls in a row give exactly the output of the workspace-taking entry point
     (bit-identical fp16, the tolerance the other GPU tests use), although the second call finds
-    the first call's leftovers in the shared array;
+    the first call's leftovers in the shared array -- on every kernel the call can route to
+    (small-M register and TMA-streamed kernels, the single-CTA tensor-core kernel including the
+    17..31-token case whose code buffer is padded to 32 rows, and the CTA-pair kernel) -- and the
+    workspace-taking entry point is itself checked against the CPU oracle on the same inputs;
+  * the calls leave the library's TMA descriptor cache (host heap) untouched;
   * a problem whose scratch need exceeds the array is refused with DUQ4_ERR_TOO_LARGE (-8)
     before anything is launched.
 
@@ -20,10 +24,14 @@ from tests import _util as U
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M,N,K,mode", [(4, 520, 1024, "sym"), (16, 384, 4096, "asym"), (100, 264, 2048, "sym")])
+@pytest.mark.parametrize("M,N,K,mode", [(4, 520, 1024, "sym"), (16, 384, 4096, "asym"), (100, 264, 2048, "sym"),
+                                        (20, 520, 1024, "asym"),        # 17..31 tokens: 32-row padded code buffer
+                                        (9, 9600, 4096, "sym"),         # small-M TMA-streamed kernel
+                                        (200, 22016, 4096, "sym")])     # CTA-pair tensor-core kernel
 def test_static_scratch_entry_matches_workspace_entry_twice(M, N, K, mode):
     import torch
     import duqlinear4bitcuda_b200.lib as L
+    from oracle import oracle as o
 
     st = L.current_stream()
     dw = torch.from_numpy(U.rand_codes(N, K, 11)).cuda()
@@ -40,11 +48,21 @@ def test_static_scratch_entry_matches_workspace_entry_twice(M, N, K, mode):
         got = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
         L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), L.ptr(want),
                L.ptr(ws), nbytes, st)
+        torch.cuda.synchronize()
+        cached = L.cdll.duq4_tensor_map_cache_entries()
         L.call("duq4_linear_w4a4_from_fp16_static", L.ptr(x), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi),
                L.ptr(got), st)
         torch.cuda.synchronize()
+        assert L.cdll.duq4_tensor_map_cache_entries() == cached, "the static entry point touched the descriptor cache"
         assert U.f16_equal_nan(got.cpu().numpy(), want.cpu().numpy()), f"call {call}"
         assert not torch.isnan(got).all()
+        if call == 0:   # the workspace entry point against the oracle, on the codes it left in its scratch
+            xn = x.cpu().numpy()
+            qa, s1, z1, _, _ = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
+            U.check_gpu_codes(torch, L, mode, xn, qa, s1, z1 if mode == "asym" else None)
+            _, ora = o.linear_w4a4(mode, qa, dw.cpu().numpy(), s1, z1 if mode == "asym" else None, dsw.cpu().numpy(),
+                                   dzc.cpu().numpy() if mode == "asym" else None, None, None, bias.cpu().numpy())
+            assert U.f16_equal_nan(want.cpu().numpy(), ora), "workspace entry point differs from the oracle"
     status = ctypes.c_int32(-1)
     L.call("duq4_last_device_status", st, ctypes.byref(status))
     assert status.value == 0
