@@ -32,7 +32,25 @@ class _PackedLinearBase(torch.nn.Module):
             self.bias = None
 
     def _vec(self, name):
-        return getattr(self, name, None) if name in self._vectors else None
+        """Per-channel vector `name` as the kernels read it: fp16. The symmetric variants register their
+        scales with torch's default dtype (fp32), as the reference does, so a module that was built
+        directly and filled by load_state_dict holds fp32 scales; those are converted once and the
+        fp16 copy is kept until the buffer changes."""
+        t = getattr(self, name, None) if name in self._vectors else None
+        if t is None or t.dtype == torch.float16:
+            return t
+        cache = self.__dict__.setdefault("_f16_vectors", {})
+        key = (t.data_ptr(), t._version, t.device)
+        hit = cache.get(name)
+        if hit is None or hit[0] != key:
+            hit = cache[name] = (key, t.to(torch.float16))
+        return hit[1]
+
+    def _bias_f16(self):
+        b = self.bias
+        if b is None or b.dtype == torch.float16:
+            return b
+        raise TypeError(f"{type(self).__name__}: bias must be float16 for the fused kernel, got {b.dtype}")
 
     def _fused_fp16(self, x):
         """fp16 input of a module that owns its quantizer: quantize + GEMM + dequant in one library
@@ -44,7 +62,7 @@ class _PackedLinearBase(torch.nn.Module):
         first = lambda a, b: self._vec(a) if a in self._vectors else self._vec(b)
         y = ops.linear_w4a4_from_fp16(self._mode, x.view(-1, x.shape[-1]), self.weight,
                                       flat(first("weight_scales", "weight_scales_1")), flat(first("weight_zeros", "weight_zeros_1")),
-                                      flat(self._vec("weight_scales_2")), flat(self._vec("weight_zeros_2")), self.bias)
+                                      flat(self._vec("weight_scales_2")), flat(self._vec("weight_zeros_2")), self._bias_f16())
         return y.view(*x.shape[:-1], -1)
 
     def _fused(self, packed):
@@ -53,7 +71,7 @@ class _PackedLinearBase(torch.nn.Module):
         return tensor_utils.linear(self._mode, packed, self.weight,
                                    self._vec("weight_scales") if "weight_scales" in self._vectors else self._vec("weight_scales_1"),
                                    self._vec("weight_zeros") if "weight_zeros" in self._vectors else self._vec("weight_zeros_1"),
-                                   self._vec("weight_scales_2"), self._vec("weight_zeros_2"), self.bias)
+                                   self._vec("weight_scales_2"), self._vec("weight_zeros_2"), self._bias_f16())
 
 
 class Linear4bitSQ(_PackedLinearBase):

@@ -161,6 +161,48 @@ def test_operator_argument_checks(env):
         tu.matmul(torch.zeros((4, 24), dtype=torch.uint8, device="cuda"), torch.zeros((4, 24), dtype=torch.uint8, device="cuda"))
     q = ops.asym_dual_quant(x, s, s, s, s)           # returns its tensor (the reference's binding does not)
     assert q.dtype == torch.uint8 and tuple(q.shape) == (4, 32)
+    # dtypes are checked, not reinterpreted: fp32 scales, an fp32 bias or bf16 activations would otherwise be read
+    # as fp16 bit patterns and give silently wrong numbers
+    w = torch.zeros((8, 32), dtype=torch.uint8, device="cuda"); sc = torch.ones(8, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.sym_quant(x, s.float())
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.sym_quant(x.to(torch.bfloat16), s)
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.linear_w4a4("sym", q, w, s, None, sc.float())
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.linear_w4a4("sym", q, w, s, None, sc, bias=torch.zeros(8, device="cuda"))
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.linear_w4a4("sym", q.to(torch.int8), w, s, None, sc)
+    with pytest.raises(RuntimeError):
+        ops.linear_w4a4_from_fp16("sym", x.float(), w, sc)
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.linear_w4a4_from_fp16("sym", x, w, sc.float())
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.quantize_sym_fused(x.float())
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.linear_w4a4_batched("asym", q.view(1, 4, 32), w.view(1, 8, 32), s.view(1, 4), s.view(1, 4), sc.view(1, 8).float(), sc.view(1, 8))
+    with pytest.raises(RuntimeError, match="unknown mode"):
+        ops.linear_w4a4("symm", q, w, s, None, sc)
+
+
+def test_module_with_fp32_scale_buffers_matches_fp16(env):
+    """Linear4bitSQ registers weight_scales with torch's default dtype (fp32), as the reference does; a module
+    built directly and filled by load_state_dict keeps them in fp32. The forward converts them once and gives
+    the same output as the from_float module (fp16 scales)."""
+    torch, qnn, tu, o = env
+    lin = _lin(torch, 256, 72, 21)
+    scales = (lin.weight.data.abs().amax(dim=1, keepdim=True).float() / 7).half()
+    a = qnn.Linear4bitSQ.from_float(lin, weight_scales=scales).cuda()
+    b = qnn.Linear4bitSQ(256, 72, bias=True)
+    assert b.weight_scales.dtype == torch.float32
+    b.load_state_dict(a.state_dict())
+    b = b.cuda()
+    assert b.weight_scales.dtype == torch.float32
+    packed = qnn.SymQuantizer()(torch.from_numpy(U.acts(20, 256, 5)).cuda())
+    ya, yb = a(packed), b(packed)
+    assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
+    assert torch.equal(b(packed).view(torch.int16), ya.view(torch.int16))   # second call: cached fp16 copy
 
 
 @pytest.mark.parametrize("rows,inter", [(5, 64), (33, 11008), (300, 1024)])
