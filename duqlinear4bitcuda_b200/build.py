@@ -43,13 +43,14 @@ def build_binding(force=False, verbose=False):
     import torch
     from torch.utils import cpp_extension as ce
     tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
-    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden",
+    # the system g++ (the host compiler nvcc uses): its libstdc++ is the shared one torch itself is linked to
+    cmd = [os.environ.get("DUQ4_CXX", "/usr/bin/g++"), "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden",
            "-DTORCH_EXTENSION_NAME=_CUDA", "-DTORCH_API_INCLUDE_EXTENSION_H",
            "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), src, "-o", EXT,
            "-I", sysconfig.get_paths()["include"], "-I", "/usr/local/cuda/include"]
     for inc in ce.include_paths():
         cmd += ["-isystem", inc]
-    cmd += [LIB, "-L", tlib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+    cmd += ["-L", HERE, "-l:libduq4.so", "-L", tlib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
             "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or p.returncode:
@@ -84,7 +85,7 @@ def build_library(force=False, verbose=False):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([NVCC, "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC"])
+    subprocess.check_call([NVCC, "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC", "-Xlinker", "-soname=libduq4.so"])
     return LIB
 
 
