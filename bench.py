@@ -461,19 +461,17 @@ def run_ours(args):
     out_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
     codes = torch.empty((M, K), dtype=torch.int8, device=device)   # tensor-core-ready activation codes
     sa = torch.empty((M,), dtype=torch.float16, device=device)
-    ws_bytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
     epi = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns)
-    epi_e2e = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns)
 
     peer = None
     gather_mode = "none" if world == 1 else args.gather
     if world > 1 and args.gather == "fused":
         try:
             from duqlinear4bitcuda_b200.parallel import PeerOutput
-            peer = PeerOutput(M, N, device)
-            epi_f = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns))
-            epi_f_e2e = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns))
+            peer = PeerOutput(M, N, device, use_multicast=not args.no_multicast)
+            epi_f = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns),
+                                    out_multicast=peer.multicast_column_ptr(rank * Ns))
+            gather_mode = "fused, multimem.st through the NVLink switch" if peer.multicast_ptr else "fused, one st.global per peer"
         except Exception as ex:  # symmetric memory not available on this box: use the collective
             peer = None
             gather_mode = f"nccl (symmetric memory unavailable: {type(ex).__name__})"
@@ -498,36 +496,35 @@ def run_ours(args):
             dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
             out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
 
-    staging = None
-    if world == 1:   # host-buffer entry point: upload, quantize + GEMM, download pipelined over row chunks
-        staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, N, K, 0)
-        staging = torch.empty(staging_bytes, dtype=torch.uint8, device=device)
+    # e2e: the job's activations and result live in HOST memory. One GPU: pinned tensors of this process.
+    # N GPUs: ONE input and ONE result in POSIX shared memory that every rank maps and page-locks for its own
+    # GPU; each rank uploads the activations over its own PCIe link, computes its column block and delivers it
+    # into columns [r*N/G, (r+1)*N/G) of the one row-major [M, N] host result -- the same C-ABI entry point as
+    # on one GPU (output pitch N, pointer at the shard's first column), no device-side gather, no collective.
+    shared_x = shared_out = None
+    if world == 1:
+        e2e_x, e2e_out, e2e_out_ptr = x_host, out_host, out_host.data_ptr()
+    else:
+        from duqlinear4bitcuda_b200.parallel import SharedHostTensor
+        tag = os.environ.get("MASTER_PORT", "0")
+        if rank == 0:
+            shared_x = SharedHostTensor(f"duq4_bench_{tag}_x", (M, K), torch.float16, create=True)
+            shared_out = SharedHostTensor(f"duq4_bench_{tag}_out", (M, N), torch.float16, create=True)
+            shared_x.tensor.copy_(x_host)
+            shared_out.tensor.zero_()
+        dist.barrier()
+        if rank != 0:
+            shared_x = SharedHostTensor(f"duq4_bench_{tag}_x", (M, K), torch.float16, create=False)
+            shared_out = SharedHostTensor(f"duq4_bench_{tag}_out", (M, N), torch.float16, create=False)
+        e2e_x, e2e_out = shared_x.tensor, shared_out.tensor
+        e2e_out_ptr = e2e_out.data_ptr() + 2 * rank * Ns
+    epi_host = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N)
+    staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, Ns, K, 0)
+    staging = torch.empty(staging_bytes, dtype=torch.uint8, device=device)
 
     def step_e2e():
-        if staging is not None:
-            L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(qw), M, N, K, L.MODE_SYM, 1.0,
-                   ctypes.byref(epi_e2e), out_host.data_ptr(), 0, L.ptr(staging), staging_bytes, st())
-            return
-        # N > 1: the job has ONE host input and ONE host result. Rank 0 uploads the activations and the
-        # ranks receive them over NVLink (broadcast); every rank computes its column block and the blocks are
-        # gathered on the devices; rank 0 alone brings the [M, N] result back to its host buffer.
-        if rank == 0:
-            x.copy_(x_host, non_blocking=True)
-        dist.broadcast(x, src=0)
-        if peer is not None:
-            peer.barrier()
-            L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_f_e2e),
-                   None, L.ptr(ws), ws_bytes, st())
-            peer.barrier()
-            if rank == 0:
-                out_host.copy_(peer.buf, non_blocking=True)
-            return
-        L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_e2e),
-               L.ptr(out_shard), L.ptr(ws), ws_bytes, st())
-        dist.all_gather_into_tensor(gathered.view(world * M, Ns), out_shard)
-        out_full.view(M, world, Ns).copy_(gathered.permute(1, 0, 2))
-        if rank == 0:
-            out_host.copy_(out_full, non_blocking=True)
+        L.call("duq4_linear_w4a4_from_fp16_host", e2e_x.data_ptr(), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0,
+               ctypes.byref(epi_host), e2e_out_ptr, 0, L.ptr(staging), staging_bytes, st())
 
     def barrier():
         if world > 1:
@@ -560,6 +557,34 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     e2e_ms, _ = timed(step_e2e, args.steps, args.warmup)
 
+    # ---- correctness of what was timed, computed OUTSIDE the timed regions -------------------------------
+    checks = {}
+    L.call("duq4_linear_w4a4_preunpacked", L.ptr(codes), L.ptr(qw), M, Ns, K, ctypes.byref(epi), L.ptr(out_shard), None, st())
+    torch.cuda.synchronize()
+    if world > 1:
+        # (1) this rank's column slice of the gathered [M, N] buffer equals its local block bit for bit;
+        # (2) a position-weighted checksum of the whole gathered buffer is the same number on every rank
+        full = peer.buf if peer is not None else out_full
+        mine = full[:, rank * Ns:(rank + 1) * Ns]
+        slice_ok = bool(torch.equal(mine.view(torch.int16), out_shard.view(torch.int16)))
+        hsum = torch.zeros((), dtype=torch.int64, device=device)
+        wts = (torch.arange(N, device=device, dtype=torch.int64) % 8191) + 1
+        for r0 in range(0, M, 512):
+            hsum += (full[r0:r0 + 512].view(torch.int16).to(torch.int64) * wts).sum() * (1 + r0 // 512)
+        lo, hi = hsum.clone(), hsum.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ok_t = torch.tensor([int(slice_ok)], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        checks["gather_check"] = "ok" if (int(ok_t.item()) == 1 and int(lo.item()) == int(hi.item())) else \
+            f"FAILED (slice_ok_all_ranks={int(ok_t.item())}, checksum min/max {int(lo.item())}/{int(hi.item())})"
+        # (3) the host result assembled from the ranks' slices equals the gathered device result
+        dist.barrier()
+        if rank == 0:
+            host_ok = bool(torch.equal(e2e_out.view(torch.int16), full.cpu().view(torch.int16)))
+            checks["e2e_host_result_check"] = "ok" if host_ok else "FAILED"
+    else:
+        checks["e2e_host_result_check"] = "ok" if bool(torch.equal(out_host.view(torch.int16), out_shard.cpu().view(torch.int16))) else "FAILED"
+
     status = ctypes.c_int32(-1)
     L.call("duq4_last_device_status", st(), ctypes.byref(status))
     if status.value != 0:
@@ -579,15 +604,19 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4xint4->int32 (kind::i8 tensor cores), fp16 epilogue", "data": "synthetic",
             "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "parallelism": f"column-parallel N/{world}, gather={gather_mode}" if world > 1 else "single GPU",
+                       "checks": "computed outside the timed regions: gathered buffer vs each rank's local block and a cross-rank checksum (gather_check), host result vs device result (e2e_host_result_check)",
                        "cache": "operands (weights 117 MB + activations 64 MB + output 235 MB) exceed the 126 MB L2; no flush",
                        "weights": "N(0,0.015) per-channel symmetric int4", "activations": "N(0,1), 1% channels x20, per-token symmetric int4"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_tops, 2), "unit": "TOPS", "ms_per_step": round(e2e_ms / args.steps, 4),
-                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "h2d_bytes_per_step": world * M * K * 2, "d2h_bytes_per_step": M * N * 2,
                     "api": ("duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, copies pipelined with the arithmetic over row chunks)"
                             if world == 1 else
-                            "rank 0 uploads the activations from pinned host memory, NCCL broadcast to the ranks, duq4_linear_w4a4_from_fp16 (C ABI) per rank with the gather on the devices, rank 0 copies the [M, N] result back to pinned host memory")},
-            "gpu_launches": args.steps * 2,
+                            "duq4_linear_w4a4_from_fp16_host (C ABI) on every rank: one input and one result in shared pinned host memory; each rank "
+                            "uploads the activations over its own PCIe link (h2d counts all ranks) and delivers its [M, N/G] column block into its "
+                            "column slice of the one host result; no device-side gather")},
+            "checks": checks,
+            "gpu_launches": args.steps * (4 if peer is not None else 2),   # per rank: quantize + GEMM (+ two barrier kernels around the fused gather)
             "roofline": {"kernel": "gemm_tc2_kernel (CTA pairs, 256x256x128 tiles, tcgen05.mma.cta_group::2.kind::i8; A int8 pre-unpacked by the quantizer, W int4 unpacked in smem)" if (M >= 256 * 8 and Ns >= 256 * 8) else "gemm_tc_kernel<MODE_A8B4> (tcgen05.mma kind::i8)", "bound": "tensor",
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
                          "frac": round(gemm_tops / int8_peak, 4),
@@ -610,6 +639,10 @@ def run_ours(args):
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()[0]
     if world > 1:
+        dist.barrier()
+        for h in (shared_x, shared_out):
+            if h is not None:
+                h.close()
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line))
@@ -623,6 +656,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
+    ap.add_argument("--no-multicast", action="store_true", help="N>1, fused gather: one plain store per peer instead of multimem.st")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "decode16", "quantize", "silu", "skinny"],

@@ -16,6 +16,7 @@ int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_
                             const EpiParams &p, void *h_out, cudaStream_t st);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
+int peer_status_read(int32_t *out);
 int tc2_status_read(int32_t *out);
 extern std::atomic<int> g_static_weights;
 int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t cols, float clip, uint8_t *q, void *s1,
@@ -48,6 +49,7 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
         if (!e->out_peers[i]) return DUQ4_ERR_NULL;
         p->peers[i] = (__half *)e->out_peers[i];
     }
+    p->mc_out = e->n_out_peers ? (__half *)e->out_multicast : nullptr;
     p->next_w = (const uint8_t *)e->next_weights;
     p->next_w_bytes = e->next_weights ? e->next_weights_bytes : 0;
     if (e->mode == DUQ4_MODE_NONE) return DUQ4_OK;
@@ -291,8 +293,11 @@ int duq4_last_device_status(void *stream, int32_t *status_out) {
     int32_t c = 0;
     rc = tc2_status_read(&c);
     if (rc) return rc;
-    // 1..9: tensor-core GEMM wait, 101..: small-M kernel wait, 201..: CTA-pair GEMM wait
-    *status_out = a ? a : (b ? 100 + b : (c ? 200 + c : 0));
+    int32_t d = 0;
+    rc = peer_status_read(&d);
+    if (rc) return rc;
+    // 1..9: tensor-core GEMM wait, 101..: small-M kernel wait, 201..: CTA-pair GEMM wait, 301: peer barrier wait
+    *status_out = a ? a : (b ? 100 + b : (c ? 200 + c : (d ? 300 + d : 0)));
     return DUQ4_OK;
 }
 

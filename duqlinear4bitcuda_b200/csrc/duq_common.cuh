@@ -99,6 +99,8 @@ struct EpiParams {
     // L2 prefetch hint (small-M kernels): packed weights of the next launch on the stream
     const uint8_t *next_w;
     uint64_t next_w_bytes;
+    // NVLS multicast address of the result buffer (see duq4_epilogue.out_multicast), or null
+    __half *mc_out;
 };
 
 // Output bases of a launch: the peer list if there is one, else the plain `out` pointer.

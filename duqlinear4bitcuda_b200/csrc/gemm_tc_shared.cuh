@@ -56,6 +56,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 16 bytes to the same offset of every rank's buffer through the NVLink switch: `mc_addr` is an address inside
+// an NVLS multicast mapping, 16-byte aligned.
+__device__ __forceinline__ void multimem_st16(void *mc_addr, const uint4 &v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 // K-major, 128-byte-swizzled operand descriptor: rows of 128 bytes, 8-row groups 1024 bytes
 // apart (stride byte offset), version 1, layout type 2 (SWIZZLE_128B).
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -143,6 +151,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
     for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
         if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
     const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
+    __half *const mc = (STAGED && vec_ok && (reinterpret_cast<uintptr_t>(pb.mc_out) & 15u) == 0) ? pb.mc_out : nullptr;
     const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -207,6 +216,10 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
             if (mr >= a.M || n0 + g0 >= n_end) continue;
             const uint4 seg = *reinterpret_cast<const uint4 *>(stg + r * 144 + (lane & 7) * 16);
             const size_t off = ((size_t)b * a.M + mr) * pb.ldo + n0 + g0;
+            if (mc && seg_full) {   // one store; the switch delivers it to every rank's buffer
+                multimem_st16(mc + off, seg);
+                continue;
+            }
 #pragma unroll
             for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
                 if (pi >= ob.n) break;

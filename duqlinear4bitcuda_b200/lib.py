@@ -31,6 +31,7 @@ class Epilogue(ctypes.Structure):
         ("out_peers", ctypes.c_void_p * 8),
         ("next_weights", ctypes.c_void_p),
         ("next_weights_bytes", ctypes.c_uint64),
+        ("out_multicast", ctypes.c_void_p),
     ]
 
 
@@ -78,6 +79,7 @@ SIGNATURES = {
     "duq4_linear_host_staging_bytes": [_u32, _u32, _u32, _u32],
     "duq4_linear_w4a4_from_fp16_host": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _u32, _vp, _sz, _vp],
     "duq4_linear_w4a4_from_fp16_static": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp],
+    "duq4_peer_barrier": [ctypes.POINTER(ctypes.c_void_p), _u32, _u32, ctypes.c_uint64, ctypes.c_uint64, _vp],
     "duq4_last_device_status": [_vp, ctypes.POINTER(ctypes.c_int32)],
 }
 _RESTYPES = {"duq4_version": ctypes.c_char_p, "duq4_error_string": ctypes.c_char_p,
@@ -117,7 +119,7 @@ def current_stream():
 
 
 def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
-                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None):
+                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None, out_multicast=None):
     """Fill a duq4_epilogue. `next_weights`: packed weight tensor of the layer that runs next on the
     stream (L2 prefetch hint of the small-M kernels; never read or written by this launch)."""
     e = Epilogue()
@@ -134,6 +136,8 @@ def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_
         e.n_out_peers = len(out_peers)
         for i, a in enumerate(out_peers):
             e.out_peers[i] = int(a)
+    if out_multicast:   # raw multicast address (int) of the same buffer, at this shard's first column
+        e.out_multicast = int(out_multicast)
     if next_weights is not None:
         e.next_weights = next_weights.data_ptr()
         e.next_weights_bytes = next_weights.numel() * next_weights.element_size()

@@ -10,6 +10,7 @@ the dual-uniform selectors, which depend on the GLOBAL output column, receive th
 column offset.
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -60,27 +61,111 @@ def gather_columns(local: torch.Tensor, n_out: int, group=None, out: torch.Tenso
     return full.contiguous()
 
 
+class SharedHostTensor:
+    """One HOST tensor that every rank process of a node maps: POSIX shared memory (a file under
+    /dev/shm) mapped MAP_SHARED, and -- with pin=True -- page-locked for the calling process's GPU
+    (cudaHostRegister), so that each rank's copy engine moves its own slice of the job over its own PCIe
+    link. The job of an N-sharded layer whose activations and result live on the host has ONE input and ONE
+    result: every rank reads the same activations from this memory and delivers its [M, N/G] column block
+    straight into columns [r*N/G, (r+1)*N/G) of the one row-major [M, N] result (`host_result_slice`); no
+    device-side gather and no second host copy are involved.
+
+    Exactly one process passes create=True (and calls it first; the others open after a barrier). `close()`
+    unpins and unmaps; the creator also removes the file."""
+
+    def __init__(self, name, shape, dtype, create, pin=True):
+        self.path = os.path.join("/dev/shm", name)
+        self.create, self.pinned = create, False
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        if create and os.path.exists(self.path):
+            os.unlink(self.path)
+        if not create and not os.path.exists(self.path):
+            raise FileNotFoundError(f"{self.path}: the creating rank has not made it yet (barrier missing?)")
+        self.tensor = torch.from_file(self.path, shared=True, size=numel, dtype=dtype).view(*shape)
+        self.nbytes = numel * self.tensor.element_size()
+        if pin:
+            rc = torch.cuda.cudart().cudaHostRegister(self.tensor.data_ptr(), self.nbytes, 0)
+            if int(rc) != 0:
+                raise RuntimeError(f"cudaHostRegister({self.path}) failed with CUDA error {int(rc)}")
+            self.pinned = True
+
+    def close(self):
+        if self.pinned:
+            torch.cuda.cudart().cudaHostUnregister(self.tensor.data_ptr())
+            self.pinned = False
+        self.tensor = None
+        if self.create and os.path.exists(self.path):
+            os.unlink(self.path)
+
+
+def host_result_slice(n_out: int, world: int, rank: int):
+    """Where rank `rank` delivers its block inside the one row-major fp16 [M, n_out] host result:
+    (byte offset of its first column from the start of a row, row pitch in elements, block width)."""
+    b, e = shard_bounds(n_out, world, rank)
+    return 2 * b, n_out, e - b
+
+
 class PeerOutput:
     """A [M, N] fp16 result buffer that exists on every rank and is mapped into every other
     rank's address space (torch symmetric memory over NVLink). The GEMM epilogue of each rank
     stores its column block straight into all of these buffers (`duq4_epilogue.out_peers`), so
-    the all-gather is fused into the kernel: no separate collective, no re-layout copy.
-    `barrier()` is a device-side barrier across the ranks on the current stream."""
+    the all-gather is fused into the kernel: no separate collective, no re-layout copy. Where the
+    NVLink switch offers a multicast mapping of the buffer (NVLS), the epilogue stores each 16-byte
+    row segment ONCE to that mapping (`duq4_epilogue.out_multicast`, multimem.st) and the switch
+    replicates it, which cuts a rank's NVLink egress from (G-1)/G of the result to 1/G of it.
 
-    def __init__(self, M, N, device, group=None):
+    `barrier()` is the library's own device-side barrier across the ranks on the current stream
+    (duq4_peer_barrier): flags in symmetric memory, a bounded wait (`barrier_timeout_ns`, 0 = one
+    second) and a status word instead of a hang when a rank does not arrive."""
+
+    def __init__(self, M, N, device, group=None, use_multicast=True, barrier_timeout_ns=0):
         import torch.distributed._symmetric_memory as symm
+        from . import lib as L
+        self._L = L
         self.M, self.N = M, N
-        self.buf = symm.empty((M, N), dtype=torch.float16, device=device)
-        self.hdl = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
-        if len(self.ptrs) > 8:
+        grp = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(grp), dist.get_rank(grp)
+        if self.world > 8:
             raise ValueError("fused all-gather supports at most 8 ranks")
+        self.buf = symm.empty((M, N), dtype=torch.float16, device=device)
+        self.hdl = symm.rendezvous(self.buf, grp)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc if use_multicast else 0
+        # barrier flags: world uint64 slots per rank, slot s of rank r is written by rank s
+        self.flags = symm.empty((self.world,), dtype=torch.int64, device=device)
+        self.flags.zero_()
+        self.fhdl = symm.rendezvous(self.flags, grp)
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.fhdl.buffer_ptrs])
+        self.epoch = 0
+        self.barrier_timeout_ns = int(barrier_timeout_ns)
+        torch.cuda.synchronize(device)
+        dist.barrier(grp)   # every rank's flags are zero before anybody's first flag store can land
 
     def column_ptrs(self, col_begin):
         return [p + 2 * col_begin for p in self.ptrs]
 
-    def barrier(self):
-        self.hdl.barrier()
+    def multicast_column_ptr(self, col_begin):
+        return self.multicast_ptr + 2 * col_begin if self.multicast_ptr else 0
+
+    def barrier(self, arrive=True):
+        """Queues the barrier on the current stream. arrive=False only advances the epoch without
+        launching (a rank that stays away -- used to exercise the time-out path of the others)."""
+        self.epoch += 1
+        if not arrive:
+            return
+        with torch.cuda.device(self.buf.device):
+            self._L.call("duq4_peer_barrier", self._flag_ptrs, self.world, self.rank, self.epoch, self.barrier_timeout_ns,
+                         self._L.current_stream())
+
+    def catch_up(self):
+        """After a barrier this rank stayed away from: publish the current epoch so that the peers' later
+        barriers see this rank as arrived (a barrier launch whose own wait is already satisfied or bounded)."""
+        with torch.cuda.device(self.buf.device):
+            self._L.call("duq4_peer_barrier", self._flag_ptrs, self.world, self.rank, self.epoch, self.barrier_timeout_ns,
+                         self._L.current_stream())
 
 
 class ColumnParallelLinear4bit(torch.nn.Module):
@@ -109,6 +194,7 @@ class ColumnParallelLinear4bit(torch.nn.Module):
                 setattr(self, name, None)
         self._ws = None
         self._peer = None
+        self._staging = None
 
     @classmethod
     def from_full(cls, mode, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None, clip_ratio=1.0,
@@ -137,7 +223,8 @@ class ColumnParallelLinear4bit(torch.nn.Module):
             out = None
             epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
                                   flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=self.n_out,
-                                  out_peers=peer.column_ptrs(self.col_begin))
+                                  out_peers=peer.column_ptrs(self.col_begin),
+                                  out_multicast=peer.multicast_column_ptr(self.col_begin))
         if n_local:
             with torch.cuda.device(x2d.device):
                 L.call("duq4_linear_w4a4_from_fp16", L.ptr(x2d), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
@@ -145,23 +232,62 @@ class ColumnParallelLinear4bit(torch.nn.Module):
                        L.current_stream())
         return out
 
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0):
+        """The layer for a job whose activations and result live in HOST memory that every rank maps
+        (`SharedHostTensor`; any pinned host tensor when world == 1): this rank uploads the activations,
+        computes its column block and delivers it into its column slice of `out_host` [M, n_out], all inside
+        one call of the host-buffer entry point of the C ABI (upload, arithmetic and download pipelined over
+        row chunks on this rank's own copy engines). No collective runs: the result is complete once every
+        rank's stream has finished (synchronize, then a host barrier). x_host fp16 [M, K]; out_host fp16
+        [M, n_out] row-major."""
+        from . import lib as L
+        if x_host.is_cuda or out_host.is_cuda:
+            raise ValueError("forward_host takes host tensors")
+        if x_host.dtype != torch.float16 or out_host.dtype != torch.float16 or not x_host.is_contiguous() or not out_host.is_contiguous():
+            raise ValueError("forward_host: contiguous fp16 host tensors expected")
+        M, K = x_host.shape
+        if tuple(out_host.shape) != (M, self.n_out):
+            raise ValueError(f"out_host must be [{M}, {self.n_out}]")
+        byte_off, ldo, n_local = host_result_slice(self.n_out, self.world, self.rank)
+        if n_local == 0 or M == 0:
+            return
+        dev = self.weight.device
+        need = L.cdll.duq4_linear_host_staging_bytes(M, n_local, K, chunk_rows)
+        if self._staging is None or self._staging.numel() < need:
+            self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
+        flat = lambda t: None if t is None else t.reshape(-1)
+        epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                              flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=ldo)
+        with torch.cuda.device(dev):
+            L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
+                   float(self.clip_ratio), ctypes.byref(epi), out_host.data_ptr() + byte_off, chunk_rows, L.ptr(self._staging),
+                   self._staging.numel(), L.current_stream())
+
     def forward(self, x: torch.Tensor, gather: str = "nccl"):
         """gather="nccl": compute the local block, then one NCCL all-gather (+ re-layout copy).
         gather="fused": the kernel's epilogue writes the block into every rank's result buffer over
-        NVLink (peer stores); two device-side barriers bracket the launch (peers finished reading
+        NVLink (one multicast store per row segment where the switch offers a multicast mapping, else one
+        store per peer; gather="fused_peer" forces the latter); two device-side barriers bracket the launch (peers finished reading
         the previous result / everybody finished writing this one). The returned tensor is a view
         of that shared buffer: it is overwritten by the next fused forward of the same shape."""
         x2d = x.reshape(-1, x.shape[-1]).contiguous()
         if self.world == 1:
             full = self.local_forward(x2d)
-        elif gather == "fused":
+        elif gather in ("fused", "fused_peer"):
             M = x2d.shape[0]
-            if self._peer is None or self._peer.M != M:
-                self._peer = PeerOutput(M, self.n_out, x2d.device, self.group)
-            self._peer.barrier()
-            self.local_forward(x2d, self._peer)
-            self._peer.barrier()
-            full = self._peer.buf
+            if self._peer is None:
+                self._peer = {}
+            peer = self._peer.get((M, gather))
+            if peer is None:
+                # one shared buffer per token count, kept for the life of the layer: a serving loop that
+                # alternates between a few token counts neither re-allocates (a collective rendezvous) nor
+                # frees memory a slower rank may still be storing into
+                peer = self._peer[(M, gather)] = PeerOutput(M, self.n_out, x2d.device, self.group,
+                                                            use_multicast=(gather == "fused"))
+            peer.barrier()
+            self.local_forward(x2d, peer)
+            peer.barrier()
+            full = peer.buf
         else:
             full = gather_columns(self.local_forward(x2d), self.n_out, self.group)
         return full.view(*x.shape[:-1], self.n_out)

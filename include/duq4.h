@@ -228,6 +228,13 @@ typedef struct duq4_epilogue {
      * do not depend on it. NULL / 0 = none. Ignored by the tensor-core kernels. */
     const void *next_weights;
     uint64_t next_weights_bytes;
+    /* Fused all-gather through the NVLink switch (optional, with n_out_peers > 0): the MULTICAST address
+     * of the same [M, ldo] result buffer (an NVLS multicast mapping that spans all ranks, as CUDA's
+     * multicast objects / torch symmetric memory provide), pointing at this shard's first column like the
+     * out_peers entries. Full 16-byte row segments then leave the GPU ONCE (multimem.st) and the switch
+     * replicates them into every rank's buffer, instead of one store per peer; ragged edges still go
+     * through out_peers. NULL = plain peer stores. Tensor-core kernels only. */
+    void *out_multicast;
 } duq4_epilogue;
 
 /* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches
@@ -334,6 +341,18 @@ int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32
                                     uint32_t K, int act_mode, float clip_ratio,
                                     const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows,
                                     void *staging, size_t staging_bytes, void *stream);
+
+/* Device-side barrier across the ranks of an N-sharded layer, on `stream` (no reference counterpart; it
+ * brackets the fused all-gather: "everybody has consumed the previous result" / "everybody's block has
+ * landed"). flag_ptrs: HOST array of `world` device addresses, entry r = rank r's flag array of `world`
+ * uint64 slots, zero-initialised, mapped into this process (its own and peer-mapped, like out_peers).
+ * The kernel makes this rank's earlier work on the stream visible system-wide, writes `epoch` into slot
+ * [rank] of every rank's array and waits until its own slots all hold a value >= epoch. `epoch` must grow
+ * by one per barrier (start at 1; all ranks count alike). The wait is BOUNDED: after timeout_ns (0 = one
+ * second) the kernel gives up, records code 301 in the device status word (duq4_last_device_status) and
+ * returns, so a rank that never arrives costs a time-out, not a hung GPU. One launch of one CTA. */
+int duq4_peer_barrier(const void *const *flag_ptrs, uint32_t world, uint32_t rank, uint64_t epoch,
+                      uint64_t timeout_ns, void *stream);
 
 /* Device-side status word of the most recent tensor-core GEMM on the current device:
  * 0 = no bounded wait expired. Reads back 4 bytes (synchronises the stream given). */

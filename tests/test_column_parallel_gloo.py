@@ -140,3 +140,53 @@ def test_row_parallel_partial_sums_match_unsharded(tmp_path, mode, k_in, world):
         ok_stats, ok = open(tmp_path / f"r{r}").read().split()
         assert ok_stats == "1", f"rank {r}: all-reduced statistics differ from the unsharded quantizer"
         assert ok == "1", f"rank {r}: row-parallel result differs from the unsharded layer"
+
+
+# ---- host-resident job: one shared host result assembled from per-rank column slices ----------------
+def _host_slice_worker(rank, world, port, n_out, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    shared = None
+    try:
+        from oracle import oracle as o
+        from duqlinear4bitcuda_b200.parallel import SharedHostTensor, host_result_slice
+        M, K = 7, 128
+        qa = U.rand_codes(M, K, 1); qw = U.rand_codes(n_out, K, 2)
+        sr = U.rand_scales(M, 3); sc1 = U.rand_scales(n_out, 5); sc2 = U.rand_scales(n_out, 7)
+        name = f"duq4_gloo_{port}_out"
+        if rank == 0:
+            shared = SharedHostTensor(name, (M, n_out), torch.float16, create=True, pin=False)
+            shared.tensor.fill_(-3.0)
+        dist.barrier()
+        if rank != 0:
+            shared = SharedHostTensor(name, (M, n_out), torch.float16, create=False, pin=False)
+        b, e = shard_bounds(n_out, world, rank)
+        _, local = o.linear_w4a4("sym_dual", qa, qw[b:e], sr, None, sc1[b:e], None, sc2[b:e], None, None, col0=b)
+        # deliver the block the way the host-buffer entry point does: base pointer + byte offset, row pitch ldo
+        byte_off, ldo, width = host_result_slice(n_out, world, rank)
+        assert (byte_off, ldo, width) == (2 * b, n_out, e - b)
+        flat = shared.tensor.view(-1).numpy()
+        for r in range(M):
+            start = byte_off // 2 + r * ldo
+            flat[start:start + width] = local[r]
+        dist.barrier()
+        _, want = o.linear_w4a4("sym_dual", qa, qw, sr, None, sc1, None, sc2, None, None, col0=0)
+        ok = np.array_equal(shared.tensor.numpy().view(np.uint16), want.view(np.uint16))
+        open(os.path.join(tmp, f"r{rank}"), "w").write(str(int(ok)))
+        dist.barrier()
+    finally:
+        if shared is not None:
+            shared.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_out,world", [(48, 2), (40, 2), (72, 3)])
+def test_host_result_assembled_from_rank_slices(tmp_path, n_out, world):
+    """Every rank maps the ONE host result (POSIX shared memory) and writes its column block at the offset and
+    pitch `host_result_slice` gives; together the slices are the unsharded layer's row-major [M, N] output
+    (even and ragged shard widths). Per-shard arithmetic by the CPU oracle."""
+    port = _free_port()
+    mp.spawn(_host_slice_worker, args=(world, port, n_out, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"r{r}").read() == "1", f"rank {r}"
+    assert not os.path.exists(f"/dev/shm/duq4_gloo_{port}_out")
