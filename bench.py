@@ -125,18 +125,34 @@ def synth_weights(torch, N, K, seed, device):
     return qw, sw
 
 
+_CPU_STATE = {}
+
+
 def cpu_baseline(sample_rows=None, threads=None, budget_s=12.0):
-    """The oracle (CPU restatement of the reference arithmetic) on a bounded sample: the first
-    `rows` tokens of the same workload against the full weight matrix."""
+    """CPU baselines on a bounded sample: the first `rows` tokens of the same workload against the full weight
+    matrix, on all host cores. Two implementations of the reference's arithmetic are timed:
+      reference-python : the reference's PyTorch fake-quant / integer-matmul path restated in torch ops
+                         (oracle/torch_path.py: per-token scale, round/clamp, pack_i4, unpack_i4, the integer
+                         contraction as a float matmul, fp16 dequant) -- the headline `value`;
+      port             : the C restatement of the reference's CUDA kernels (oracle/duq_oracle.c, OpenMP).
+    The weights are unpacked once outside the timed region in the torch path (a module holds its weights
+    prepared); the C port reads the packed weights."""
     import numpy as np
+    import torch
     from oracle import oracle as o
+    from oracle import torch_path as tp
     threads = threads or os.cpu_count()
     os.environ["OMP_NUM_THREADS"] = str(threads)
-    rng = np.random.default_rng(0)
-    qw = rng.integers(0, 256, (N_OUT, K_IN // 2), dtype=np.uint8)
-    sw = (0.002 + 0.01 * rng.random(N_OUT)).astype(np.float16)
+    torch.set_num_threads(threads)
+    state = _CPU_STATE   # weights are synthesised once per process
+    if "qw" not in state:
+        rng0 = np.random.default_rng(0)
+        state["qw"] = rng0.integers(0, 256, (N_OUT, K_IN // 2), dtype=np.uint8)
+        state["sw_np"] = (0.002 + 0.01 * rng0.random(N_OUT)).astype(np.float16)
+    qw, sw = state["qw"], state["sw_np"]
+    rng = np.random.default_rng(1)
 
-    def run(rows):
+    def run_port(rows):
         x = rng.standard_normal((rows, K_IN)).astype(np.float16)
         t0 = time.perf_counter()
         s = o.sym_scales(x)
@@ -145,14 +161,28 @@ def cpu_baseline(sample_rows=None, threads=None, budget_s=12.0):
         o.sym_dequant(acc, s, sw)
         return time.perf_counter() - t0
 
+    def run_torch(rows):
+        if "wf" not in state:
+            state["wf"] = tp.unpack_i4(torch.from_numpy(qw)).float()
+            state["sw"] = torch.from_numpy(sw)
+        x = torch.from_numpy(rng.standard_normal((rows, K_IN)).astype(np.float16))
+        t0 = time.perf_counter()
+        tp.linear_w4a4_sym(x, state["wf"], state["sw"])
+        return time.perf_counter() - t0
+
     if sample_rows is None:
-        t = run(4)
+        t = run_port(4)
         sample_rows = int(max(4, min(512, 4 * budget_s / max(t, 1e-3))))
-    t = run(sample_rows)
-    tops = 2.0 * sample_rows * N_OUT * K_IN / t / 1e12
-    return {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port",
-            "sample": f"first {sample_rows} of {M_TOK} tokens x full {K_IN}->{N_OUT} layer (quantize+int4 matmul+dequant), "
-                      f"{t:.2f} s, oracle/duq_oracle.c with OpenMP"}, t, sample_rows
+    t_port = run_port(sample_rows)
+    run_torch(min(sample_rows, 64))   # first call pays the one-off weight unpack and thread start-up
+    t_torch = run_torch(sample_rows)
+    tops = lambda t: 2.0 * sample_rows * N_OUT * K_IN / t / 1e12
+    return {"value": tops(t_torch), "unit": "TOPS", "cores": threads, "kind": "reference-python",
+            "sample": f"first {sample_rows} of {M_TOK} tokens x full {K_IN}->{N_OUT} layer (per-token scale, quantize, pack/unpack, "
+                      f"integer matmul as float matmul, fp16 dequant) in torch on the host cores, {t_torch:.2f} s; the figure is normalised "
+                      "to TOPS, so it is a sample of the workload, not the whole 4096-token step",
+            "port": {"value": tops(t_port), "unit": "TOPS", "kind": "port", "seconds": round(t_port, 3),
+                     "what": "oracle/duq_oracle.c (C restatement of the reference's CUDA kernels, OpenMP) on the same sample"}}, t_torch, sample_rows
 
 
 def run_reference(args):
@@ -170,8 +200,9 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "w4a4_linear_tops_M4096", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4xint4->int32, fp16 epilogue", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sample_rows_per_step": rows, "note": "CPU path of the reference arithmetic "
-                       "(oracle port); the reference's CUDA kernels need a GPU and are not the CPU arm"},
+            "config": {"workload": WORKLOAD, "sample_rows_per_step": rows, "note": "CPU arm: the reference's PyTorch fake-quant / "
+                       "integer-matmul path restated in torch (oracle/torch_path.py) on a token sample of the workload, all host cores; the C "
+                       "port of the reference's CUDA kernels is timed beside it (cpu_baseline.port); the reference's CUDA kernels need a GPU"},
             "cpu_baseline": cb,
             "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -179,12 +210,15 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------------------------
 def time_decode(torch, L, device, peaks, Ms=(1, 16)):
-    """us/layer of the small-M kernel on the Llama-2-7B shapes with COLD weights: a CUDA graph
-    walks over enough distinct weight buffers to exceed L2 (126 MB) before reusing one."""
+    """us/layer at M <= 16 tokens on the Llama-2-7B shapes with COLD weights: a CUDA graph walks over enough
+    distinct weight buffers to exceed L2 (126 MB) before reusing one. Two kinds of rows:
+      what = "layer"             the whole W4A4 linear, fp16 activations in -> fp16 out, through
+                                 duq4_linear_w4a4_from_fp16 (activation quantizer included; one launch per layer)
+      what = "gemv+dequant only" pre-quantized codes in -> fp16 out through duq4_linear_w4a4 (the quantizer is NOT
+                                 in the timed region)
+    each with the serving options on (weights declared static so consecutive layers overlap their weight
+    streaming, next-layer L2 hint) and, for the layer rows, also with both off ("plain")."""
     out = []
-    st = L.current_stream()
-    # weights are inference parameters: let consecutive layers overlap their weight streaming
-    prev = L.cdll.duq4_set_static_weights(0 if os.environ.get("DUQ4_BENCH_NO_PDL") else 1)
     for (K, N) in DECODE_SHAPES:
         wbytes = N * K // 2
         ncopy = max(4, int(320e6 // wbytes) + 1)
@@ -193,49 +227,58 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
         for M in Ms:
             qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=device)
             sa = (torch.rand(M, device=device) * 0.1 + 0.01).to(torch.float16)
+            x = torch.randn((M, K), device=device).to(torch.float16)
             y = torch.empty((M, N), dtype=torch.float16, device=device)
-            # one epilogue per layer: each names the NEXT layer's weights (L2 prefetch hint), as a model
-            # runner that knows its layer order would
-            epis = []
-            for c in range(ncopy):
-                epis.append(L.make_epilogue("sym", sa, None, sw, next_weights=None if os.environ.get("DUQ4_BENCH_NO_HINT")
-                                            else W[(c + 1) % ncopy]))
+            ws_bytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+            ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=device)
             passes = -(-100 // ncopy)   # at least 100 layer invocations per graph replay
+            for what, serving in (("layer", True), ("layer", False), ("gemv+dequant only", True)):
+                if os.environ.get("DUQ4_BENCH_NO_PDL") and serving:
+                    continue
+                # one epilogue per layer: each names the NEXT layer's weights (L2 prefetch hint), as a model
+                # runner that knows its layer order would
+                epis = [L.make_epilogue("sym", None if what == "layer" else sa, None, sw,
+                                        next_weights=W[(c + 1) % ncopy] if serving and not os.environ.get("DUQ4_BENCH_NO_HINT") else None)
+                        for c in range(ncopy)]
+                prev = L.cdll.duq4_set_static_weights(1 if serving else 0)
 
-            def body():
-                for _ in range(passes):
-                    for c in range(ncopy):
-                        L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epis[c]),
-                               L.ptr(y), None, L.current_stream())
+                def body():
+                    for _ in range(passes):
+                        for c in range(ncopy):
+                            if what == "layer":
+                                L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), ctypes.c_void_p(W[c].data_ptr()), M, N, K, L.MODE_SYM, 1.0,
+                                       ctypes.byref(epis[c]), L.ptr(y), L.ptr(ws), ws.numel(), L.current_stream())
+                            else:
+                                L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epis[c]),
+                                       L.ptr(y), None, L.current_stream())
 
-            s = torch.cuda.Stream()
-            with torch.cuda.stream(s):
-                body()
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=s):
+                s = torch.cuda.Stream()
+                with torch.cuda.stream(s):
                     body()
-                for _ in range(3):
-                    g.replay()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 10
-                e0.record(s)
-                for _ in range(reps):
-                    g.replay()
-                e1.record(s)
-                torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy * passes)
-            gbs = wbytes / (us * 1e-6) / 1e9
-            out.append({"K": K, "N": N, "M": M, "us_per_layer": round(us, 3), "weight_GBps": round(gbs, 1),
-                        "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
-                        "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4), "cold_weight_buffers": ncopy,
-                        "layers_per_graph": ncopy * passes,
-                        "static_weights_overlap": not os.environ.get("DUQ4_BENCH_NO_PDL"),
-                        "next_layer_hint": not os.environ.get("DUQ4_BENCH_NO_HINT")})
-            del g
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=s):
+                        body()
+                    for _ in range(3):
+                        g.replay()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 10
+                    e0.record(s)
+                    for _ in range(reps):
+                        g.replay()
+                    e1.record(s)
+                    torch.cuda.synchronize()
+                L.cdll.duq4_set_static_weights(prev)
+                us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy * passes)
+                gbs = wbytes / (us * 1e-6) / 1e9
+                out.append({"K": K, "N": N, "M": M, "what": what, "options": "static weights + next-layer hint" if serving else "plain",
+                            "us_per_layer": round(us, 3), "weight_GBps": round(gbs, 1),
+                            "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                            "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4), "cold_weight_buffers": ncopy,
+                            "layers_per_graph": ncopy * passes, "launches_per_layer": 1})
+                del g
         del W
-    L.cdll.duq4_set_static_weights(prev)
     return out
 
 
@@ -335,6 +378,51 @@ def time_prefill_sweep(torch, L, device, Ms=(512, 2048, 4096, 8192)):
     return rows
 
 
+def time_weight_prelayout_ablation(torch, L, device):
+    """Headline layer (M=4096, 8192 -> 28672, symmetric) with the three operand formats the tensor-core kernel takes:
+      packed x packed      activations and weights as packed int4 (the reference's formats; both unpacked in the CTA pair)
+      int8 x packed        activations pre-unpacked by the fused quantizer, weights unpacked in the kernel (the default path)
+      int8 x int8 prelaid  weights re-laid out ONCE to int8 (duq4_weight_prelayout_i8, twice the bytes), no in-kernel unpack
+    Same result bits for all three; TOPS of the GEMM launch alone."""
+    M, K, N = M_TOK, K_IN, N_OUT
+    x = synth_activations(torch, M, K, seed=0, pinned=False).to(device)
+    qw, sw = synth_weights(torch, N, K, seed=1000, device=device)
+    a8 = torch.empty((M, K), dtype=torch.int8, device=device); a4 = torch.empty((M, K // 2), dtype=torch.uint8, device=device)
+    w8 = torch.empty((N, K), dtype=torch.int8, device=device)
+    sa = torch.empty(M, dtype=torch.float16, device=device)
+    y = torch.empty((M, N), dtype=torch.float16, device=device)
+    st = L.current_stream
+    L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
+    L.call("duq4_quantize_sym_fused", L.ptr(x), M, K, 1.0, L.ptr(a4), L.ptr(sa), st())
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(); L.call("duq4_weight_prelayout_i8", L.ptr(qw), N, K, L.ptr(w8), st()); t1.record(); torch.cuda.synchronize()
+    prelayout_ms = t0.elapsed_time(t1)
+    epi = L.make_epilogue("sym", sa, None, sw)
+    variants = {
+        "packed x packed": lambda: L.call("duq4_linear_w4a4", L.ptr(a4), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st()),
+        "int8 x packed": lambda: L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st()),
+        "int8 x int8 prelaid": lambda: L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(y), None, st()),
+    }
+    res, ref = {}, None
+    for name, fn in variants.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        bits = y.view(torch.int16).clone()
+        same = True if ref is None else bool(torch.equal(bits, ref))
+        ref = bits if ref is None else ref
+        res[name] = {"ms": round(ms, 4), "tops": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1), "same_bits_as_first": same}
+    res["one_off_prelayout_ms"] = round(prelayout_ms, 4)
+    res["weight_bytes_packed_vs_prelaid"] = [N * K // 2, N * K]
+    return res
+
+
 def time_batched(torch, L, device):
     """B = 8 independent 4096 x 4096 weight sets over M = 256 tokens each, one batched launch with
     the asymmetric dequant in the epilogue."""
@@ -395,15 +483,33 @@ def run_profile_case(args):
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         for _ in range(4):
             L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
-    elif args.profile_case in ("decode", "decode16"):
-        M, N, K = (1 if args.profile_case == "decode" else 16), 22016, 4096
+    elif args.profile_case == "gemm_prelaid":
+        M, N, K = 2048, 8192, 8192
+        x = torch.randn((M, K), device=dev).half()
+        qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev)
+        a8 = torch.empty((M, K), dtype=torch.int8, device=dev); w8 = torch.empty((N, K), dtype=torch.int8, device=dev)
+        sa = torch.empty(M, dtype=torch.float16, device=dev); sw = torch.rand(N, device=dev).half()
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        epi = L.make_epilogue("sym", sa, None, sw)
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
+        L.call("duq4_weight_prelayout_i8", L.ptr(qw), N, K, L.ptr(w8), st())
+        for _ in range(4):
+            L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
+    elif args.profile_case in ("decode", "decode16", "decode_layer"):
+        M, N, K = (16 if args.profile_case == "decode16" else 1), 22016, 4096
         W = torch.randint(0, 256, (8, N, K // 2), dtype=torch.uint8, device=dev)  # 8 x 45 MB: cold in L2
         qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev)
+        x = torch.randn((M, K), device=dev).half()
         sa = torch.rand(M, device=dev).half(); sw = torch.rand(N, device=dev).half()
         y = torch.empty((M, N), dtype=torch.float16, device=dev)
         epi = L.make_epilogue("sym", sa, None, sw)
+        ws = torch.empty(max(256, L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)), dtype=torch.uint8, device=dev)
         for c in range(8):
-            L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
+            if args.profile_case == "decode_layer":   # fp16 tokens in: the kernel quantizes them itself (one launch)
+                L.call("duq4_linear_w4a4_from_fp16", L.ptr(x), ctypes.c_void_p(W[c].data_ptr()), M, N, K, L.MODE_SYM, 1.0, ctypes.byref(epi),
+                       L.ptr(y), L.ptr(ws), ws.numel(), st())
+            else:
+                L.call("duq4_linear_w4a4", L.ptr(qa), ctypes.c_void_p(W[c].data_ptr()), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
     elif args.profile_case == "quantize":
         M, K = 4096, 8192
         xs = [torch.randn((M, K), device=dev).half() for _ in range(4)]  # 4 x 64 MB
@@ -635,6 +741,7 @@ def run_ours(args):
             line["decode"] = time_decode(torch, L, device, peaks)
             line["mlp_block"] = time_mlp_block(torch, L, device)
             line["batched"] = time_batched(torch, L, device)
+            line["weight_prelayout_ablation"] = time_weight_prelayout_ablation(torch, L, device)
             line["prefill_sweep"] = time_prefill_sweep(torch, L, device)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()[0]
@@ -659,7 +766,7 @@ def main():
     ap.add_argument("--no-multicast", action="store_true", help="N>1, fused gather: one plain store per peer instead of multimem.st")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "decode", "decode16", "quantize", "silu", "skinny"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_prelaid", "decode", "decode16", "decode_layer", "quantize", "silu", "skinny"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.warmup < 3:

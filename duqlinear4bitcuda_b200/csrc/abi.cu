@@ -9,11 +9,16 @@ namespace duq4 {
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true);
 int tma_map_cache_entries();
+bool gemv_fused_quant_fits(const void *x, uint32_t M, uint32_t K);
+int gemv_w4a4_from_fp16_launch(const void *x, int act_mode, float clip, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
+                               const EpiParams &p, void *out, cudaStream_t st, bool cache_maps);
 int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
                    const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps = true,
                    uint32_t a_rows = 0);
 int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_t M, uint32_t inter, uint32_t K,
                             const EpiParams &p, void *h_out, cudaStream_t st);
+int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
+                            int32_t *acc_out, cudaStream_t st);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
 int peer_status_read(int32_t *out);
@@ -163,6 +168,20 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, A_i8, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
 }
 
+int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, const duq4_epilogue *epi,
+                             void *out, int32_t *acc_out, void *stream) {
+    EpiParams p;
+    int rc = check_epi(epi, N, true, &p);
+    if (rc) return rc;
+    if (!A_i8 || !W_i8) return DUQ4_ERR_NULL;
+    if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
+    if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
+    if (((reinterpret_cast<uintptr_t>(A_i8) | reinterpret_cast<uintptr_t>(W_i8)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    return gemm_tc2_launch_prelaid(A_i8, W_i8, M, N, K, p, out, acc_out, (cudaStream_t)stream);
+}
+
 int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W, uint32_t M, uint32_t inter, uint32_t K,
                                   const duq4_epilogue *epi, void *h_out, void *stream) {
     if (!A || !W || !epi) return DUQ4_ERR_NULL;
@@ -212,6 +231,9 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
     const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
     const bool act_asym = act_mode == DUQ4_MODE_ASYM || act_mode == DUQ4_MODE_ASYM_DUAL;
     if (epi_asym && !act_asym) return DUQ4_ERR_MODE;  // an asymmetric epilogue needs per-token zero-points
+    // up to 16 tokens: ONE launch -- every CTA of the small-M kernel quantizes the tokens into its own shared
+    // memory; codes and per-token scales never reach the workspace
+    if (small && gemv_fused_quant_fits(x, M, K)) return gemv_w4a4_from_fp16_launch(x, act_mode, clip_ratio, W, M, N, K, p, out, st, true);
     rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, codes, s1, z1, s2, z2, st, !small);
     if (rc) return rc;
     p.s_row = (const __half *)s1;
@@ -271,6 +293,8 @@ int duq4_linear_w4a4_from_fp16_static(const void *x, const uint8_t *W, uint32_t 
     const bool small = M <= kSmallM;
     void *s1 = ws + off, *z1 = ws + off + vec, *s2 = ws + off + 2 * vec, *z2 = ws + off + 3 * vec;
     cudaStream_t st = (cudaStream_t)stream;
+    // up to 16 tokens: one launch that needs no scratch at all (see duq4_linear_w4a4_from_fp16)
+    if (small && gemv_fused_quant_fits(x, M, K)) return gemv_w4a4_from_fp16_launch(x, act_mode, clip_ratio, W, M, N, K, p, out, st, false);
     // Nothing in the scratch has to start at zero: the quantizer overwrites every code byte and
     // every per-token vector entry the GEMM reads before the GEMM reads it.
     rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, ws, s1, z1, s2, z2, st, !small);

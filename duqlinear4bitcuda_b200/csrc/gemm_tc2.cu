@@ -51,7 +51,11 @@ constexpr int kUnpackedStage = (BMH + BNH) * BKE;   // 32 KiB: A tile then W hal
 constexpr int kStageOutWarp = 32 * 144;
 // APK = activations arrive packed (int4, the reference's format) and are unpacked here too;
 // otherwise they arrive as the quantizer's tensor-core-ready int8 and go straight into the MMA ring.
-template <bool APK, bool GU = false>
+// WI8 = the weights arrive pre-laid-out as int8 as well (duq4_weight_prelayout_i8: 16 * code, K permuted like
+// the activations): both operands go straight from TMA into the MMA ring and the unpack warps have nothing to do.
+// Twice the weight bytes from HBM / L2, no shared-memory unpack traffic -- the measured alternative to the
+// in-kernel unpack.
+template <bool APK, bool GU = false, bool WI8 = false>
 struct Cfg2 {
     static constexpr int EPI = GU ? 8 : 4;    // epilogue warps
     static constexpr int UWN = GU ? 4 : 8;    // unpack warps
@@ -60,8 +64,8 @@ struct Cfg2 {
     // (L2 / HBM latency) while a k-step of MMA work takes 0.3-0.4 us, so the packed ring has to
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
-    static constexpr int NPK = GU ? (APK ? 3 : 5) : (APK ? 4 : 5);
-    static constexpr int NUP = (APK || GU) ? 4 : 5;
+    static constexpr int NPK = WI8 ? 1 : (GU ? (APK ? 3 : 5) : (APK ? 4 : 5));
+    static constexpr int NUP = WI8 ? 6 : ((APK || GU) ? 4 : 5);
     static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
     static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
@@ -223,10 +227,11 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
     }
 }
 
-template <bool APK, bool GU>
+template <bool APK, bool GU, bool WI8>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
-    using C2 = Cfg2<APK, GU>;
+    static_assert(!WI8 || (!APK && !GU), "pre-laid-out weights go with int8 activations and the plain epilogue");
+    using C2 = Cfg2<APK, GU, WI8>;
     constexpr int NPK = C2::NPK, NUP = C2::NUP, kPackedStage = C2::kPackedStage;
     constexpr int EPI = C2::EPI, UW = C2::UWN, kColTerms = C2::kColTerms;
     extern __shared__ uint8_t smem_raw[];
@@ -266,7 +271,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(pk_empty(s), UW);
         }
         for (int s = 0; s < 6; ++s) {
-            mbar_init(up_full(s), (APK ? 0 : 1) + 2 * UW);
+            mbar_init(up_full(s), WI8 ? 1 : (APK ? 0 : 1) + 2 * UW);
             mbar_init(up_empty(s), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -304,6 +309,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 uint32_t b, tm, tn;
                 tile_coords(tile, b, tm, tn);
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                    if (WI8) {   // this CTA's half of the int8 W block straight into the MMA ring, credited to the leader
+                        const uint32_t u = it % NUP, uph = (it / NUP) & 1;
+                        if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 1))) break;
+                        tma_load_3d_pair(up0 + u * kUnpackedStage + BMH * BKE, &tmB, mapa(up_full(u), 0), ks * BKE, tn * bn + rank * bnh, b);
+                        continue;
+                    }
                     const uint32_t s = it % NPK, ph = (it / NPK) & 1;
                     if (!(ok = mbar_wait(pk_empty(s), ph ^ 1, abortp, &g_tc2_status, 1))) break;
                     mbar_expect_tx(pk_full(s), ((APK ? BMH : 0) + bnh) * (BKE / 2));
@@ -333,7 +344,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                     const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                     if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 7))) break;
-                    if (rank == 0) mbar_expect_tx(up_full(u), 2 * BMH * BKE);   // both CTAs' A tiles
+                    if (rank == 0) mbar_expect_tx(up_full(u), 2 * BMH * BKE + (WI8 ? 2 * bnh * BKE : 0));   // both CTAs' A tiles (and int8 W halves)
                     tma_load_3d_pair(up0 + u * kUnpackedStage, &tmA, mapa(up_full(u), 0), ks * BKE, tm * 256 + rank * BMH, b);
                 }
             }
@@ -417,7 +428,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
         }
-    } else if (warp < kLastWarp) {
+    } else if (!WI8 && warp < kLastWarp) {
         // ---------------- unpack warps: this CTA's packed W half (and packed A rows) -> swizzled int8 ----------------
         const int ut = (warp - 2 - EPI) * 32 + lane;
         const int kChunks = (int)((APK ? BMH + bnh : bnh) * 4);   // 16-byte chunks of packed rows in a stage
@@ -486,12 +497,12 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
     return rounds(224) <= rounds(256) ? 224u : 256u;
 }
 
-template <bool APK, bool GU = false>
+template <bool APK, bool GU = false, bool WI8 = false>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
                    void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0, bool cache_maps = true) {
     using namespace tc2;
-    constexpr int kSmem2 = Cfg2<APK, GU>::kSmem;
-    auto *kernel = gemm_tc2_kernel<APK, GU>;
+    constexpr int kSmem2 = Cfg2<APK, GU, WI8>::kSmem;
+    auto *kernel = gemm_tc2_kernel<APK, GU, WI8>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
     static DeviceOnce once;
@@ -540,7 +551,8 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma, cache_maps)
                  : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma, cache_maps);
     if (rc) return rc;
-    rc = tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb, cache_maps);
+    rc = WI8 ? tma_map_bytes_3d(B, K, N, batch, BKE, a.bn / 2, true, &mb, cache_maps)
+             : tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb, cache_maps);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
     const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
@@ -571,6 +583,13 @@ int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uin
                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
     return a_packed ? launch2<true>(A, B, M, N, K, batch, p, out, acc_out, st, 0, cache_maps)
                     : launch2<false>(A, B, M, N, K, batch, p, out, acc_out, st, 0, cache_maps);
+}
+
+// Both operands int8 in the tensor-core-ready layout (A from duq4_quantize_fused_i8, W from
+// duq4_weight_prelayout_i8). DUQ4_ERR_DEVICE when the device cannot co-schedule CTA pairs.
+int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
+                            int32_t *acc_out, cudaStream_t st) {
+    return launch2<false, false, true>(A, W_i8, M, N, K, 1, p, out, acc_out, st, 0, true);
 }
 
 // SiLU-gated gate/up projection: W packed [2*I, K/2] (gate rows, then up rows), per-channel vectors of

@@ -19,10 +19,44 @@
 
 #include "duq_common.cuh"
 #include "duq_ptx.cuh"
+#include "quant_device.cuh"
 
 namespace duq4 {
 
 constexpr int kGemvWarps = 8;
+
+// Activation quantizer inside the linear kernel (template flag FQ): the kernel receives the fp16 tokens instead of
+// packed codes; every CTA quantizes them into its own shared memory (quantize_tokens_to_smem) once its first
+// batch of weight loads is in flight, so codes and per-token scales never travel through global memory and the
+// layer is ONE launch. Replaces the reference's separate quantize launch (src/kernels/quant.cu:48-61 after the
+// torch ops of qlinear4bit/nn/quantizer.py:10-16, :24-35) in front of the GEMM.
+struct FusedQ {
+    const __half *x;   // fp16 [M, K]
+    int act_mode;      // DUQ4_MODE_SYM .. ASYM_DUAL
+    float clip;
+};
+// Shared-memory layout of the FQ variants (dynamic shared memory): scratch, M code rows, then the fp16 staging
+// copy of the tokens.
+__host__ __device__ constexpr uint32_t fq_code_stride(uint32_t kb) { return kb + 64; }   // +64: the 8 tokens a quarter-warp reads fall into distinct banks
+__host__ __device__ constexpr uint32_t fq_scratch_bytes() { return (uint32_t)((sizeof(TokenQuantScratch) + 15) / 16 * 16); }
+__host__ __device__ inline uint32_t fq_smem_bytes(uint32_t M, uint32_t kb) {
+    return fq_scratch_bytes() + M * fq_code_stride(kb) + M * kb * 4u;
+}
+__device__ __forceinline__ void fq_quantize(const FusedQ &fq, uint32_t M, uint32_t K, uint8_t *codes, uint32_t stride, TokenQuantScratch &sc) {
+    uint8_t *raw = codes + (size_t)M * stride;   // staging copy of the fp16 tokens, behind the code rows
+    switch (fq.act_mode) {
+        case QSYM: quantize_tokens_to_smem<QSYM>(fq.x, M, K, fq.clip, raw, codes, stride, sc, kGemvWarps * 32); break;
+        case QSYM_DUAL: quantize_tokens_to_smem<QSYM_DUAL>(fq.x, M, K, fq.clip, raw, codes, stride, sc, kGemvWarps * 32); break;
+        case QASYM: quantize_tokens_to_smem<QASYM>(fq.x, M, K, fq.clip, raw, codes, stride, sc, kGemvWarps * 32); break;
+        default: quantize_tokens_to_smem<QASYM_DUAL>(fq.x, M, K, fq.clip, raw, codes, stride, sc, kGemvWarps * 32); break;
+    }
+}
+// 16 bytes of token codes: global memory (read-only path) or the CTA's shared memory
+template <bool FQ>
+__device__ __forceinline__ uint4 ld_codes(const uint4 *p) {
+    if (FQ) return *p;
+    return __ldg(p);
+}
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -69,13 +103,19 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     return v;
 }
 
-// R  = 16-row weight groups per CTA (1 or 2); TH = token halves (1: M <= 8, 2: M <= 16).
-template <int R, int TH>
+// R  = 16-row weight groups per CTA (1 or 2); TH = token halves (1: M <= 8, 2: M <= 16); FQ: A is unused and the
+// tokens come as fp16 through `fq` (see FusedQ).
+template <int R, int TH, bool FQ>
 __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_t *__restrict__ A,
                                                                     const uint8_t *__restrict__ W, uint32_t M, uint32_t N,
                                                                     uint32_t K, EpiParams p, __half *__restrict__ out,
-                                                                    int32_t *__restrict__ acc_out) {
-    {   // batched launch: blockIdx.y selects one of the independent problems
+                                                                    int32_t *__restrict__ acc_out, FusedQ fq) {
+    extern __shared__ __align__(16) uint8_t fq_smem[];
+    TokenQuantScratch &qsc = *reinterpret_cast<TokenQuantScratch *>(fq_smem);
+    uint8_t *const qcodes = fq_smem + fq_scratch_bytes();
+    const uint32_t kb = K >> 1;           // bytes per packed row
+    const uint32_t a_stride = FQ ? fq_code_stride(kb) : kb;
+    if (!FQ) {   // batched launch: blockIdx.y selects one of the independent problems
         const uint32_t b = blockIdx.y;
         A += (size_t)b * M * (K >> 1);
         W += (size_t)b * N * (K >> 1);
@@ -86,7 +126,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
     __shared__ int red[kGemvWarps][16][16 * R + 1];  // [warp][token][row]; +1 pads the row stride
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t kb = K >> 1;           // bytes per packed row
     const uint32_t nchunk = kb >> 4;      // 16-byte chunks per row
     const uint32_t nstep = (nchunk + 3) >> 2;
     const uint32_t row0 = blockIdx.x * (16 * R);
@@ -113,7 +152,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
     for (int h = 0; h < TH; ++h) {
         uint32_t m = g + 8 * h;
         aok[h] = m < M;
-        ap[h] = reinterpret_cast<const uint4 *>(A + (size_t)(aok[h] ? m : 0) * kb);
+        ap[h] = reinterpret_cast<const uint4 *>((FQ ? qcodes : A) + (size_t)(aok[h] ? m : 0) * a_stride);
     }
 
     // Weights are parameters: with the "static weights" option on, the launch carries the
@@ -133,6 +172,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         if (p.mode != DUQ4_MODE_NONE && n_mine < N) ct_mine = load_col_terms(p, n_mine);
     }
     bool waited = false;
+    if (FQ) {
+        // The tokens are quantized before this thread holds any weight registers; meanwhile L2 is asked for the
+        // CTA's weight rows (one bulk prefetch per row), so the DRAM pipe works while the tokens are coded.
+        if (threadIdx.x < 16 * R && row0 + threadIdx.x < N && (kb & 15u) == 0)
+            l2_prefetch_bulk(W + (size_t)(row0 + threadIdx.x) * kb, kb);
+        if (threadIdx.x == 0 && blockIdx.y == 0) prefetch_next_weights(p, blockIdx.x, gridDim.x);
+        pdl_wait();
+        fq_quantize(fq, M, K, qcodes, a_stride, qsc);   // every warp takes part (named barrier inside)
+        waited = true;
+    }
     constexpr int U = 4;  // k-steps in flight per warp
     for (uint32_t s0 = warp * U; s0 < nstep; s0 += kGemvWarps * U) {
         uint4 wv[U][R][2], av[U][TH];
@@ -146,7 +195,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
                 wv[u][r][1] = ok ? ldg_stream(wp[r][1] + ch) : make_uint4(0, 0, 0, 0);
             }
         }
-        if (!waited) {
+        if (!waited) {   // the first batch of weight loads is in flight before anything waits
             if (threadIdx.x == 0 && blockIdx.y == 0) prefetch_next_weights(p, blockIdx.x, gridDim.x);
             pdl_wait();
             waited = true;
@@ -156,7 +205,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
             uint32_t ch = (s0 + u) * 4 + t;
             bool ok = ch < nchunk;
 #pragma unroll
-            for (int h = 0; h < TH; ++h) av[u][h] = (ok && aok[h]) ? __ldg(ap[h] + ch) : make_uint4(0, 0, 0, 0);
+            for (int h = 0; h < TH; ++h) av[u][h] = (ok && aok[h]) ? ld_codes<FQ>(ap[h] + ch) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -177,7 +226,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         }
     }
 
-    if (!waited) pdl_wait();
+    if (!waited) pdl_wait();   // a warp without a K slice of its own (short rows)
     // Cross-warp (split-K) reduction. Fragment element i of acc[r][h]: weight row
     // 16r + g + 8*(i>>1), token 8h + 2t + (i&1).
 #pragma unroll
@@ -188,6 +237,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
             for (int i = 0; i < 4; ++i) red[warp][8 * h + 2 * t + (i & 1)][16 * r + g + 8 * (i >> 1)] = acc[r][h][i];
     __syncthreads();
 
+    const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
     for (uint32_t o = threadIdx.x; o < 16u * R * 8u * TH; o += blockDim.x) {
         uint32_t nl = o % (16 * R), m = o / (16 * R);
         uint32_t n = row0 + nl;
@@ -198,8 +248,15 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
         s >>= 8;  // exact: s is a multiple of 256
         if (acc_out) acc_out[(size_t)m * N + n] = s;
         if (p.mode != DUQ4_MODE_NONE) {
-            __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
-            const __half v = dequant_one(p.mode, s, p.s_row[m], zr, ct_mine);   // nl == threadIdx.x % (16*R) for every o of this thread
+            __half sr, zr = __ushort_as_half(0);
+            if (FQ) {   // the per-token terms this CTA computed itself
+                sr = qsc.rowq[m].s1;
+                if (epi_asym) zr = qsc.rowq[m].z1;
+            } else {
+                sr = p.s_row[m];
+                if (p.z_row) zr = p.z_row[m];
+            }
+            const __half v = dequant_one(p.mode, s, sr, zr, ct_mine);   // nl == threadIdx.x % (16*R) for every o of this thread
             const size_t off = (size_t)m * p.ldo + n;
             if (p.n_peers == 0) {
                 out[off] = v;
@@ -236,10 +293,10 @@ struct GemvSmem {
     static constexpr int kBytes = 1024 + kStages * kStageBytes + kRedInts * 4 + 2 * kStages * 8 + 16;
 };
 
-template <int R, int TH>
+template <int R, int TH, bool FQ>
 __global__ void __launch_bounds__((kGemvWarps + 1) * 32, 1)
 gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__restrict__ A, uint32_t M, uint32_t N,
-                     uint32_t K, uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0) {
+                     uint32_t K, uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0, FusedQ fq) {
     using namespace ptx;
     using S = GemvSmem<R>;
     extern __shared__ uint8_t smem_raw[];
@@ -247,6 +304,10 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
     const uint32_t raw = smem_u32(smem_raw), base = (raw + 1023u) & ~1023u;
     int *red = reinterpret_cast<int *>(smem_raw + (base - raw) + S::kStages * S::kStageBytes);
     const uint32_t bar0 = base + S::kStages * S::kStageBytes + S::kRedInts * 4;
+    // FQ: scratch and code rows follow the barriers (S::kBytes leaves 16 spare bytes after them)
+    uint8_t *const fq_base = smem_raw + (base - raw) + S::kStages * S::kStageBytes + S::kRedInts * 4 + 2 * S::kStages * 8 + 16;
+    TokenQuantScratch &qsc = *reinterpret_cast<TokenQuantScratch *>(fq_base);
+    uint8_t *const qcodes = fq_base + fq_scratch_bytes();
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (S::kStages + s); };
 
@@ -303,9 +364,12 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
         uint32_t it = 0, lu = 0;
         bool ok = true;
         pdl_wait();   // activations come from the previous grid; outputs may still be read by it
+        const uint32_t a_stride = FQ ? fq_code_stride(kb) : kb;
+        if (FQ) fq_quantize(fq, M, K, qcodes, a_stride, qsc);   // the producer warp keeps filling the ring meanwhile (one CTA per SM: registers to spare)
+        const bool epi_asym = p0.mode == DUQ4_MODE_ASYM || p0.mode == DUQ4_MODE_ASYM_DUAL;
         for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, ++lu) {
             const uint32_t b = u / blocks_per_b, row0 = (u % blocks_per_b) * S::kRows;
-            const uint8_t *Ab = A + (size_t)b * M * kb;
+            const uint8_t *Ab = FQ ? qcodes : A + (size_t)b * M * kb;
             int acc[R][TH][4];
 #pragma unroll
             for (int r = 0; r < R; ++r)
@@ -324,9 +388,9 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
                 for (int h = 0; h < TH; ++h) {
                     const uint32_t m = g + 8 * h;
                     const bool lok = kin && m < M;
-                    const uint4 *ap = reinterpret_cast<const uint4 *>(Ab + (size_t)(lok ? m : 0) * kb + (lok ? kbyte : 0));
-                    tk[h][0] = lok ? __ldg(ap) : make_uint4(0, 0, 0, 0);
-                    tk[h][1] = lok ? __ldg(ap + 1) : make_uint4(0, 0, 0, 0);
+                    const uint4 *ap = reinterpret_cast<const uint4 *>(Ab + (size_t)(lok ? m : 0) * a_stride + (lok ? kbyte : 0));
+                    tk[h][0] = lok ? ld_codes<FQ>(ap) : make_uint4(0, 0, 0, 0);
+                    tk[h][1] = lok ? ld_codes<FQ>(ap + 1) : make_uint4(0, 0, 0, 0);
                 }
                 if (ok) ok = mbar_wait(full(s), ph, abortp, &g_gemv_status, 2);
                 if (ok && ks * kStageKBytes + warp * 128u < kb) {
@@ -378,8 +442,15 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
                 if (acc0) acc0[((size_t)b * M + m) * N + n] = sum;
                 if (p.mode != DUQ4_MODE_NONE) {
                     ColTerms ct = load_col_terms(p, n);
-                    __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
-                    const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, ct);
+                    __half sr, zr = __ushort_as_half(0);
+                    if (FQ) {
+                        sr = qsc.rowq[m].s1;
+                        if (epi_asym) zr = qsc.rowq[m].z1;
+                    } else {
+                        sr = p.s_row[m];
+                        if (p.z_row) zr = p.z_row[m];
+                    }
+                    const __half v = dequant_one(p.mode, sum, sr, zr, ct);
                     const size_t off = ((size_t)b * M + m) * p.ldo + n;
                     if (p.n_peers == 0) {
                         out0[off] = v;
@@ -402,19 +473,33 @@ int tma_map_bytes_3d(const void *ptr, uint64_t kbytes, uint64_t rows, uint64_t b
 // while the previous kernel is still finishing.
 std::atomic<int> g_static_weights{0};
 
-template <int R, int TH>
+// Dynamic shared memory above the default 48 KiB needs an opt-in per kernel and device; the FQ variants ask for
+// the most they can use once.
+constexpr int kFqMaxDynSmem = 160 * 1024;
+
+template <int R, int TH, bool FQ>
 static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p,
-                      __half *out, int32_t *acc_out, cudaStream_t st) {
+                      __half *out, int32_t *acc_out, cudaStream_t st, const FusedQ &fq) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kGemvWarps * 32);
     cfg.stream = st;
+    if (FQ) {
+        static DeviceOnce once;
+        const int dev = current_device_slot();
+        if (dev < 0) return DUQ4_ERR_DEVICE;
+        int rc = once.run(dev, [] {
+            return (int)cudaFuncSetAttribute(gemv_w4a4_kernel<R, TH, FQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFqMaxDynSmem);
+        });
+        if (rc) return rc;
+        cfg.dynamicSmemBytes = fq_smem_bytes(M, K / 2);
+    }
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_kernel<R, TH>, A, W, M, N, K, p, out, acc_out);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_kernel<R, TH, FQ>, A, W, M, N, K, p, out, acc_out, fq);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)e;
@@ -422,15 +507,19 @@ static int launch_reg(dim3 grid, const uint8_t *A, const uint8_t *W, uint32_t M,
     return launch_status();
 }
 
-template <int R, int TH>
+constexpr int kMaxSmemPerCta = 232448;   // 227 KiB
+constexpr int kTmaFqMaxDynSmem = kMaxSmemPerCta - 512;   // the kernel also has a few bytes of static shared memory
+
+template <int R, int TH, bool FQ>
 static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms, bool cache_maps) {
+                      const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms, bool cache_maps, const FusedQ &fq) {
     using S = GemvSmem<R>;
     static DeviceOnce once;
     const int dev = current_device_slot();
     if (dev < 0) return DUQ4_ERR_DEVICE;
     int rc = once.run(dev, [] {
-        return (int)cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+        return (int)cudaFuncSetAttribute(gemv_w4a4_tma_kernel<R, TH, FQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FQ ? kTmaFqMaxDynSmem : S::kBytes);
     });
     if (rc) return rc;
     CUtensorMap mw;
@@ -441,14 +530,14 @@ static int launch_tma(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3((kGemvWarps + 1) * 32);
-    cfg.dynamicSmemBytes = S::kBytes;
+    cfg.dynamicSmemBytes = S::kBytes + (FQ ? fq_smem_bytes(M, K / 2) : 0);
     cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_tma_kernel<R, TH>, mw, A, M, N, K, batch, p, (__half *)out, acc_out);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_tma_kernel<R, TH, FQ>, mw, A, M, N, K, batch, p, (__half *)out, acc_out, fq);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)e;
@@ -481,10 +570,13 @@ struct GemvBuf {
     ColTerms ct;      // per-channel terms of this thread's output column (valid in a block's last batch)
 };
 
-template <int TH, int U>
+template <int TH, int U, bool FQ>
 __global__ void __launch_bounds__(kGemvWarps * 32, 2)
 gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ W, uint32_t M, uint32_t N, uint32_t K,
-                         uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0) {
+                         uint32_t batch, EpiParams p0, __half *__restrict__ out0, int32_t *__restrict__ acc0, FusedQ fq) {
+    extern __shared__ __align__(16) uint8_t fq_smem[];
+    TokenQuantScratch &qsc = *reinterpret_cast<TokenQuantScratch *>(fq_smem);
+    uint8_t *const qcodes = fq_smem + fq_scratch_bytes();
     __shared__ int red[2][kGemvWarps][16][17];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -513,9 +605,11 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
         const uint32_t n_mine = row0 + (threadIdx.x & 15);
         if (bi == nb - 1 && p0.mode != DUQ4_MODE_NONE && n_mine < N) buf.ct = load_col_terms(epi_for_batch(p0, b), n_mine);
     };
+    const uint32_t a_stride = FQ ? fq_code_stride(kb) : kb;
+    const bool epi_asym = p0.mode == DUQ4_MODE_ASYM || p0.mode == DUQ4_MODE_ASYM_DUAL;
     auto issue_a = [&](GemvBuf<TH, U> &buf, uint32_t f) {
         const uint32_t unit = unit_of(f), bi = f % nb;
-        const uint8_t *Ab = A + (size_t)(unit / blocks_per_b) * M * kb;
+        const uint8_t *Ab = FQ ? qcodes : A + (size_t)(unit / blocks_per_b) * M * kb;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint32_t ch = ((bi * kGemvWarps + warp) * U + u) * 4 + t;
@@ -523,7 +617,7 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
             for (int h = 0; h < TH; ++h) {
                 const uint32_t m = g + 8 * h;
                 const bool ok = ch < nchunk && m < M;
-                buf.a[u][h] = ok ? __ldg(reinterpret_cast<const uint4 *>(Ab + (size_t)m * kb) + ch) : make_uint4(0, 0, 0, 0);
+                buf.a[u][h] = ok ? ld_codes<FQ>(reinterpret_cast<const uint4 *>(Ab + (size_t)m * a_stride) + ch) : make_uint4(0, 0, 0, 0);
             }
         }
     };
@@ -573,8 +667,15 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
                 const EpiParams p = epi_for_batch(p0, b);
                 if (acc0) acc0[((size_t)b * M + m) * N + n] = sum;
                 if (p.mode != DUQ4_MODE_NONE) {
-                    __half zr = p.z_row ? p.z_row[m] : __ushort_as_half(0);
-                    const __half v = dequant_one(p.mode, sum, p.s_row[m], zr, buf.ct);   // nl == threadIdx.x & 15
+                    __half sr, zr = __ushort_as_half(0);
+                    if (FQ) {
+                        sr = qsc.rowq[m].s1;
+                        if (epi_asym) zr = qsc.rowq[m].z1;
+                    } else {
+                        sr = p.s_row[m];
+                        if (p.z_row) zr = p.z_row[m];
+                    }
+                    const __half v = dequant_one(p.mode, sum, sr, zr, buf.ct);   // nl == threadIdx.x & 15
                     const size_t off = ((size_t)b * M + m) * p.ldo + n;
                     if (p.n_peers == 0) {
                         out0[off] = v;
@@ -591,11 +692,25 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
     pdl_launch_dependents();
     GemvBuf<TH, U> b0, b1;
     if (total > 0) issue_w(b0, 0);   // weights are parameters: fetched before the previous grid has finished
+    if (FQ && total > 1) issue_w(b1, 1);   // FQ: the wait below is followed by the token quantizer, so both batches fly meanwhile
     if (threadIdx.x == 0) prefetch_next_weights(p0, blockIdx.x, gridDim.x);
+    if (FQ) {
+        // While the tokens are quantized this CTA holds one batch of weight loads in registers; L2 is asked for the
+        // rest of its first row blocks (one bulk prefetch per weight row) so that the DRAM pipe keeps working.
+        constexpr uint32_t kAhead = 3;   // row blocks
+        const uint32_t r = threadIdx.x & 15, j = threadIdx.x >> 4;
+        if (j < kAhead && j < my_units && (kb & 15u) == 0) {
+            const uint32_t unit = blockIdx.x + j * gridDim.x;
+            const uint32_t b = unit / blocks_per_b, row = (unit % blocks_per_b) * 16 + r;
+            if (row < N) l2_prefetch_bulk(W + ((size_t)b * N + row) * kb, kb);
+        }
+    }
     pdl_wait();                      // activations / outputs belong to the stream's earlier work
+    if (FQ) fq_quantize(fq, M, K, qcodes, a_stride, qsc);
     if (total > 0) issue_a(b0, 0);
+    if (FQ && total > 1) issue_a(b1, 1);
     for (uint32_t f = 0; f < total; f += 2) {
-        if (f + 1 < total) { issue_w(b1, f + 1); issue_a(b1, f + 1); }
+        if (f + 1 < total && !(FQ && f == 0)) { issue_w(b1, f + 1); issue_a(b1, f + 1); }
         consume(b0, f);
         if (f + 1 >= total) break;
         if (f + 2 < total) { issue_w(b0, f + 2); issue_a(b0, f + 2); }
@@ -603,9 +718,9 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
     }
 }
 
-template <int TH, int U>
+template <int TH, int U, bool FQ>
 static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                          const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms) {
+                          const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, int sms, const FusedQ &fq) {
     const uint32_t units = cdiv(N, 16) * batch;
     uint32_t grid = 2u * (uint32_t)sms;
     if (grid > units) grid = units;
@@ -613,12 +728,22 @@ static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kGemvWarps * 32);
     cfg.stream = st;
+    if (FQ) {
+        static DeviceOnce once;
+        const int dev = current_device_slot();
+        if (dev < 0) return DUQ4_ERR_DEVICE;
+        int rc = once.run(dev, [] {
+            return (int)cudaFuncSetAttribute(gemv_w4a4_persist_kernel<TH, U, FQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFqMaxDynSmem);
+        });
+        if (rc) return rc;
+        cfg.dynamicSmemBytes = fq_smem_bytes(M, K / 2);
+    }
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = g_static_weights.load(std::memory_order_relaxed) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_persist_kernel<TH, U>, A, W, M, N, K, batch, p, (__half *)out, acc_out);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_persist_kernel<TH, U, FQ>, A, W, M, N, K, batch, p, (__half *)out, acc_out, fq);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)e;
@@ -626,9 +751,11 @@ static int launch_persist(const uint8_t *A, const uint8_t *W, uint32_t M, uint32
     return launch_status();
 }
 
-int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
-                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
-    if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) != 0) return DUQ4_ERR_ALIGN;
+// Kernel choice for M <= 16 tokens. FQ = the tokens arrive as fp16 (`fq`, A unused, batch 1) and the kernel
+// quantizes them itself.
+template <bool FQ>
+static int gemv_dispatch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                         const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps, const FusedQ &fq) {
     const int sms = sm_count_current_device();
     static const int force = [] {
         const char *e = getenv("DUQ4_GEMV_VARIANT");   // debug: 0 = one-shot register kernel, 1 = TMA-streamed kernel, 3 = persistent register kernel
@@ -644,18 +771,24 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
     // ... and for any token count on the largest layers (>= 4 32-row blocks per SM; 4096->22016 at M=1 with the
     //    next-layer hint: 9.8 us TMA-streamed vs 10.1 us one-shot, while 4096->12288 is 6.15 vs 5.8)
     const bool huge_n = (uint64_t)cdiv(N, 32) * batch >= 4ull * sms;
-    const bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && big_n && (M > 8 || huge_n));
-    const bool persist = force >= 0 ? force == 3 : (!use_tma && (long_k || M > 8));
+    // FQ (one token in practice): the TMA-streamed kernel whenever the layer has two row blocks per SM -- its ring keeps
+    // 128 KiB of weights per SM in flight while the token is quantized (4096->12288: 7.2 us against 7.7 us persistent)
+    bool use_tma = force >= 0 ? force == 1 : (K / 2 >= 2048 && big_n && (FQ || M > 8 || huge_n));
+    const bool two = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
+    // FQ: the code rows must fit beside the TMA ring
+    if (FQ && use_tma && (two ? GemvSmem<2>::kBytes : GemvSmem<1>::kBytes) + fq_smem_bytes(M, K / 2) > (uint32_t)kTmaFqMaxDynSmem) use_tma = false;
+    // FQ: every CTA quantizes the tokens once, so only the persistent kernels (a CTA per SM or two, not a CTA per
+    // 16 rows) carry it: measured on 4096->12288 at one token, 13.2 us with 768 one-shot CTAs.
+    const bool persist = force >= 0 ? (force == 3 || (force == 1 && !use_tma) || (FQ && force == 0)) : (!use_tma && (FQ || long_k || M > 8));
     if (persist) {
-        if (M <= 8) return launch_persist<1, 4>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
-        return launch_persist<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms);
+        if (M <= 8) return launch_persist<1, 4, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, fq);
+        return launch_persist<2, 2, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, fq);
     }
     if (use_tma) {
-        const bool two = (uint64_t)cdiv(N, 32) * batch >= 2ull * sms;
-        if (M <= 8) return two ? launch_tma<2, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps)
-                               : launch_tma<1, 1>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps);
-        return two ? launch_tma<2, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps)
-                   : launch_tma<1, 2>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps);
+        if (M <= 8) return two ? launch_tma<2, 1, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps, fq)
+                               : launch_tma<1, 1, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps, fq);
+        return two ? launch_tma<2, 2, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps, fq)
+                   : launch_tma<1, 2, FQ>(A, W, M, N, K, batch, p, out, acc_out, st, sms, cache_maps, fq);
     }
     // Up to 8 tokens: 16-row CTAs (three per SM) -- more, smaller CTAs keep the weight stream smoother
     // across CTA boundaries than 32-row ones (4096->22016, M=1: 10.3 vs 10.8 us). 9..16 tokens: two row
@@ -664,8 +797,41 @@ int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
     const uint32_t rows_per_cta = r2 ? 32 : 16;
     dim3 grid(cdiv(N, rows_per_cta), batch);
     __half *o = (__half *)out;
-    if (M <= 8) return r2 ? launch_reg<2, 1>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 1>(grid, A, W, M, N, K, p, o, acc_out, st);
-    return r2 ? launch_reg<2, 2>(grid, A, W, M, N, K, p, o, acc_out, st) : launch_reg<1, 2>(grid, A, W, M, N, K, p, o, acc_out, st);
+    if (M <= 8) return r2 ? launch_reg<2, 1, FQ>(grid, A, W, M, N, K, p, o, acc_out, st, fq) : launch_reg<1, 1, FQ>(grid, A, W, M, N, K, p, o, acc_out, st, fq);
+    return r2 ? launch_reg<2, 2, FQ>(grid, A, W, M, N, K, p, o, acc_out, st, fq) : launch_reg<1, 2, FQ>(grid, A, W, M, N, K, p, o, acc_out, st, fq);
+}
+
+int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
+                     const EpiParams &p, void *out, int32_t *acc_out, cudaStream_t st, bool cache_maps) {
+    if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    return gemv_dispatch<false>(A, W, M, N, K, batch, p, out, acc_out, st, cache_maps, FusedQ{});
+}
+
+// True when gemv_w4a4_from_fp16_launch should take the layer. Measured (B200, cold weights, graph chain of layers,
+// us per layer at 1 / 2 / 4 / 8 tokens; single launch | quantizer launch + linear launch with programmatic overlap):
+//   4096->12288  7.2  9.2 10.9 17.3 |  7.8  8.3  8.5  8.5      4096->4096   4.0  5.6  7.4 12.5 | 4.2 4.3 4.4 4.6
+//   4096->22016 10.3 11.2 13.2 24.0 | 11.5 11.4 12.2 13.8      11008->4096  8.3 10.5   -    -  | 8.0 8.1 8.3 8.5
+// Every CTA repeats the quantization, so the single launch pays off for ONE token only (where it also halves the
+// host-side launch work); from two tokens on the separate quantizer, started early by programmatic dependent
+// launch, is faster. The tokens' staging copy and code rows have to fit into shared memory beside what the kernels
+// already hold, and the asynchronous copies need 16-byte aligned rows.
+bool gemv_fused_quant_fits(const void *x, uint32_t M, uint32_t K) {
+    static const uint32_t max_m = [] {   // debug override of the token count up to which the single-launch route is taken
+        const char *e = getenv("DUQ4_FUSEQ_MAX_M");
+        const int v = e ? atoi(e) : 1;
+        return (uint32_t)(v < 0 ? 0 : (v > 16 ? 16 : v));
+    }();
+    return M >= 1 && M <= max_m && K % 64 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && fq_smem_bytes(M, K / 2) <= 96u * 1024u;
+}
+
+// M <= 16 tokens given as fp16: ONE launch that quantizes the tokens per CTA and runs the layer. p.s_row / p.z_row
+// are ignored (the kernel uses the per-token terms it computes; set 1 for the dual-uniform schemes).
+int gemv_w4a4_from_fp16_launch(const void *x, int act_mode, float clip, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
+                               const EpiParams &p, void *out, cudaStream_t st, bool cache_maps) {
+    if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return DUQ4_ERR_ALIGN;
+    if (!gemv_fused_quant_fits(x, M, K)) return DUQ4_ERR_SHAPE;
+    FusedQ fq{(const __half *)x, act_mode, clip};
+    return gemv_dispatch<true>(nullptr, W, M, N, K, 1, p, out, nullptr, st, cache_maps, fq);
 }
 
 }  // namespace duq4

@@ -12,47 +12,9 @@
 // fused kernels a CTA owns one token and keeps it in registers between the reduction and
 // the coding pass, so x is read from HBM exactly once.
 #include "duq_common.cuh"
+#include "quant_device.cuh"
 
 namespace duq4 {
-
-enum { QSYM = DUQ4_MODE_SYM, QSYM_DUAL = DUQ4_MODE_SYM_DUAL, QASYM = DUQ4_MODE_ASYM, QASYM_DUAL = DUQ4_MODE_ASYM_DUAL };
-
-struct RowQ {  // per-row quantization terms
-    __half s1, z1, s2, z2;
-    int zi1;  // rn(z1) for the single-scale asymmetric scheme
-};
-
-template <int MODE>
-__device__ __forceinline__ int code_at(__half x, uint32_t col, const RowQ &r) {
-    if (MODE == QSYM) return code_sym(x, r.s1);
-    if (MODE == QSYM_DUAL) return code_sym(x, col < kColK ? r.s1 : r.s2);
-    if (MODE == QASYM) return code_asym(x, r.s1, r.zi1);
-    return code_asym_dual(x, col < kColK ? r.s1 : r.s2, col < kColK ? r.z1 : r.z2);
-}
-
-// 8 halves (one uint4) starting at column col0 -> 8 nibbles (one uint32), low nibble first.
-template <int MODE>
-__device__ __forceinline__ uint32_t code8(const uint4 &v, uint32_t col0, const RowQ &r) {
-    const __half *h = reinterpret_cast<const __half *>(&v);
-    uint32_t out = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) out |= (uint32_t)(code_at<MODE>(h[i], col0 + i, r) & 0xF) << (4 * i);
-    return out;
-}
-
-template <int MODE>
-__device__ __forceinline__ RowQ load_rowq(const __half *s1, const __half *z1, const __half *s2, const __half *z2,
-                                          uint32_t row) {
-    RowQ r;
-    r.s1 = s1[row];
-    r.z1 = r.z2 = r.s2 = __ushort_as_half(0);
-    r.zi1 = 0;
-    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) r.s2 = s2[row];
-    if (MODE == QASYM || MODE == QASYM_DUAL) r.z1 = z1[row];
-    if (MODE == QASYM_DUAL) r.z2 = z2[row];
-    if (MODE == QASYM) r.zi1 = __half2int_rn(r.z1);
-    return r;
-}
 
 // ---- scales given: vector path (colsSrc % 8 == 0, colsDst == colsSrc/2, aligned) -------
 template <int MODE>
@@ -93,202 +55,6 @@ __global__ void quant_given_scalar_kernel(const __half *__restrict__ x, const __
     }
 }
 
-// ---- fast coding path of the fused kernels -------------------------------------------------
-// Same codes as code8<MODE>, far fewer instructions (the fused kernel is otherwise issue-bound,
-// not HBM-bound). Valid for a row whose scales are finite and non-zero, whose zero-points are
-// finite (|rint(z)| <= 400 for the single-scale asymmetric scheme) and which contains no
-// inf/NaN -- everything else takes code8<MODE>.
-//   * __hdiv(x, s) is half(rcp.approx.ftz(float(s)) * float(x)) plus a refinement that only
-//     fires for quotients below 8.6e-6, which round to the same code either way; the reciprocal
-//     is taken once per row with the same instruction.
-//   * rounding to integer and clamping happen in fp16x2: adding 1024 + offset to a value already
-//     clamped to a 16-wide integer window rounds it to nearest-even exactly like
-//     __half2int_rn, and leaves the code in the low four bits of each half.
-__device__ __forceinline__ float rcp_approx_ftz(float b) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
-    return r;
-}
-struct FastQ {
-    float r1, r2;          // reciprocals of scale set 1 / 2
-    __half2 z1, z2;        // zero-point terms, duplicated in both halves (rint(z) for QASYM)
-    bool ok;
-};
-__device__ __forceinline__ bool finite_nonzero(__half h) {
-    const unsigned short b = __half_as_ushort(h) & 0x7FFFu;
-    return b != 0 && b < 0x7C00u;
-}
-__device__ __forceinline__ bool finite_h(__half h) { return (__half_as_ushort(h) & 0x7FFFu) < 0x7C00u; }
-
-template <int MODE>
-__device__ __forceinline__ FastQ make_fastq(const RowQ &r, bool row_special) {
-    FastQ f;
-    f.ok = !row_special && finite_nonzero(r.s1);
-    f.r1 = rcp_approx_ftz(__half2float(r.s1));
-    f.r2 = f.r1;
-    f.z1 = f.z2 = __float2half2_rn(0.f);
-    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) {
-        f.ok = f.ok && finite_nonzero(r.s2);
-        f.r2 = rcp_approx_ftz(__half2float(r.s2));
-    }
-    if (MODE == QASYM) {
-        f.ok = f.ok && finite_h(r.z1) && fabsf(__half2float(r.z1)) <= 400.f;
-        f.z1 = __float2half2_rn(rintf(__half2float(r.z1)));
-    }
-    if (MODE == QASYM_DUAL) {
-        f.ok = f.ok && finite_h(r.z1) && finite_h(r.z2);
-        f.z1 = __half2half2(r.z1);
-        f.z2 = __half2half2(r.z2);
-    }
-    return f;
-}
-
-// One 32-bit word (two halves) -> two codes in bits [0,4) and [16,20).
-template <int MODE>
-__device__ __forceinline__ uint32_t code2_fast(uint32_t w, float rcp, __half2 z) {
-    const __half2 h = *reinterpret_cast<const __half2 *>(&w);
-    const float2 f = __half22float2(h);
-    const __half2 q = __floats2half2_rn(__fmul_rn(rcp, f.x), __fmul_rn(rcp, f.y));
-    __half2 t;
-    if (MODE == QSYM || MODE == QSYM_DUAL) {
-        const __half2 c = __hmin2(__hmax2(q, __float2half2_rn(-8.f)), __float2half2_rn(6.f));
-        t = __hadd2(c, __float2half2_rn(1032.f));            // 0x6400 + (code + 8)
-    } else if (MODE == QASYM) {
-        const __half2 c = __hmin2(__hmax2(q, __float2half2_rn(-500.f)), __float2half2_rn(500.f));
-        const __half2 s = __hadd2(__hadd2(c, __float2half2_rn(1536.f)), z);   // rint(x/s) + rint(z) + 1536
-        t = __hmin2(__hmax2(s, __float2half2_rn(1536.f)), __float2half2_rn(1551.f));   // 0x6600 + code
-    } else {
-        const __half2 c = __hmin2(__hmax2(__hadd2(q, z), __float2half2_rn(0.f)), __float2half2_rn(15.f));
-        t = __hadd2(c, __float2half2_rn(1024.f));            // 0x6400 + code
-    }
-    // each half is 0x6400 (or 0x6600) + code: the code is the low BYTE of the half, the high byte is constant
-    return *reinterpret_cast<const uint32_t *>(&t);
-}
-
-// 8 halves -> 8 nibbles, low nibble first. col0 >= 16 for the dual schemes (set 2 only).
-template <int MODE>
-__device__ __forceinline__ uint32_t code8_fast(const uint4 &v, const FastQ &f) {
-    const bool dual = MODE == QSYM_DUAL || MODE == QASYM_DUAL;
-    const float rcp = dual ? f.r2 : f.r1;
-    const __half2 z = dual ? f.z2 : f.z1;
-    const uint32_t a = code2_fast<MODE>(v.x, rcp, z), b = code2_fast<MODE>(v.y, rcp, z);
-    const uint32_t c = code2_fast<MODE>(v.z, rcp, z), d = code2_fast<MODE>(v.w, rcp, z);
-    // Each word holds its two codes in bytes 0 and 2. Gather the four code bytes of two words with one byte
-    // permute ([c0, c1, c2, c3], one nibble each), fold odd bytes onto even ones (x | x >> 4 puts c1 into the
-    // high nibble of byte 0 and c3 into that of byte 2), and gather the four finished bytes of the two halves.
-    const uint32_t ab = __byte_perm(a, b, 0x6420), cd = __byte_perm(c, d, 0x6420);
-    uint32_t out = __byte_perm(ab | (ab >> 4), cd | (cd >> 4), 0x6420);
-    if (MODE == QSYM || MODE == QSYM_DUAL) out ^= 0x88888888u;   // (code + 8) -> two's complement nibble
-    return out;
-}
-
-// ---- fused ---------------------------------------------------------------------------
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-__device__ __forceinline__ float warp_min(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-// Row statistics gathered by one thread. Symmetric schemes track max|x| (a: columns < 10
-// for the dual scheme, b: the rest / everything); asymmetric ones track min and max.
-struct Stats {
-    float a_hi, a_lo, b_hi, b_lo;
-};
-template <int MODE>
-__device__ __forceinline__ void stats_init(Stats &s) {
-    if (MODE == QSYM || MODE == QSYM_DUAL) {
-        s.a_hi = s.b_hi = 0.f;
-        s.a_lo = s.b_lo = 0.f;
-    } else {
-        s.a_hi = s.b_hi = -INFINITY;
-        s.a_lo = s.b_lo = INFINITY;
-    }
-}
-template <int MODE>
-__device__ __forceinline__ void stats_add(Stats &s, float v, uint32_t col) {
-    if (MODE == QSYM) {
-        s.b_hi = fmaxf(s.b_hi, fabsf(v));
-    } else if (MODE == QSYM_DUAL) {
-        if (col < kColK) s.a_hi = fmaxf(s.a_hi, fabsf(v)); else s.b_hi = fmaxf(s.b_hi, fabsf(v));
-    } else if (MODE == QASYM) {
-        s.b_hi = fmaxf(s.b_hi, v);
-        s.b_lo = fminf(s.b_lo, v);
-    } else {
-        if (col < kColK) { s.a_hi = fmaxf(s.a_hi, v); s.a_lo = fminf(s.a_lo, v); }
-        else { s.b_hi = fmaxf(s.b_hi, v); s.b_lo = fminf(s.b_lo, v); }
-    }
-}
-
-// Block-wide reduction of Stats over 256 threads; result valid in every thread.
-template <int MODE>
-__device__ __forceinline__ void stats_reduce(Stats &s, float (*sm)[4]) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    s.b_hi = warp_max(s.b_hi);
-    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) s.a_hi = warp_max(s.a_hi);
-    if (MODE == QASYM || MODE == QASYM_DUAL) s.b_lo = warp_min(s.b_lo);
-    if (MODE == QASYM_DUAL) s.a_lo = warp_min(s.a_lo);
-    if (lane == 0) { sm[warp][0] = s.a_hi; sm[warp][1] = s.a_lo; sm[warp][2] = s.b_hi; sm[warp][3] = s.b_lo; }
-    __syncthreads();
-    Stats r;
-    stats_init<MODE>(r);
-    for (int w = 0; w < nwarp; ++w) {
-        r.a_hi = fmaxf(r.a_hi, sm[w][0]);
-        r.a_lo = fminf(r.a_lo, sm[w][1]);
-        r.b_hi = fmaxf(r.b_hi, sm[w][2]);
-        r.b_lo = fminf(r.b_lo, sm[w][3]);
-    }
-    s = r;
-}
-
-// torch semantics of the quantizer modules, each op rounded to fp16 (opmath fp32):
-//   sym : scale = half(half(amax) * (1/7)) * clip            (nn/quantizer.py:13)
-//   asym: scale = half(half(max - min) * (1/15)); zero = rint(half(-min / scale))   (:27-31)
-// torch's CUDA division of an fp16 tensor by a host scalar multiplies by the fp32
-// reciprocal; for every fp16 input that equals the correctly rounded quotient by 7 or 15.
-__device__ __forceinline__ __half sym_scale(float amax, float clip) {
-    __half s = __float2half_rn(amax * (1.0f / 7.0f));
-    return __float2half_rn(__half2float(s) * clip);
-}
-__device__ __forceinline__ void asym_scale_zero(float mn, float mx, __half &s, __half &z) {
-    __half d = __float2half_rn(mx - mn);
-    s = __float2half_rn(__half2float(d) * (1.0f / 15.0f));
-    __half zq = __float2half_rn(__fdiv_rn(-mn, __half2float(s)));
-    z = __float2half_rn(rintf(__half2float(zq)));
-}
-
-template <int MODE>
-__device__ __forceinline__ RowQ rowq_from_stats(const Stats &s, float clip) {
-    RowQ r;
-    r.s1 = r.s2 = r.z1 = r.z2 = __ushort_as_half(0);
-    r.zi1 = 0;
-    if (MODE == QSYM) {
-        r.s1 = sym_scale(s.b_hi, clip);
-    } else if (MODE == QSYM_DUAL) {
-        r.s1 = sym_scale(s.a_hi, clip);
-        r.s2 = sym_scale(s.b_hi, clip);
-    } else if (MODE == QASYM) {
-        asym_scale_zero(s.b_lo, s.b_hi, r.s1, r.z1);
-        r.zi1 = __half2int_rn(r.z1);
-    } else {
-        asym_scale_zero(s.a_lo, s.a_hi, r.s1, r.z1);
-        asym_scale_zero(s.b_lo, s.b_hi, r.s2, r.z2);
-    }
-    return r;
-}
-
-template <int MODE>
-__device__ __forceinline__ void store_rowq(const RowQ &r, uint32_t row, __half *s1, __half *z1, __half *s2, __half *z2) {
-    s1[row] = r.s1;
-    if (MODE == QSYM_DUAL || MODE == QASYM_DUAL) s2[row] = r.s2;
-    if (MODE == QASYM || MODE == QASYM_DUAL) z1[row] = r.z1;
-    if (MODE == QASYM_DUAL) z2[row] = r.z2;
-}
-
 // One CTA (256 threads) per token; the token lives in VPT uint4 registers per thread.
 // Requires cols % 8 == 0, cols <= 256*8*VPT, x 16-byte aligned.
 // SiLU-gated MLP glue: h = half(half(silu(g)) * u), each step rounded to fp16 the way the torch
@@ -312,6 +78,11 @@ __global__ void __launch_bounds__(NT) quant_fused_vec_kernel(const __half *__res
                                                               uint32_t in_stride = 0, uint32_t up_off = 0) {
     __shared__ float sm[NT / 32][4];
     const uint32_t nvec = cols >> 3;
+    // Programmatic dependent launch (both instructions do nothing unless the launch carries the attribute): the
+    // kernel that follows on the stream -- the small-M linear kernel, which streams weights before it needs these
+    // codes -- may start right away; this kernel itself touches memory only after the stream's earlier work is done.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * (SILU ? in_stride : cols));
         uint4 d[VPT];
@@ -455,6 +226,22 @@ __global__ void asym_quant8_kernel(const float *__restrict__ x, const float *__r
     }
 }
 
+// One-off re-layout of packed int4 weights [rows, K/2] into the tensor-core-ready int8 form [rows, K] that
+// duq4_quantize_fused_i8 writes for activations: one int8 = 16 * code per element, K permuted inside 128-blocks.
+// Thread = one 32-bit packed word (8 codes).
+__global__ void __launch_bounds__(256) prelayout_i8_kernel(const uint32_t *__restrict__ w, uint32_t rows, uint32_t words_per_row,
+                                                           uint8_t *__restrict__ out) {
+    const size_t total = (size_t)rows * words_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / words_per_row), v = (uint32_t)(i - (size_t)row * words_per_row);
+        const uint32_t word = __ldg(w + i);
+        uint8_t *qr = out + (size_t)row * words_per_row * 8;
+        const uint32_t off = (v >> 4) * 128 + ((v & 15) >> 2) * 32 + (v & 3) * 4;
+        *reinterpret_cast<uint32_t *>(qr + off) = (word << 4) & 0xF0F0F0F0u;
+        *reinterpret_cast<uint32_t *>(qr + off + 16) = word & 0xF0F0F0F0u;
+    }
+}
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int grid_for(size_t work_items, int block) {
@@ -499,16 +286,34 @@ static int launch_fused(const void *x, uint32_t rows, uint32_t cols, float clip,
     uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
     bool vec = cols % 8 == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 3) == 0 && cols <= 256u * 8u * 16u;
     if (out8 && (!vec || cols % 64 != 0)) return DUQ4_ERR_SHAPE;
+    // Few tokens (decode): the launch may begin while the stream's previous kernel drains (the kernel waits for it
+    // before its first memory access), which takes the launch latency off the layer's critical path.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = rows <= 16 ? 1 : 0;
+    const uint32_t zero = 0;
+    cudaError_t e;
     if (!vec) {
         quant_fused_scalar_kernel<MODE><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d);
+        return launch_status();
     } else if (cols <= 256u * 8u * 2u) {
-        quant_fused_vec_kernel<MODE, 2><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
+        e = cudaLaunchKernelEx(&cfg, quant_fused_vec_kernel<MODE, 2>, hx, rows, cols, clip, q, a, b, c, d, out8, zero, zero);
     } else if (cols <= 256u * 8u * 4u) {
-        quant_fused_vec_kernel<MODE, 4><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
+        e = cudaLaunchKernelEx(&cfg, quant_fused_vec_kernel<MODE, 4>, hx, rows, cols, clip, q, a, b, c, d, out8, zero, zero);
     } else if (cols <= 256u * 8u * 8u) {
-        quant_fused_vec_kernel<MODE, 8><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
+        e = cudaLaunchKernelEx(&cfg, quant_fused_vec_kernel<MODE, 8>, hx, rows, cols, clip, q, a, b, c, d, out8, zero, zero);
     } else {
-        quant_fused_vec_kernel<MODE, 16><<<grid, 256, 0, st>>>(hx, rows, cols, clip, q, a, b, c, d, out8);
+        e = cudaLaunchKernelEx(&cfg, quant_fused_vec_kernel<MODE, 16>, hx, rows, cols, clip, q, a, b, c, d, out8, zero, zero);
+    }
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)e;
     }
     return launch_status();
 }
@@ -578,6 +383,15 @@ int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros,
     if (!x || !scale || !zeros || !q) return DUQ4_ERR_NULL;
     if (rows == 0 || cols == 0) return DUQ4_OK;
     asym_quant8_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, zeros, rows, cols, q);
+    return launch_status();
+}
+
+int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W_i8, void *stream) {
+    if (!W || !W_i8) return DUQ4_ERR_NULL;
+    if (N == 0) return DUQ4_OK;
+    if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
+    if (!aligned16(W) || !aligned16(W_i8)) return DUQ4_ERR_ALIGN;
+    prelayout_i8_kernel<<<grid_for((size_t)N * (K / 8), 256), 256, 0, (cudaStream_t)stream>>>((const uint32_t *)W, N, K / 8, (uint8_t *)W_i8);
     return launch_status();
 }
 

@@ -62,6 +62,8 @@ SIGNATURES = {
     "duq4_quantize_fused_i8": [_i, _vp, _u32, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp],
     "duq4_silu_mul_quantize_fused": [_i, _vp, _u32, _u32, _u32, _u32, _f32, _vp, _i, _vp, _vp, _vp],
     "duq4_linear_w4a4_preunpacked": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
+    "duq4_weight_prelayout_i8": [_vp, _u32, _u32, _vp, _vp],
+    "duq4_linear_w4a4_prelaid": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
     "duq4_sym_dequant": [_vp, _vp, _vp, _u32, _u32, _vp, _vp],
     "duq4_sym_dual_dequant": [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],
     "duq4_asym_dequant": [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],

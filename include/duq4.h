@@ -253,6 +253,17 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
                                  uint32_t K, const duq4_epilogue *epi, void *out, int32_t *acc_out,
                                  void *stream);
 
+/* Weight pre-layout (optional, no reference counterpart; SURVEY of the design space: "one-off int8 pre-unpack of
+ * W"): duq4_weight_prelayout_i8 turns packed weights W [N, K/2] into W_i8 [N, K] in the tensor-core-ready form of
+ * duq4_quantize_fused_i8 (int8 = 16 * code, K permuted inside 128-blocks; K % 128 == 0; twice the bytes), once per
+ * weight tensor. duq4_linear_w4a4_prelaid then runs the layer with BOTH operands in that form on the CTA-pair
+ * tensor-core kernel with no in-kernel unpack (any M >= 1; DUQ4_ERR_DEVICE where CTA pairs cannot be scheduled).
+ * Results are identical to duq4_linear_w4a4_preunpacked on the packed weights. The packed format stays the
+ * format of record (state_dict); a caller derives W_i8 lazily and keeps it beside the packed tensor. */
+int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W_i8, void *stream);
+int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K,
+                             const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream);
+
 /* Batched form: A [batch,M,K/2], W [batch,N,K/2], out [batch,M,N]; the epilogue's row
  * vectors are [batch,M] and its column vectors [batch,N] (the layout of the reference's
  * asym_batch_dequant, src/kernels/quant.cu:211-218). */
@@ -268,7 +279,13 @@ size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K);
  * and replaced by the computed ones, which live in `workspace` (256-byte aligned, at
  * least duq4_linear_from_fp16_workspace_bytes(M,K)). For ASYM_DUAL/SYM_DUAL activation
  * modes the epilogue uses set 1 of the computed row scales, as the reference modules do
- * (they only ever carry one row-scale vector, qlinear4bit/tools/tensor_utils.py:20-27). */
+ * (they only ever carry one row-scale vector, qlinear4bit/tools/tensor_utils.py:20-27).
+ * Launches: ONE token runs as a single kernel -- each CTA of the weight-streaming kernel quantizes the token into
+ * its own shared memory once its first weight loads are in flight, and the workspace is left untouched (K up to
+ * about 38000). Everything else is two launches (fused quantizer into the workspace, then the linear kernel); for
+ * up to 16 tokens the quantizer is launched with programmatic stream serialization, so it is already resident
+ * when the stream's previous kernel ends, and -- with duq4_set_static_weights(1) -- the linear kernel streams its
+ * first weights while the quantizer runs. The results do not depend on which route is taken. */
 int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N,
                                uint32_t K, int act_mode, float clip_ratio,
                                const duq4_epilogue *epi, void *out, void *workspace,

@@ -216,7 +216,7 @@ def test_batched(env, B, M, N, K):
     assert U.f16_equal_nan(out.cpu().numpy(), o.asym_batch_dequant(want, sr, zr, sc, zc))
 
 
-@pytest.mark.parametrize("M", [4, 20, 31, 300])   # 20, 31: the int8 code buffer is padded to 32 rows
+@pytest.mark.parametrize("M", [1, 4, 20, 31, 300])   # 1: single launch; 20, 31: the int8 code buffer is padded to 32 rows
 @pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
 def test_linear_from_fp16(env, M, mode):
     """quantize -> GEMM -> dequant in one call, scratch supplied by the caller. The codes and per-token
@@ -241,14 +241,70 @@ def test_linear_from_fp16(env, M, mode):
     torch.cuda.synchronize()
     if M > 16:
         assert tc_status(L) == 0
-    qa, s1, z1, s2, z2 = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
-    U.check_gpu_codes(torch, L, mode, x, qa, s1, z1 if asym else None, s2 if dual else None, z2 if mode == "asym_dual" else None)
+    if M > 1:    # two launches: the codes and per-token vectors the call's quantizer wrote are in its scratch
+        qa, s1, z1, s2, z2 = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
+        U.check_gpu_codes(torch, L, mode, x, qa, s1, z1 if asym else None, s2 if dual else None, z2 if mode == "asym_dual" else None)
+    else:        # one launch, codes never leave the CTAs' shared memory (their parity: test_small_m_fused_quantizer_codes);
+        # the oracle runs on the stand-alone fused quantizer's codes, which U.gpu_quantize checks
+        assert not ws.any(), "the single-launch route must leave the workspace untouched"
+        qa, s1, z1, s2, z2 = U.gpu_quantize(torch, L, mode, x)
     # the epilogue uses set 1 of the per-token vectors (the reference modules carry one row-scale vector)
     _, want = o.linear_w4a4(mode, qa, qw, s1, z1 if asym else None, sw, zc if asym else None, sw2 if dual else None,
                             zc2 if mode == "asym_dual" else None)
     assert U.f16_equal_nan(out.cpu().numpy(), want), f"{mode} M={M}: fp16 outputs differ from the oracle on the call's own codes"
     assert L.cdll.duq4_linear_w4a4_from_fp16(L.ptr(dx), L.ptr(dw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), L.ptr(out),
                                              L.ptr(ws), nbytes - 1, L.current_stream()) == -4
+
+
+@pytest.mark.parametrize("variant", [None, "0", "1", "3"])
+@pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
+def test_small_m_fused_quantizer_codes(env, mode, variant):
+    """The single-launch route of duq4_linear_w4a4_from_fp16: the CTAs of the small-M kernel quantize the tokens in
+    shared memory. It is taken for one token by default; DUQ4_FUSEQ_MAX_M=16 (set here, in a fresh process) lets
+    every token count up to 16 take it, so the in-kernel quantizer is checked for all of them.
+    The codes are made visible through the public entry point with a weight matrix that copies them out: weight
+    row n holds code 1 at input channel n and 0 elsewhere, all per-channel scales 1 (zero-points 0), so the fp16
+    output element [m, n] is (s_m * 1) * (code[m, n] (- z_m)) -- a different value for each of the 16 codes.
+    Scales, zero-points and codes must equal those of the stand-alone fused quantizer (which U.gpu_quantize
+    checks against the oracle and the reference's kernel), for every token count 1..16, on each of the three
+    small-M kernels (variant pins one in a fresh process), including an all-zero token, a constant token and
+    tokens holding inf / NaN."""
+    import os
+    if variant is not None or os.environ.get("DUQ4_FUSEQ_MAX_M") != "16":
+        import subprocess, sys
+        env2 = dict(os.environ, DUQ4_FUSEQ_MAX_M="16")
+        if variant is not None:
+            env2["DUQ4_GEMV_VARIANT"] = variant
+        r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu",
+                            f"{os.path.abspath(__file__)}::test_small_m_fused_quantizer_codes[{mode}-None]"],
+                           env=env2, capture_output=True, text=True, cwd=U.ROOT)
+        assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+        return
+    torch, L, o = env
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    for K in (64, 704, 4096):
+        eye = np.zeros((K, K), dtype=np.int8); np.fill_diagonal(eye, 1)
+        dw = dev(torch, o.pack_s4(eye))
+        one = torch.ones(K, dtype=torch.float16, device="cuda"); zero = torch.zeros(K, dtype=torch.float16, device="cuda")
+        epi = L.make_epilogue(mode, None, None, one, zero if asym else None, one if dual else None, zero if mode == "asym_dual" else None)
+        for M in (1, 2, 3, 5, 8, 9, 13, 16):
+            if M * (K // 2 * 5 + 64) + 1024 > 96 * 1024:
+                continue   # staging copy + code rows exceed the shared-memory budget: the call takes two launches
+            x = U.acts(M, K, 100 + M + K, mean=0.1 if asym else 0.0)
+            if M >= 5:
+                x[1] = 0; x[2] = x[2, 0]; x[3, 5] = np.inf; x[4, 7] = np.nan
+            dx = dev(torch, x)
+            nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+            ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+            out = torch.full((M, K), float("nan"), dtype=torch.float16, device="cuda")
+            L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dw), M, K, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(out),
+                   L.ptr(ws), nbytes, L.current_stream())
+            torch.cuda.synchronize()
+            qa, s1, z1, s2, z2 = U.gpu_quantize(torch, L, mode, x, clip=0.9, check=(M < 5))   # inf/NaN tokens: no oracle bracket
+            codes = o.unpack_s4(qa).astype(np.int32)   # asymmetric codes 8..15 read back as -8..-1, as the GEMM reads them
+            want = o.asym_dequant(codes, s1, z1, np.ones(K, np.float16), np.zeros(K, np.float16)) if asym else \
+                o.sym_dequant(codes, s1, np.ones(K, np.float16))
+            assert U.f16_equal_nan(out.cpu().numpy(), want), f"{mode} K={K} M={M}"
 
 
 @pytest.mark.parametrize("M,chunk_rows,pinned,pitch", [(4, 0, True, 0), (300, 0, True, 0), (1300, 256, True, 0),
@@ -375,6 +431,38 @@ def test_preunpacked_activations_match_packed_path(env, mode, M, N, K):
     assert tc_status(L) == 0
     assert np.array_equal(acc_b.cpu().numpy(), o.matmul_4bit(q.cpu().numpy(), qw))
     assert U.f16_equal_nan(out_a.cpu().numpy(), out_b.cpu().numpy())
+
+
+@pytest.mark.parametrize("mode", ["sym", "asym_dual"])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (17, 1000, 128), (300, 520, 256), (2000, 2100, 384), (512, 4096, 4096)])
+def test_prelaid_int8_weights_match_packed_weights(env, mode, M, N, K):
+    """duq4_weight_prelayout_i8 + duq4_linear_w4a4_prelaid (both operands int8 in the tensor-core-ready layout, no
+    in-kernel unpack) give the int32 accumulators of the oracle and the fp16 outputs of the packed-weight path."""
+    torch, L, o = env
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    x = U.acts(M, K, M + K, mean=0.1 if asym else 0.0); dx = dev(torch, x)
+    qw = U.rand_codes(N, K, 3); dqw = dev(torch, qw)
+    sc1 = dev(torch, U.rand_scales(N, 4)); zc1 = dev(torch, U.rand_zeros(N, 5))
+    sc2 = dev(torch, U.rand_scales(N, 6)); zc2 = dev(torch, U.rand_zeros(N, 7))
+    vec = lambda: torch.zeros(M, dtype=torch.float16, device="cuda")
+    s1, z1, s2, z2 = vec(), vec(), vec(), vec()
+    a8 = torch.zeros((M, K), dtype=torch.int8, device="cuda")
+    w8 = torch.zeros((N, K), dtype=torch.int8, device="cuda")
+    st = L.current_stream()
+    L.call("duq4_quantize_fused_i8", L.MODES[mode], L.ptr(dx), M, K, 1.0, L.ptr(a8), L.ptr(s1), L.ptr(z1), L.ptr(s2), L.ptr(z2), st)
+    L.call("duq4_weight_prelayout_i8", L.ptr(dqw), N, K, L.ptr(w8), st)
+    torch.cuda.synchronize()
+    assert np.array_equal(U.i8_codes_to_packed(w8.cpu().numpy()), qw)   # the same layout the activation quantizer writes
+    epi = L.make_epilogue(mode, s1, z1 if asym else None, sc1, zc1 if asym else None, sc2 if dual else None, zc2 if dual and asym else None)
+    out_a = torch.zeros((M, N), dtype=torch.float16, device="cuda"); out_b = torch.full_like(out_a, float("nan"))
+    acc_b = torch.full((M, N), -5, dtype=torch.int32, device="cuda")
+    L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(dqw), M, N, K, ctypes.byref(epi), L.ptr(out_a), None, st)
+    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(out_b), L.ptr(acc_b), st)
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert np.array_equal(acc_b.cpu().numpy(), o.matmul_4bit(U.i8_codes_to_packed(a8.cpu().numpy()), qw))
+    assert U.f16_equal_nan(out_a.cpu().numpy(), out_b.cpu().numpy())
+    assert L.cdll.duq4_weight_prelayout_i8(L.ptr(dqw), N, 192, L.ptr(w8), st) == -2   # K must be a multiple of 128
 
 
 @pytest.mark.parametrize("K", [512, 4096])

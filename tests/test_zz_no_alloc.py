@@ -24,7 +24,8 @@ from tests import _util as U
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M,N,K,mode", [(4, 520, 1024, "sym"), (16, 384, 4096, "asym"), (100, 264, 2048, "sym"),
+@pytest.mark.parametrize("M,N,K,mode", [(1, 4096, 4096, "asym"),        # one token: single-launch route, no scratch used at all
+                                        (4, 520, 1024, "sym"), (16, 384, 4096, "asym"), (100, 264, 2048, "sym"),
                                         (20, 520, 1024, "asym"),        # 17..31 tokens: 32-row padded code buffer
                                         (9, 9600, 4096, "sym"),         # small-M TMA-streamed kernel
                                         (200, 22016, 4096, "sym")])     # CTA-pair tensor-core kernel
@@ -58,8 +59,11 @@ def test_static_scratch_entry_matches_workspace_entry_twice(M, N, K, mode):
         assert not torch.isnan(got).all()
         if call == 0:   # the workspace entry point against the oracle, on the codes it left in its scratch
             xn = x.cpu().numpy()
-            qa, s1, z1, _, _ = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
-            U.check_gpu_codes(torch, L, mode, xn, qa, s1, z1 if mode == "asym" else None)
+            if M > 1:
+                qa, s1, z1, _, _ = U.from_fp16_scratch(ws.cpu().numpy(), M, K)
+                U.check_gpu_codes(torch, L, mode, xn, qa, s1, z1 if mode == "asym" else None)
+            else:   # one token: a single launch, the codes stay in shared memory
+                qa, s1, z1, _, _ = U.gpu_quantize(torch, L, mode, xn)
             _, ora = o.linear_w4a4(mode, qa, dw.cpu().numpy(), s1, z1 if mode == "asym" else None, dsw.cpu().numpy(),
                                    dzc.cpu().numpy() if mode == "asym" else None, None, None, bias.cpu().numpy())
             assert U.f16_equal_nan(want.cpu().numpy(), ora), "workspace entry point differs from the oracle"
