@@ -242,6 +242,33 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, codes, W, M, N, K, 1, p, out, nullptr, st, true, code_rows(M));
 }
 
+int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                       float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
+                                       size_t workspace_bytes, void *stream) {
+    if (!x || !W_i8 || !epi || (!out && !epi->n_out_peers)) return DUQ4_ERR_NULL;
+    if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
+    if (M == 0 || N == 0) return DUQ4_OK;
+    if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
+    const size_t cbytes = align_up((size_t)M * K, 256), vec = align_up((size_t)M * 2, 256);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0 || workspace_bytes < cbytes + 4 * vec) return DUQ4_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(W_i8) & 15) != 0) return DUQ4_ERR_ALIGN;
+    EpiParams p;
+    int rc = check_epi(epi, N, false, &p);
+    if (rc) return rc;
+    if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
+    const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;
+    const bool act_asym = act_mode == DUQ4_MODE_ASYM || act_mode == DUQ4_MODE_ASYM_DUAL;
+    if (epi_asym && !act_asym) return DUQ4_ERR_MODE;
+    uint8_t *ws = (uint8_t *)workspace;
+    void *s1 = ws + cbytes, *z1 = ws + cbytes + vec, *s2 = ws + cbytes + 2 * vec, *z2 = ws + cbytes + 3 * vec;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = quantize_fused_dispatch(act_mode, x, M, K, clip_ratio, ws, s1, z1, s2, z2, st, true);
+    if (rc) return rc;
+    p.s_row = (const __half *)s1;
+    p.z_row = epi_asym ? (const __half *)z1 : nullptr;
+    return gemm_tc2_launch_prelaid(ws, W_i8, M, N, K, p, out, nullptr, st);
+}
+
 // ---- scratch held inside the library ------------------------------------------------------
 // duq4_linear_w4a4_from_fp16_static keeps its intermediate (activation codes and per-token
 // scales / zero-points) in this array instead of caller memory. The array is part of the

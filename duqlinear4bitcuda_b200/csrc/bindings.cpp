@@ -460,24 +460,47 @@ Tensor scratch_for(const Tensor &x, void *stream, size_t need) {
 // activations stay in an internal scratch tensor. Same result as quantizer module + linear_w4a4. `act_mode` defaults
 // to the single-scale quantizer of the epilogue's family ("sym" for sym / sym_dual, "asym" otherwise), which is what
 // the reference modules pair with each linear variant (qlinear4bit/nn/linear.py:104-115, :239-250).
+// `W_prelaid`: optional int8 [N, K] made once from W by weight_prelayout_i8; when given, layers that see more than
+// 128 tokens run on it (no in-kernel weight unpack), fewer tokens use the packed W (half the bytes to stream).
 Tensor linear_w4a4_from_fp16(const std::string &mode, const Tensor &x, const Tensor &W, const Tensor &scale_col_1, const OptTensor &zeros_col_1,
                              const OptTensor &scale_col_2, const OptTensor &zeros_col_2, const OptTensor &bias, double clip_ratio,
-                             const std::optional<std::string> &act_mode_) {
+                             const std::optional<std::string> &act_mode_, const OptTensor &W_prelaid) {
     const char *fn = "linear_w4a4_from_fp16";
     check_tensors(fn, {{&x, "x"}, {&W, "W"}, {&scale_col_1, "scale_col_1"}, {opt(zeros_col_1), "zeros_col_1"}, {opt(scale_col_2), "scale_col_2"},
-                       {opt(zeros_col_2), "zeros_col_2"}, {opt(bias), "bias"}});
+                       {opt(zeros_col_2), "zeros_col_2"}, {opt(bias), "bias"}, {opt(W_prelaid), "W_prelaid"}});
     TORCH_CHECK(x.scalar_type() == torch::kFloat16 && x.dim() == 2, fn, ": x must be fp16 [M, K]");
     check_dtype(fn, W, "W", torch::kUInt8);
     const int64_t M = x.size(0), K = x.size(1), N = W.size(0);
     TORCH_CHECK(W.dim() == 2 && W.size(1) * 2 == K, fn, ": x and W disagree on K");
+    if (opt(W_prelaid)) {
+        check_dtype(fn, *W_prelaid, "W_prelaid", torch::kInt8);
+        TORCH_CHECK(W_prelaid->dim() == 2 && W_prelaid->size(0) == N && W_prelaid->size(1) == K, fn, ": W_prelaid must be int8 [N, K]");
+    }
     const std::string act_mode = act_mode_.has_value() ? *act_mode_ : ((mode == "sym" || mode == "sym_dual") ? "sym" : "asym");
     duq4_epilogue e = make_epi(fn, mode, N, std::nullopt, std::nullopt, scale_col_1, zeros_col_1, scale_col_2, zeros_col_2, bias, 0, 0);
     auto out = empty_like_dev(x, {M, N}, torch::kFloat16);
     Launch l(x);
-    const size_t need = duq4_linear_from_fp16_workspace_bytes(M, K);
+    const size_t need = duq4_linear_from_fp16_workspace_bytes(M < 32 ? 32 : M, K);
     Tensor ws = scratch_for(x, l.stream, need);
-    ok(fn, duq4_linear_w4a4_from_fp16(x.data_ptr(), W.data_ptr<uint8_t>(), M, N, K, mode_of(fn, act_mode), (float)clip_ratio, &e, out.data_ptr(),
-                                      ws.data_ptr(), (size_t)ws.numel(), l.stream));
+    if (opt(W_prelaid) && M > 128)
+        ok(fn, duq4_linear_w4a4_from_fp16_prelaid(x.data_ptr(), W_prelaid->data_ptr<int8_t>(), M, N, K, mode_of(fn, act_mode), (float)clip_ratio, &e,
+                                                  out.data_ptr(), ws.data_ptr(), (size_t)ws.numel(), l.stream));
+    else
+        ok(fn, duq4_linear_w4a4_from_fp16(x.data_ptr(), W.data_ptr<uint8_t>(), M, N, K, mode_of(fn, act_mode), (float)clip_ratio, &e, out.data_ptr(),
+                                          ws.data_ptr(), (size_t)ws.numel(), l.stream));
+    return out;
+}
+
+// (new) One-off re-layout of packed weights uint8 [N, K/2] into the tensor-core-ready int8 [N, K] that
+// linear_w4a4_from_fp16(W_prelaid=...) and the library's duq4_linear_w4a4_prelaid read (K % 128 == 0).
+Tensor weight_prelayout_i8(const Tensor &W) {
+    check_tensors("weight_prelayout_i8", {{&W, "W"}});
+    check_dtype("weight_prelayout_i8", W, "W", torch::kUInt8);
+    TORCH_CHECK(W.dim() == 2, "weight_prelayout_i8: expected W [N, K/2]");
+    const int64_t N = W.size(0), K = W.size(1) * 2;
+    auto out = empty_like_dev(W, {N, K}, torch::kInt8);
+    Launch l(W);
+    ok("weight_prelayout_i8", duq4_weight_prelayout_i8(W.data_ptr<uint8_t>(), N, K, out.data_ptr<int8_t>(), l.stream));
     return out;
 }
 
@@ -568,7 +591,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("return_acc") = false, py::arg("next_weights") = py::none());
     m.def("linear_w4a4_from_fp16", &linear_w4a4_from_fp16, py::arg("mode"), py::arg("x"), py::arg("W"), py::arg("scale_col_1"),
           py::arg("zeros_col_1") = py::none(), py::arg("scale_col_2") = py::none(), py::arg("zeros_col_2") = py::none(), py::arg("bias") = py::none(),
-          py::arg("clip_ratio") = 1.0, py::arg("act_mode") = py::none());
+          py::arg("clip_ratio") = 1.0, py::arg("act_mode") = py::none(), py::arg("W_prelaid") = py::none());
+    m.def("weight_prelayout_i8", &weight_prelayout_i8, py::arg("W"));
     m.def("linear_w4a4_gate_up_silu", &linear_w4a4_gate_up_silu, py::arg("mode"), py::arg("A"), py::arg("W"), py::arg("scale_row"),
           py::arg("zeros_row") = py::none(), py::arg("scale_col") = py::none(), py::arg("zeros_col") = py::none(), py::arg("bias") = py::none());
     m.def("linear_w4a4_batched", &linear_w4a4_batched, py::arg("mode"), py::arg("A"), py::arg("W"), py::arg("scale_row"),

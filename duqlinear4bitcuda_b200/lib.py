@@ -64,6 +64,7 @@ SIGNATURES = {
     "duq4_linear_w4a4_preunpacked": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
     "duq4_weight_prelayout_i8": [_vp, _u32, _u32, _vp, _vp],
     "duq4_linear_w4a4_prelaid": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
+    "duq4_linear_w4a4_from_fp16_prelaid": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp, _sz, _vp],
     "duq4_sym_dequant": [_vp, _vp, _vp, _u32, _u32, _vp, _vp],
     "duq4_sym_dual_dequant": [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],
     "duq4_asym_dequant": [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],

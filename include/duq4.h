@@ -263,6 +263,13 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
 int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W_i8, void *stream);
 int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K,
                              const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream);
+/* duq4_linear_w4a4_from_fp16 on pre-laid-out weights: fused quantizer (tensor-core-ready int8 codes into the
+ * workspace) + duq4_linear_w4a4_prelaid; the route for layers that see many tokens at a time (prefill). Same
+ * arguments and results as duq4_linear_w4a4_from_fp16 except that W_i8 is the output of duq4_weight_prelayout_i8
+ * and K % 128 == 0; the workspace need is that of duq4_linear_from_fp16_workspace_bytes(max(M, 32), K). */
+int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                       float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
+                                       size_t workspace_bytes, void *stream);
 
 /* Batched form: A [batch,M,K/2], W [batch,N,K/2], out [batch,M,N]; the epilogue's row
  * vectors are [batch,M] and its column vectors [batch,N] (the layout of the reference's

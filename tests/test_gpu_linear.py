@@ -465,6 +465,32 @@ def test_prelaid_int8_weights_match_packed_weights(env, mode, M, N, K):
     assert L.cdll.duq4_weight_prelayout_i8(L.ptr(dqw), N, 192, L.ptr(w8), st) == -2   # K must be a multiple of 128
 
 
+@pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
+@pytest.mark.parametrize("M,N,K", [(5, 264, 128), (300, 520, 1024), (2100, 2000, 256)])
+def test_linear_from_fp16_prelaid_equals_packed_weight_entry(env, mode, M, N, K):
+    """The one-call layer on pre-laid-out int8 weights == the one-call layer on the packed weights, bit for bit."""
+    torch, L, o = env
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    dx = dev(torch, U.acts(M, K, 3, mean=0.1 if asym else 0.0)); dqw = dev(torch, U.rand_codes(N, K, 4))
+    sc1, zc1, sc2, zc2 = (dev(torch, v) for v in (U.rand_scales(N, 5), U.rand_zeros(N, 6), U.rand_scales(N, 7), U.rand_zeros(N, 8)))
+    bias = dev(torch, np.random.default_rng(9).standard_normal(N).astype(np.float16))
+    epi = L.make_epilogue(mode, None, None, sc1, zc1 if asym else None, sc2 if dual else None, zc2 if mode == "asym_dual" else None, bias)
+    w8 = torch.zeros((N, K), dtype=torch.int8, device="cuda")
+    L.call("duq4_weight_prelayout_i8", L.ptr(dqw), N, K, L.ptr(w8), L.current_stream())
+    nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(max(M, 32), K)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    want = torch.zeros((M, N), dtype=torch.float16, device="cuda"); got = torch.full_like(want, float("nan"))
+    L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(want), L.ptr(ws), nbytes,
+           L.current_stream())
+    L.call("duq4_linear_w4a4_from_fp16_prelaid", L.ptr(dx), L.ptr(w8), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(got), L.ptr(ws), nbytes,
+           L.current_stream())
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert U.f16_equal_nan(got.cpu().numpy(), want.cpu().numpy())
+    assert L.cdll.duq4_linear_w4a4_from_fp16_prelaid(L.ptr(dx), L.ptr(w8), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(got), L.ptr(ws),
+                                                     M * K, L.current_stream()) == -4
+
+
 @pytest.mark.parametrize("K", [512, 4096])
 def test_decode_static_weights_overlap_keeps_stream_order(env, K):
     """With duq4_set_static_weights(1) the small-M kernels start streaming weights before the

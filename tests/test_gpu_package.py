@@ -186,6 +186,29 @@ def test_operator_argument_checks(env):
         ops.linear_w4a4("symm", q, w, s, None, sc)
 
 
+def test_module_weight_prelayout_cache(env):
+    """A module that owns its quantizer runs forwards of >= 256 tokens on a lazily built int8 copy of its packed
+    weights: same output bits as with the cache disabled, the copy is rebuilt when the weights change, and the
+    state_dict is unaffected."""
+    torch, qnn, tu, o = env
+    lin = _lin(torch, 256, 72, 31)
+    m = qnn.Linear4bitASQ.from_linear(lin, require_quantizer=True).cuda()
+    x = torch.from_numpy(U.acts(300, 256, 5, mean=0.1)).cuda()
+    y_cached = m(x)
+    assert "_prelaid" in m.__dict__ and m.__dict__["_prelaid"][1].dtype == torch.int8 and tuple(m.__dict__["_prelaid"][1].shape) == (72, 256)
+    m.weight_prelayout = False
+    y_plain = m(x)
+    assert torch.equal(y_cached.view(torch.int16), y_plain.view(torch.int16))
+    m.weight_prelayout = True
+    assert m(x[:8]).shape == (8, 72) and torch.equal(m(x[:8]).view(torch.int16), y_plain[:8].view(torch.int16))   # few tokens: packed weights
+    with torch.no_grad():
+        m.weight.copy_(torch.randint(0, 256, m.weight.shape, dtype=torch.uint8))   # in-place change -> new version -> rebuilt copy
+    y_new = m(x)
+    m.weight_prelayout = False
+    assert torch.equal(y_new.view(torch.int16), m(x).view(torch.int16)) and not torch.equal(y_new, y_cached)
+    assert sorted(m.state_dict()) == ["bias", "weight", "weight_scales", "weight_zeros"]
+
+
 def test_module_with_fp32_scale_buffers_matches_fp16(env):
     """Linear4bitSQ registers weight_scales with torch's default dtype (fp32), as the reference does; a module
     built directly and filled by load_state_dict keeps them in fp32. The forward converts them once and gives
