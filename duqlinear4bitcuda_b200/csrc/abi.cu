@@ -18,7 +18,8 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
 int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_t M, uint32_t inter, uint32_t K,
                             const EpiParams &p, void *h_out, cudaStream_t st);
 int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
-                            int32_t *acc_out, cudaStream_t st);
+                            int32_t *acc_out, cudaStream_t st, void *sk_scratch = nullptr, size_t sk_bytes = 0);
+size_t gemm_tc2_split_scratch_bytes();
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
 int peer_status_read(int32_t *out);
@@ -168,8 +169,10 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, A_i8, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
 }
 
+size_t duq4_gemm_split_scratch_bytes(void) { return gemm_tc2_split_scratch_bytes(); }
+
 int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, const duq4_epilogue *epi,
-                             void *out, int32_t *acc_out, void *stream) {
+                             void *out, int32_t *acc_out, void *split_scratch, size_t split_scratch_bytes, void *stream) {
     EpiParams p;
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
@@ -179,7 +182,7 @@ int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M,
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
     if (((reinterpret_cast<uintptr_t>(A_i8) | reinterpret_cast<uintptr_t>(W_i8)) & 15) != 0) return DUQ4_ERR_ALIGN;
-    return gemm_tc2_launch_prelaid(A_i8, W_i8, M, N, K, p, out, acc_out, (cudaStream_t)stream);
+    return gemm_tc2_launch_prelaid(A_i8, W_i8, M, N, K, p, out, acc_out, (cudaStream_t)stream, split_scratch, split_scratch_bytes);
 }
 
 int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W, uint32_t M, uint32_t inter, uint32_t K,
@@ -242,6 +245,8 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, codes, W, M, N, K, 1, p, out, nullptr, st, true, code_rows(M));
 }
 
+size_t duq4_linear_from_fp16_prelaid_workspace_bytes(uint32_t M, uint32_t K);
+
 int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                        float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
                                        size_t workspace_bytes, void *stream) {
@@ -250,7 +255,8 @@ int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
     const size_t cbytes = align_up((size_t)M * K, 256), vec = align_up((size_t)M * 2, 256);
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0 || workspace_bytes < cbytes + 4 * vec) return DUQ4_ERR_WORKSPACE;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0 || workspace_bytes < duq4_linear_from_fp16_prelaid_workspace_bytes(M, K))
+        return DUQ4_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(W_i8) & 15) != 0) return DUQ4_ERR_ALIGN;
     EpiParams p;
     int rc = check_epi(epi, N, false, &p);
@@ -266,7 +272,11 @@ int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32
     if (rc) return rc;
     p.s_row = (const __half *)s1;
     p.z_row = epi_asym ? (const __half *)z1 : nullptr;
-    return gemm_tc2_launch_prelaid(ws, W_i8, M, N, K, p, out, nullptr, st);
+    return gemm_tc2_launch_prelaid(ws, W_i8, M, N, K, p, out, nullptr, st, ws + cbytes + 4 * vec, gemm_tc2_split_scratch_bytes());
+}
+
+size_t duq4_linear_from_fp16_prelaid_workspace_bytes(uint32_t M, uint32_t K) {
+    return align_up((size_t)M * K, 256) + 4 * align_up((size_t)M * 2, 256) + gemm_tc2_split_scratch_bytes();
 }
 
 // ---- scratch held inside the library ------------------------------------------------------

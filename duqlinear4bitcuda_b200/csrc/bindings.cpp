@@ -480,9 +480,10 @@ Tensor linear_w4a4_from_fp16(const std::string &mode, const Tensor &x, const Ten
     duq4_epilogue e = make_epi(fn, mode, N, std::nullopt, std::nullopt, scale_col_1, zeros_col_1, scale_col_2, zeros_col_2, bias, 0, 0);
     auto out = empty_like_dev(x, {M, N}, torch::kFloat16);
     Launch l(x);
-    const size_t need = duq4_linear_from_fp16_workspace_bytes(M < 32 ? 32 : M, K);
+    const bool prelaid = opt(W_prelaid) && M > 128;
+    const size_t need = prelaid ? duq4_linear_from_fp16_prelaid_workspace_bytes(M, K) : duq4_linear_from_fp16_workspace_bytes(M, K);
     Tensor ws = scratch_for(x, l.stream, need);
-    if (opt(W_prelaid) && M > 128)
+    if (prelaid)
         ok(fn, duq4_linear_w4a4_from_fp16_prelaid(x.data_ptr(), W_prelaid->data_ptr<int8_t>(), M, N, K, mode_of(fn, act_mode), (float)clip_ratio, &e,
                                                   out.data_ptr(), ws.data_ptr(), (size_t)ws.numel(), l.stream));
     else

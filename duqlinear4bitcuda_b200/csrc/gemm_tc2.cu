@@ -292,6 +292,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
 
+    // Work list of this pair: its tiles of the full rounds (tile = pair, pair + npairs, ... below dp_tiles), then --
+    // when the launch splits its last, partly filled round along K -- one K range of one of the remaining tiles.
+    struct Work {
+        uint32_t tile, k0, k1;
+        int sk_rank;        // -1: whole tile; 0: K-split tile, this pair owns the result; > 0: contributes a partial
+        uint32_t sk_slot;
+    };
+    const uint32_t dp_tiles = num_tiles - a.sk_tiles;
+    const uint32_t n_dp = pair < dp_tiles ? (dp_tiles - pair + npairs - 1) / npairs : 0;
+    auto work_at = [&](uint32_t i, Work &w) -> bool {
+        if (i < n_dp) {
+            w.tile = pair + i * npairs; w.k0 = 0; w.k1 = ksteps; w.sk_rank = -1; w.sk_slot = 0;
+            return true;
+        }
+        if (i == n_dp && pair < a.sk_tiles * a.sk_group) {
+            const uint32_t g = pair / a.sk_group, r = pair % a.sk_group;
+            w.tile = dp_tiles + g; w.k0 = r * ksteps / a.sk_group; w.k1 = (r + 1) * ksteps / a.sk_group;
+            w.sk_rank = (int)r; w.sk_slot = g;
+            return true;
+        }
+        return false;
+    };
     auto tile_coords = [&](uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
         const uint32_t per_b = a.tiles_m * a.tiles_n;
         b = tile / per_b;
@@ -305,10 +327,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
+            Work w;
+            for (uint32_t wi = 0; ok && work_at(wi, w); ++wi) {
                 uint32_t b, tm, tn;
-                tile_coords(tile, b, tm, tn);
-                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                tile_coords(w.tile, b, tm, tn);
+                for (uint32_t ks = w.k0; ks < w.k1; ++ks, ++it) {
                     if (WI8) {   // this CTA's half of the int8 W block straight into the MMA ring, credited to the leader
                         const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                         if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 1))) break;
@@ -338,10 +361,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
+            Work w;
+            for (uint32_t wi = 0; ok && work_at(wi, w); ++wi) {
                 uint32_t b, tm, tn;
-                tile_coords(tile, b, tm, tn);
-                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                tile_coords(w.tile, b, tm, tn);
+                for (uint32_t ks = w.k0; ks < w.k1; ++ks, ++it) {
                     const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                     if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 7))) break;
                     if (rank == 0) mbar_expect_tx(up_full(u), 2 * BMH * BKE + (WI8 ? 2 * bnh * BKE : 0));   // both CTAs' A tiles (and int8 W halves)
@@ -359,12 +383,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t idesc = make_idesc(256, (int)bn);
             uint32_t it = 0, lt = 0;
             bool ok = true, issued = false;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs, ++lt) {
+            Work w;
+            for (uint32_t wi = 0; ok && work_at(wi, w); ++wi, ++lt) {
                 const uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
                 if (!(ok = mbar_wait_cluster(acc_empty(buf), aph ^ 1, abortp, 2))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                for (uint32_t ks = w.k0; ks < w.k1; ++ks, ++it) {
                     const uint32_t u = it % NUP, ph = (it / NUP) & 1;
                     if (!(ok = mbar_wait_cluster(up_full(u), ph, abortp, 3))) break;
                     tc_fence_after();
@@ -372,7 +397,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint64_t da = make_desc(sa), db = make_desc(sb);
 #pragma unroll
                     for (int kk = 0; kk < BKE / 32; ++kk)
-                        umma2_i8(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (ks | kk) != 0);
+                        umma2_i8(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, ((ks - w.k0) | kk) != 0);
                     issued = true;
                     umma2_commit(up_empty(u));            // this CTA's stage ...
                     umma2_commit(mapa(up_empty(u), 1));   // ... and the partner's
@@ -393,9 +418,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int quad = warp & 3;
         uint32_t lt = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs, ++lt) {
+        Work w;
+        for (uint32_t wi = 0; ok && work_at(wi, w); ++wi, ++lt) {
             uint32_t b, tm, tn;
-            tile_coords(tile, b, tm, tn);
+            tile_coords(w.tile, b, tm, tn);
             const uint32_t buf = lt & 1, aph = (lt >> 1) & 1;
             const uint32_t n0 = tn * bn;
             EpiParams pb = a.epi;
@@ -421,9 +447,46 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (GU)   // warps 2..5 take hidden channels [0,64) of the tile, warps 6..9 [64,128)
                 epi_store_tile_gate_up(a, pb, tm * 256 + rank * BMH, tn * 128u, tmem_base + buf * BN, quad, lane, cs, cz, cb,
                                        stage_out + (warp - 2) * kStageOutWarp, ((warp - 2) >> 2) * 4, ((warp - 2) >> 2) * 4 + 4);
-            else
+            else if (w.sk_rank < 0)
                 epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                          stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
+            else {
+                // K-split tile. Partial slabs: [tile slot][contributor][CTA of the pair][128 rows][BN] int32.
+                const uint32_t G = a.sk_group;
+                const size_t slab = (size_t)BMH * BN;
+                int32_t *slot0 = a.sk_scratch + (size_t)w.sk_slot * (G - 1) * 2 * slab;
+                if (w.sk_rank > 0) {
+                    epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                                             stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), nullptr, 0, 0,
+                                             slot0 + ((size_t)(w.sk_rank - 1) * 2 + rank) * slab);
+                    __threadfence();   // this lane's partial sums are visible device-wide before the arrival below
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(a.sk_counters + w.sk_slot, 1u);
+                } else {
+                    // bounded wait for the 2 x EPI epilogue warps of each of the G - 1 contributing pairs
+                    const unsigned int want = (G - 1) * 2 * EPI;
+                    bool arrived = false;
+                    uint64_t t0 = 0;
+                    for (uint32_t spin = 1; !arrived; ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sk_counters + w.sk_slot) : "memory");
+                        arrived = v >= want;
+                        if (arrived || (spin & 0x3Fu) != 0) continue;
+                        if (*abortp) break;
+                        const uint64_t now = globaltimer();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > kPtxWaitLimitNs) {
+                            *abortp = 1;
+                            atomicCAS(&g_tc2_status, 0, 8);
+                            break;
+                        }
+                    }
+                    if (!(ok = arrived)) break;
+                    epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                                             stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), slot0 + (size_t)rank * slab, G - 1,
+                                             2 * slab);
+                }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));
@@ -435,8 +498,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         constexpr uint32_t kDstOff = APK ? 0 : BMH * BKE;
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles && ok; tile += npairs) {
-            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+        Work w;
+        for (uint32_t wi = 0; ok && work_at(wi, w); ++wi) {
+            for (uint32_t ks = w.k0; ks < w.k1; ++ks, ++it) {
                 const uint32_t s = it % NPK, ph = (it / NPK) & 1;
                 const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                 if (!(ok = mbar_wait(pk_full(s), ph, abortp, &g_tc2_status, 5))) break;
@@ -497,9 +561,15 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
     return rounds(224) <= rounds(256) ? 224u : 256u;
 }
 
+// Scratch the K-split of a launch's last round may use: partial int32 tiles of at most one round of pairs, plus the
+// arrival counters (the first 1 KiB).
+constexpr size_t kSkCounterBytes = 1024;
+size_t gemm_tc2_split_scratch_bytes() { return kSkCounterBytes + (size_t)148 / 2 * 256 * 256 * sizeof(int32_t); }
+
 template <bool APK, bool GU = false, bool WI8 = false>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
-                   void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0, bool cache_maps = true) {
+                   void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0, bool cache_maps = true,
+                   void *sk_scratch = nullptr, size_t sk_bytes = 0) {
     using namespace tc2;
     constexpr int kSmem2 = Cfg2<APK, GU, WI8>::kSmem;
     auto *kernel = gemm_tc2_kernel<APK, GU, WI8>;
@@ -555,7 +625,31 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
              : tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb, cache_maps);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
-    const uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
+    uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
+    // K-split of the last, partly filled round (needs caller scratch): T tiles are left after the full rounds; when
+    // they occupy at most half of the pairs, each is computed by G pairs, a K range each, and the group's first pair
+    // adds the partial sums of the others before its epilogue. The round then costs about 1/G of a tile (plus the
+    // partial tiles' trip through L2) instead of a whole one: 8192 -> 28672 at 512 tokens is 224 tiles on 74 pairs,
+    // 3 rounds + 2 tiles; the 2 tiles are split eight ways instead of taking a fourth round.
+    a.sk_tiles = a.sk_group = 0;
+    if (!GU && sk_scratch && (reinterpret_cast<uintptr_t>(sk_scratch) & 255) == 0) {
+        const uint32_t T = tiles % (uint32_t)max_pairs;
+        uint32_t G = T ? (uint32_t)max_pairs / T : 0;
+        if (G > 8) G = 8;
+        const uint32_t ksteps = cdiv(K, (uint32_t)BKE);
+        while (G >= 2 && ksteps < 4 * G) --G;   // every K range keeps at least four pipeline stages of work
+        const size_t need = kSkCounterBytes + (size_t)T * (G > 1 ? G - 1 : 0) * 256 * 256 * sizeof(int32_t);
+        if (T && G >= 2 && T * sizeof(unsigned int) <= kSkCounterBytes && need <= sk_bytes) {
+            a.sk_tiles = T;
+            a.sk_group = G;
+            a.sk_counters = (unsigned int *)sk_scratch;
+            a.sk_scratch = (int32_t *)((uint8_t *)sk_scratch + kSkCounterBytes);
+            const uint32_t busy = tiles - T >= (uint32_t)max_pairs ? (uint32_t)max_pairs : T * G;   // full rounds use every pair
+            pairs = busy;
+            cudaError_t me = cudaMemsetAsync(sk_scratch, 0, kSkCounterBytes, st);
+            if (me != cudaSuccess) return (int)me;
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(kThreads2);
@@ -588,8 +682,8 @@ int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uin
 // Both operands int8 in the tensor-core-ready layout (A from duq4_quantize_fused_i8, W from
 // duq4_weight_prelayout_i8). DUQ4_ERR_DEVICE when the device cannot co-schedule CTA pairs.
 int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
-                            int32_t *acc_out, cudaStream_t st) {
-    return launch2<false, false, true>(A, W_i8, M, N, K, 1, p, out, acc_out, st, 0, true);
+                            int32_t *acc_out, cudaStream_t st, void *sk_scratch, size_t sk_bytes) {
+    return launch2<false, false, true>(A, W_i8, M, N, K, 1, p, out, acc_out, st, 0, true, sk_scratch, sk_bytes);
 }
 
 // SiLU-gated gate/up projection: W packed [2*I, K/2] (gate rows, then up rows), per-channel vectors of

@@ -89,6 +89,12 @@ struct Args {
     uint32_t bn;              // CTA-pair kernel only: accumulator columns per tile (multiple of 32, <= 256)
     uint32_t a_rows;          // rows of the A buffer the tensor map may read (>= M; the extra rows are never stored)
     uint32_t gate_up;         // CTA-pair kernel only: 0, or I = width of a SiLU-gated gate/up projection (W has 2*I rows)
+    // CTA-pair kernel only, K-split of the last, partly filled round of tiles: the last sk_tiles tiles are each
+    // computed by sk_group pairs (a K range each); pair 0 of a group adds the others' int32 partial tiles (sk_scratch)
+    // to its own before the dequant, the others signal sk_counters[tile slot] once per epilogue warp.
+    uint32_t sk_tiles, sk_group;
+    int32_t *sk_scratch;
+    unsigned int *sk_counters;
     EpiParams epi;
     __half *out;
     int32_t *acc_out;
@@ -130,7 +136,14 @@ __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb,
 template <int BN, bool STAGED>
 __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &pb, uint32_t b, uint32_t m_base, uint32_t n0,
                                    uint32_t tmem_acc, int quad, int lane, uint32_t shift, const __half *cs,
-                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16) {
+                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16,
+                                   const int32_t *sk_add = nullptr, uint32_t sk_n = 0, size_t sk_stride = 0, int32_t *sk_out = nullptr) {
+    // sk_out: this CTA only contributes a K range of the tile -- its raw accumulators go to the slab sk_out and nothing
+    // else happens. sk_add / sk_n / sk_stride: sk_n such slabs (sk_stride ints apart) are added to the accumulators
+    // before they are used. A slab (128 x BN int32) is private to the two warps that exchange it -- the same lane
+    // quadrant of the same CTA of the contributing and of the owning pair -- so it is laid out for their access
+    // pattern: element (chunk ch, group of four columns j4, lane, 4 ints), i.e. every 128-bit access of a warp
+    // covers 512 contiguous bytes.
     // nch: 16-column chunks of the accumulator that belong to this tile (tiles narrower than BN)
     const uint32_t n_end = min(a.N, n0 + 16u * (uint32_t)nch);   // first column not written by this tile
     const int mode = a.epi.mode;
@@ -161,6 +174,28 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         tmem_ld16(taddr + ch * 16, v);
         tmem_ld_wait();
         const uint32_t c0 = ch * 16;
+        if (sk_out) {   // contributor of a K-split tile: raw accumulators to the scratch slab
+            int4 *dst = reinterpret_cast<int4 *>(sk_out) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) dst[(j >> 2) * 32] = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+            continue;
+        }
+        for (uint32_t c = 0; c < sk_n; c += 2) {   // owner of a K-split tile: add the other pairs' partial sums, two slabs at a time
+            const int4 *s0 = reinterpret_cast<const int4 *>(sk_add + c * sk_stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
+            const bool two = c + 1 < sk_n;
+            const int4 *s1 = two ? reinterpret_cast<const int4 *>(sk_add + (c + 1) * sk_stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane : s0;
+            int4 t0[4], t1[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                t0[q] = __ldcg(s0 + q * 32);
+                t1[q] = two ? __ldcg(s1 + q * 32) : make_int4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                v[4 * q] += (uint32_t)(t0[q].x + t1[q].x); v[4 * q + 1] += (uint32_t)(t0[q].y + t1[q].y);
+                v[4 * q + 2] += (uint32_t)(t0[q].z + t1[q].z); v[4 * q + 3] += (uint32_t)(t0[q].w + t1[q].w);
+            }
+        }
         const bool col_any = n0 + c0 < n_end;
         const bool full = n0 + c0 + 16 <= n_end;
 #pragma unroll

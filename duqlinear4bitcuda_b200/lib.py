@@ -63,7 +63,8 @@ SIGNATURES = {
     "duq4_silu_mul_quantize_fused": [_i, _vp, _u32, _u32, _u32, _u32, _f32, _vp, _i, _vp, _vp, _vp],
     "duq4_linear_w4a4_preunpacked": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
     "duq4_weight_prelayout_i8": [_vp, _u32, _u32, _vp, _vp],
-    "duq4_linear_w4a4_prelaid": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
+    "duq4_gemm_split_scratch_bytes": [],
+    "duq4_linear_w4a4_prelaid": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp, _sz, _vp],
     "duq4_linear_w4a4_from_fp16_prelaid": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp, _sz, _vp],
     "duq4_sym_dequant": [_vp, _vp, _vp, _u32, _u32, _vp, _vp],
     "duq4_sym_dual_dequant": [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],
@@ -77,6 +78,7 @@ SIGNATURES = {
     "duq4_linear_w4a4": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
     "duq4_linear_w4a4_batched": [_vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp, _vp],
     "duq4_linear_from_fp16_workspace_bytes": [_u32, _u32],
+    "duq4_linear_from_fp16_prelaid_workspace_bytes": [_u32, _u32],
     "duq4_linear_w4a4_from_fp16": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp, _sz, _vp],
     "duq4_linear_w4a4_gate_up_silu": [_vp, _i, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
     "duq4_linear_host_staging_bytes": [_u32, _u32, _u32, _u32],
@@ -86,7 +88,8 @@ SIGNATURES = {
     "duq4_last_device_status": [_vp, ctypes.POINTER(ctypes.c_int32)],
 }
 _RESTYPES = {"duq4_version": ctypes.c_char_p, "duq4_error_string": ctypes.c_char_p,
-             "duq4_linear_from_fp16_workspace_bytes": ctypes.c_size_t,
+             "duq4_linear_from_fp16_workspace_bytes": ctypes.c_size_t, "duq4_gemm_split_scratch_bytes": ctypes.c_size_t,
+             "duq4_linear_from_fp16_prelaid_workspace_bytes": ctypes.c_size_t,
              "duq4_linear_host_staging_bytes": ctypes.c_size_t}
 
 if not os.path.exists(LIB_PATH):

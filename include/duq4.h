@@ -259,14 +259,25 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
  * weight tensor. duq4_linear_w4a4_prelaid then runs the layer with BOTH operands in that form on the CTA-pair
  * tensor-core kernel with no in-kernel unpack (any M >= 1; DUQ4_ERR_DEVICE where CTA pairs cannot be scheduled).
  * Results are identical to duq4_linear_w4a4_preunpacked on the packed weights. The packed format stays the
- * format of record (state_dict); a caller derives W_i8 lazily and keeps it beside the packed tensor. */
+ * format of record (state_dict); a caller derives W_i8 lazily and keeps it beside the packed tensor.
+ * split_scratch (optional; NULL / 0 = none): device memory, 256-byte aligned, duq4_gemm_split_scratch_bytes()
+ * bytes. With it, a launch whose tile count leaves a partly filled last round on the GPU's CTA pairs splits
+ * those tiles along K over the idle pairs (int32 partial tiles meet in the scratch and are added before the
+ * dequant -- exact, so the results do not change); without it every tile is computed by one pair. The call
+ * clears the few bytes it needs to start from zero; calls sharing one scratch must not overlap on the GPU. */
 int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W_i8, void *stream);
+size_t duq4_gemm_split_scratch_bytes(void);
 int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K,
-                             const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream);
+                             const duq4_epilogue *epi, void *out, int32_t *acc_out, void *split_scratch,
+                             size_t split_scratch_bytes, void *stream);
 /* duq4_linear_w4a4_from_fp16 on pre-laid-out weights: fused quantizer (tensor-core-ready int8 codes into the
  * workspace) + duq4_linear_w4a4_prelaid; the route for layers that see many tokens at a time (prefill). Same
  * arguments and results as duq4_linear_w4a4_from_fp16 except that W_i8 is the output of duq4_weight_prelayout_i8
- * and K % 128 == 0; the workspace need is that of duq4_linear_from_fp16_workspace_bytes(max(M, 32), K). */
+ * and K % 128 == 0, and the workspace need is duq4_linear_from_fp16_prelaid_workspace_bytes(M, K): codes and
+ * per-token vectors plus about 19 MiB in which the kernel splits the last, partly filled round of tiles along K
+ * (partial int32 tiles of up to 74 CTA pairs), so that a launch whose tile count is just above a multiple of the
+ * pair count does not pay a whole extra round. */
+size_t duq4_linear_from_fp16_prelaid_workspace_bytes(uint32_t M, uint32_t K);
 int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                        float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
                                        size_t workspace_bytes, void *stream);

@@ -434,7 +434,7 @@ def test_preunpacked_activations_match_packed_path(env, mode, M, N, K):
 
 
 @pytest.mark.parametrize("mode", ["sym", "asym_dual"])
-@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (17, 1000, 128), (300, 520, 256), (2000, 2100, 384), (512, 4096, 4096)])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (17, 1000, 128), (300, 520, 256), (2000, 2100, 384), (512, 4096, 4096), (300, 520, 2048)])
 def test_prelaid_int8_weights_match_packed_weights(env, mode, M, N, K):
     """duq4_weight_prelayout_i8 + duq4_linear_w4a4_prelaid (both operands int8 in the tensor-core-ready layout, no
     in-kernel unpack) give the int32 accumulators of the oracle and the fp16 outputs of the packed-weight path."""
@@ -457,7 +457,13 @@ def test_prelaid_int8_weights_match_packed_weights(env, mode, M, N, K):
     out_a = torch.zeros((M, N), dtype=torch.float16, device="cuda"); out_b = torch.full_like(out_a, float("nan"))
     acc_b = torch.full((M, N), -5, dtype=torch.int32, device="cuda")
     L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(dqw), M, N, K, ctypes.byref(epi), L.ptr(out_a), None, st)
-    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(out_b), L.ptr(acc_b), st)
+    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(out_b), L.ptr(acc_b), None, 0, st)
+    # ... and with scratch for the K-split of the last round of tiles (same bits: the partial sums are exact)
+    split = torch.full((L.cdll.duq4_gemm_split_scratch_bytes(),), 0x5A, dtype=torch.uint8, device="cuda")
+    out_c = torch.full_like(out_a, float("nan")); acc_c = torch.full_like(acc_b, -5)
+    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(out_c), L.ptr(acc_c), L.ptr(split), split.numel(), st)
+    torch.cuda.synchronize()
+    assert torch.equal(acc_c, acc_b) and torch.equal(out_c.view(torch.int16), out_b.view(torch.int16))
     torch.cuda.synchronize()
     assert tc_status(L) == 0
     assert np.array_equal(acc_b.cpu().numpy(), o.matmul_4bit(U.i8_codes_to_packed(a8.cpu().numpy()), qw))
@@ -466,9 +472,14 @@ def test_prelaid_int8_weights_match_packed_weights(env, mode, M, N, K):
 
 
 @pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
-@pytest.mark.parametrize("M,N,K", [(5, 264, 128), (300, 520, 1024), (2100, 2000, 256)])
+@pytest.mark.parametrize("M,N,K", [(5, 264, 128), (300, 520, 1024), (2100, 2000, 256),
+                                   # launches whose last round of tiles is split along K: 6 tiles by 8 pairs each (32 k-steps),
+                                   # 150 tiles = 2 full rounds + 2 tiles by 2 pairs each (8 k-steps), 76 tiles = 1 round + 2 tiles by 8
+                                   (300, 520, 4096), (512, 19200, 1024), (256, 19456, 4224)])
 def test_linear_from_fp16_prelaid_equals_packed_weight_entry(env, mode, M, N, K):
-    """The one-call layer on pre-laid-out int8 weights == the one-call layer on the packed weights, bit for bit."""
+    """The one-call layer on pre-laid-out int8 weights == the one-call layer on the packed weights, bit for bit
+    (the packed-weight entry is checked against the oracle elsewhere), including launches that split the tiles of
+    their last round along K and add int32 partial tiles before the dequant."""
     torch, L, o = env
     asym, dual = mode.startswith("asym"), mode.endswith("dual")
     dx = dev(torch, U.acts(M, K, 3, mean=0.1 if asym else 0.0)); dqw = dev(torch, U.rand_codes(N, K, 4))
@@ -477,13 +488,15 @@ def test_linear_from_fp16_prelaid_equals_packed_weight_entry(env, mode, M, N, K)
     epi = L.make_epilogue(mode, None, None, sc1, zc1 if asym else None, sc2 if dual else None, zc2 if mode == "asym_dual" else None, bias)
     w8 = torch.zeros((N, K), dtype=torch.int8, device="cuda")
     L.call("duq4_weight_prelayout_i8", L.ptr(dqw), N, K, L.ptr(w8), L.current_stream())
-    nbytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(max(M, 32), K)
-    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    nbytes = L.cdll.duq4_linear_from_fp16_prelaid_workspace_bytes(M, K)
+    assert nbytes >= L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
+    ws = torch.full((nbytes,), 0xAB, dtype=torch.uint8, device="cuda")   # the call must not rely on a cleared workspace
     want = torch.zeros((M, N), dtype=torch.float16, device="cuda"); got = torch.full_like(want, float("nan"))
     L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(want), L.ptr(ws), nbytes,
            L.current_stream())
-    L.call("duq4_linear_w4a4_from_fp16_prelaid", L.ptr(dx), L.ptr(w8), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(got), L.ptr(ws), nbytes,
-           L.current_stream())
+    for _ in range(2):   # twice: the arrival counters of the K-split are cleared by every call
+        L.call("duq4_linear_w4a4_from_fp16_prelaid", L.ptr(dx), L.ptr(w8), M, N, K, L.MODES[mode], 0.9, ctypes.byref(epi), L.ptr(got), L.ptr(ws), nbytes,
+               L.current_stream())
     torch.cuda.synchronize()
     assert tc_status(L) == 0
     assert U.f16_equal_nan(got.cpu().numpy(), want.cpu().numpy())
