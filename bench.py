@@ -589,13 +589,18 @@ def run_ours(args):
 
     peer = None
     gather_mode = "none" if world == 1 else args.gather
-    if world > 1 and args.gather == "fused":
+    if world > 1 and args.gather in ("fused", "copy"):
         try:
             from duqlinear4bitcuda_b200.parallel import PeerOutput
-            peer = PeerOutput(M, N, device, use_multicast=not args.no_multicast)
+            peer = PeerOutput(M, N, device, use_multicast=args.multicast and args.gather == "fused")
             epi_f = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns),
                                     out_multicast=peer.multicast_column_ptr(rank * Ns))
             gather_mode = "fused, multimem.st through the NVLink switch" if peer.multicast_ptr else "fused, one st.global per peer"
+            if args.gather == "copy":
+                gather_mode = "copy engines: 2-D peer copies per row chunk, overlapped with the next chunk's GEMM"
+                epi_c = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns))
+                copy_staging_bytes = L.cdll.duq4_linear_pipeline_staging_bytes(0, 1, M, Ns, K, args.chunk_rows)
+                copy_staging = torch.empty(copy_staging_bytes, dtype=torch.uint8, device=device)
         except Exception as ex:  # symmetric memory not available on this box: use the collective
             peer = None
             gather_mode = f"nccl (symmetric memory unavailable: {type(ex).__name__})"
@@ -603,6 +608,16 @@ def run_ours(args):
     def step(ev=None):
         # the two launches duq4_linear_w4a4_from_fp16 makes, issued separately so that the GEMM
         # launch can be bracketed by its own events
+        if peer is not None and args.gather == "copy":
+            peer.barrier()   # every rank has consumed the previous result
+            if ev:
+                ev[0].record()
+            L.call("duq4_linear_w4a4_from_fp16_to_peers", L.ptr(x), L.ptr(w8), 1, M, Ns, K, L.MODE_SYM, 1.0, ctypes.byref(epi_c), rank,
+                   args.chunk_rows, L.ptr(copy_staging), copy_staging_bytes, st())
+            if ev:
+                ev[1].record()
+            peer.barrier()   # every rank's block has landed everywhere
+            return
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(codes), L.ptr(sa), None, None, None, st())
         if ev:
             ev[0].record()
@@ -643,11 +658,27 @@ def run_ours(args):
         e2e_x, e2e_out = shared_x.tensor, shared_out.tensor
         e2e_out_ptr = e2e_out.data_ptr() + 2 * rank * Ns
     epi_host = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N)
-    staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, Ns, K, 0)
+    if world == 1:
+        staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, Ns, K, 0)
+    else:
+        staging_bytes = L.cdll.duq4_linear_pipeline_staging_bytes(1, 1, M, Ns, K, 0)
+        rows_per = -(-M // world)
+        x_gather = torch.empty((rows_per * world, K), dtype=torch.float16, device=device)
+        x_slice = torch.zeros((rows_per, K), dtype=torch.float16, device=device)
+        r0, r1 = min(M, rank * rows_per), min(M, (rank + 1) * rows_per)
     staging = torch.empty(staging_bytes, dtype=torch.uint8, device=device)
 
     def step_e2e():
-        L.call("duq4_linear_w4a4_from_fp16_host", e2e_x.data_ptr(), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0,
+        if world == 1:
+            L.call("duq4_linear_w4a4_from_fp16_host", e2e_x.data_ptr(), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0,
+                   ctypes.byref(epi_host), e2e_out_ptr, 0, L.ptr(staging), staging_bytes, st())
+            return
+        # every byte crosses PCIe once: this rank uploads its row slice of the one host input over its own link, the
+        # slices are all-gathered over NVLink (the path's one exchange step), the rank computes its column block and
+        # delivers it into its column slice of the one host result, download overlapped with the arithmetic
+        x_slice[: r1 - r0].copy_(e2e_x[r0:r1], non_blocking=True)
+        dist.all_gather_into_tensor(x_gather, x_slice)
+        L.call("duq4_linear_w4a4_from_fp16_to_host", L.ptr(x_gather), L.ptr(w8), 1, M, Ns, K, L.MODE_SYM, 1.0,
                ctypes.byref(epi_host), e2e_out_ptr, 0, L.ptr(staging), staging_bytes, st())
 
     def barrier():
@@ -700,6 +731,7 @@ def run_ours(args):
 
     # ---- correctness of what was timed, computed OUTSIDE the timed regions -------------------------------
     checks = {}
+    L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(codes), L.ptr(sa), None, None, None, st())
     L.call("duq4_linear_w4a4_preunpacked", L.ptr(codes), L.ptr(qw), M, Ns, K, ctypes.byref(epi), L.ptr(out_shard), None, st())
     torch.cuda.synchronize()
     if world > 1:
@@ -752,15 +784,16 @@ def run_ours(args):
                                   "route on the packed tensor is timed under weight_prelayout_ablation", "activations": "N(0,1), 1% channels x20, per-token symmetric int4"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_tops, 2), "unit": "TOPS", "ms_per_step": round(e2e_ms / args.steps, 4),
-                    "h2d_bytes_per_step": world * M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                     "api": ("duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, copies pipelined with the arithmetic over row chunks)"
                             if world == 1 else
-                            "duq4_linear_w4a4_from_fp16_host (C ABI) on every rank: one input and one result in shared pinned host memory; each rank "
-                            "uploads the activations over its own PCIe link (h2d counts all ranks) and delivers its [M, N/G] column block into its "
-                            "column slice of the one host result; no device-side gather")},
+                            "one input and one result in shared pinned host memory; each rank uploads its row slice of the activations over its own "
+                            "PCIe link, NCCL all-gather of the slices over NVLink, duq4_linear_w4a4_from_fp16_to_host (C ABI) per rank delivers its "
+                            "[M, N/G] column block into its column slice of the one host result, download overlapped with the arithmetic")},
             "checks": checks,
             "sustained": sustained,
-            "gpu_launches": args.steps * (4 if peer is not None else 2),   # per rank: quantize + GEMM (+ two barrier kernels around the fused gather)
+            "gpu_launches": args.steps * ((2 * -(-M // max(256, -(-(args.chunk_rows or (M + 15) // 16) // 256) * 256)) + 2) if (peer is not None and args.gather == "copy")
+                                          else (4 if peer is not None else 2)),   # per rank: quantize + GEMM (per row chunk with --gather copy) + two barrier kernels around a device-side gather
             "roofline": {"kernel": "gemm_tc2_kernel<WI8> (CTA pairs, 256x256x128 tiles, tcgen05.mma.cta_group::2.kind::i8; A int8 from the fused quantizer, W int8 pre-laid-out, both straight from TMA into the MMA ring)", "bound": "tensor",
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
                          "frac": round(gemm_tops / int8_peak, 4),
@@ -800,9 +833,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N>1: 'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
-    ap.add_argument("--no-multicast", action="store_true", help="N>1, fused gather: one plain store per peer instead of multimem.st")
+    ap.add_argument("--gather", default="fused", choices=["copy", "fused", "nccl"],
+                    help="N>1: 'copy' = local epilogue + copy-engine peer copies per row chunk, overlapped with the next chunk's GEMM; "
+                         "'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
+    ap.add_argument("--multicast", action="store_true", help="N>1, --gather fused: one multimem.st per row segment instead of one plain store per peer")
+    ap.add_argument("--chunk-rows", type=int, default=0, help="N>1, --gather copy: rows per pipeline chunk (0 = M/16 rounded to 256)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2-second back-to-back run")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -8,9 +8,19 @@
 //     download stream : out chunk c-1 device -> host
 //
 // The output is 3.5x larger than the input for the layers this library targets (N > K), so the
-// download leg bounds the call; the upload and the arithmetic hide behind it. The two helper
+// download leg bounds the call; the upload and the arithmetic hide behind it. The helper
 // streams fork from the caller's stream at entry and join it before the call returns, so the
 // call is ordered like a single piece of work on that stream.
+//
+// Two relatives share the machinery (run_pipeline):
+//   duq4_linear_w4a4_from_fp16_to_host   activations already on the device (e.g. gathered from the ranks' row
+//                                        slices over NVLink), result to host memory: arithmetic of chunk c overlaps
+//                                        the download of chunk c-1;
+//   duq4_linear_w4a4_from_fp16_to_peers  N-sharded layer whose [M, N] result is replicated on every rank: the GEMM
+//                                        of chunk c writes this rank's column block into its OWN result buffer and the
+//                                        copy engines push chunk c-1 to the other ranks' buffers (2-D peer copies over
+//                                        NVLink, one helper stream per peer) -- the all-gather runs on the copy
+//                                        engines, overlapped with the arithmetic, instead of as stores of the epilogue.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -22,10 +32,14 @@ namespace {
 constexpr int kMaxDevices = 64;
 constexpr uint32_t kMaxChunks = 64;
 
+constexpr int kMaxPeers = DUQ4_MAX_OUT_PEERS;
+
 struct PipeState {
     bool ready = false;
     cudaStream_t up = nullptr, down = nullptr;
+    cudaStream_t peer[kMaxPeers] = {};
     cudaEvent_t fork = nullptr, join_down = nullptr;
+    cudaEvent_t join_peer[kMaxPeers] = {};
     cudaEvent_t uploaded[kMaxChunks] = {}, computed[kMaxChunks] = {};
 };
 
@@ -49,6 +63,10 @@ int pipe_state(PipeState **out) {
             if (t.down) cudaStreamDestroy(t.down);
             if (t.fork) cudaEventDestroy(t.fork);
             if (t.join_down) cudaEventDestroy(t.join_down);
+            for (int i = 0; i < kMaxPeers; ++i) {
+                if (t.peer[i]) cudaStreamDestroy(t.peer[i]);
+                if (t.join_peer[i]) cudaEventDestroy(t.join_peer[i]);
+            }
             for (uint32_t i = 0; i < kMaxChunks; ++i) {
                 if (t.uploaded[i]) cudaEventDestroy(t.uploaded[i]);
                 if (t.computed[i]) cudaEventDestroy(t.computed[i]);
@@ -59,6 +77,10 @@ int pipe_state(PipeState **out) {
         if ((e = cudaStreamCreateWithFlags(&t.down, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
         if ((e = cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
         if ((e = cudaEventCreateWithFlags(&t.join_down, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
+        for (int i = 0; i < kMaxPeers; ++i) {
+            if ((e = cudaStreamCreateWithFlags(&t.peer[i], cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+            if ((e = cudaEventCreateWithFlags(&t.join_peer[i], cudaEventDisableTiming)) != cudaSuccess) return fail(e);
+        }
         for (uint32_t i = 0; i < kMaxChunks; ++i) {
             if ((e = cudaEventCreateWithFlags(&t.uploaded[i], cudaEventDisableTiming)) != cudaSuccess) return fail(e);
             if ((e = cudaEventCreateWithFlags(&t.computed[i], cudaEventDisableTiming)) != cudaSuccess) return fail(e);
@@ -84,39 +106,44 @@ uint32_t pick_chunk_rows(uint32_t M, uint32_t chunk_rows) {
     return (uint32_t)r;
 }
 
-}  // namespace
+// Where a chunk's fp16 result goes.
+struct Sink {
+    void *host = nullptr;          // host sink: base of the [M, ldo] host result (first column of this call's block)
+    void *const *peers = nullptr;  // peer sink: every rank's [M, ldo] device buffer at this block's first column, own included
+    uint32_t n_peers = 0, self = 0;
+};
 
-extern "C" {
-
-size_t duq4_linear_host_staging_bytes(uint32_t M, uint32_t N, uint32_t K, uint32_t chunk_rows) {
-    if (M == 0 || N == 0 || K == 0) return 0;
-    const uint32_t rows = pick_chunk_rows(M, chunk_rows);
-    return align_up((size_t)M * K * 2, 256) + align_up((size_t)M * N * 2, 256) +
-           align_up(duq4_linear_from_fp16_workspace_bytes(rows, K), 256);
+size_t pipeline_staging_bytes(bool x_on_host, bool host_sink, bool prelaid, uint32_t M, uint32_t N, uint32_t K, uint32_t rows) {
+    return (x_on_host ? align_up((size_t)M * K * 2, 256) : 0) + (host_sink ? align_up((size_t)M * N * 2, 256) : 0) +
+           align_up(prelaid ? duq4_linear_from_fp16_prelaid_workspace_bytes(rows, K) : duq4_linear_from_fp16_workspace_bytes(rows, K), 256);
 }
 
-int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
-                                    int act_mode, float clip_ratio, const duq4_epilogue *epi, void *out_host,
-                                    uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream) {
-    if (!x_host || !W || !epi || !out_host) return DUQ4_ERR_NULL;
-    if (epi->n_out_peers != 0) return DUQ4_ERR_MODE;   // the result goes to host memory, not to peers
+int run_pipeline(const void *x, bool x_on_host, const void *W, bool prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                 float clip_ratio, const duq4_epilogue *epi, const Sink &sink, uint32_t chunk_rows, void *staging, size_t staging_bytes,
+                 void *stream) {
+    const bool host_sink = sink.host != nullptr;
+    if (!x || !W || !epi || (!host_sink && (!sink.peers || sink.n_peers == 0))) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0) return DUQ4_OK;
-    if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (K == 0 || K % 64 != 0 || (prelaid && K % 128 != 0)) return DUQ4_ERR_SHAPE;
     const uint64_t ldo = epi->ldo ? epi->ldo : N;
     if (ldo < N) return DUQ4_ERR_SHAPE;
+    if (!host_sink && (sink.n_peers > (uint32_t)kMaxPeers || sink.self >= sink.n_peers)) return DUQ4_ERR_SHAPE;
+    const uint32_t rows = pick_chunk_rows(M, chunk_rows);
     if (!staging || (reinterpret_cast<uintptr_t>(staging) & 255) != 0 ||
-        staging_bytes < duq4_linear_host_staging_bytes(M, N, K, chunk_rows))
+        staging_bytes < pipeline_staging_bytes(x_on_host, host_sink, prelaid, M, N, K, rows))
         return DUQ4_ERR_WORKSPACE;
     PipeState *ps = nullptr;
     int rc = pipe_state(&ps);
     if (rc) return rc;
 
-    const uint32_t rows = pick_chunk_rows(M, chunk_rows);
     const uint32_t chunks = (M + rows - 1) / rows;
-    uint8_t *x_dev = (uint8_t *)staging;
-    uint8_t *o_dev = x_dev + align_up((size_t)M * K * 2, 256);
-    uint8_t *ws = o_dev + align_up((size_t)M * N * 2, 256);
-    const size_t ws_bytes = duq4_linear_from_fp16_workspace_bytes(rows, K);
+    uint8_t *cur = (uint8_t *)staging;
+    uint8_t *x_dev = x_on_host ? cur : (uint8_t *)const_cast<void *>(x);
+    if (x_on_host) cur += align_up((size_t)M * K * 2, 256);
+    uint8_t *o_dev = host_sink ? cur : nullptr;
+    if (host_sink) cur += align_up((size_t)M * N * 2, 256);
+    uint8_t *ws = cur;
+    const size_t ws_bytes = prelaid ? duq4_linear_from_fp16_prelaid_workspace_bytes(rows, K) : duq4_linear_from_fp16_workspace_bytes(rows, K);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     std::lock_guard<std::mutex> enqueue_lock(g_call_mu);
@@ -126,40 +153,116 @@ int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32
         if (e != cudaSuccess) return (int)e; \
     } while (0)
 
-    // fork: earlier work of the caller's stream may still use the staging area
+    // fork: earlier work of the caller's stream may still use the staging area / the result buffers
     DUQ4_TRY(cudaEventRecord(ps->fork, st));
-    DUQ4_TRY(cudaStreamWaitEvent(ps->up, ps->fork, 0));
-    DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->fork, 0));
-    for (uint32_t c = 0; c < chunks; ++c) {
-        const uint32_t r0 = c * rows, nr = (M - r0 < rows) ? M - r0 : rows;
-        DUQ4_TRY(cudaMemcpyAsync(x_dev + (size_t)r0 * K * 2, (const uint8_t *)x_host + (size_t)r0 * K * 2,
-                                 (size_t)nr * K * 2, cudaMemcpyHostToDevice, ps->up));
-        DUQ4_TRY(cudaEventRecord(ps->uploaded[c], ps->up));
+    if (x_on_host) DUQ4_TRY(cudaStreamWaitEvent(ps->up, ps->fork, 0));
+    if (host_sink) DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->fork, 0));
+    if (!host_sink)
+        for (uint32_t p = 0; p < sink.n_peers; ++p)
+            if (p != sink.self) DUQ4_TRY(cudaStreamWaitEvent(ps->peer[p], ps->fork, 0));
+    if (x_on_host) {
+        for (uint32_t c = 0; c < chunks; ++c) {
+            const uint32_t r0 = c * rows, nr = (M - r0 < rows) ? M - r0 : rows;
+            DUQ4_TRY(cudaMemcpyAsync(x_dev + (size_t)r0 * K * 2, (const uint8_t *)x + (size_t)r0 * K * 2, (size_t)nr * K * 2,
+                                     cudaMemcpyHostToDevice, ps->up));
+            DUQ4_TRY(cudaEventRecord(ps->uploaded[c], ps->up));
+        }
     }
     duq4_epilogue dev_epi = *epi;
-    dev_epi.ldo = N;   // the device copy of the output is dense; the row pitch is applied by the download
+    dev_epi.n_out_peers = 0;
+    dev_epi.out_multicast = nullptr;
+    if (host_sink) dev_epi.ldo = N;   // the device copy of the output is dense; the row pitch is applied by the download
     for (uint32_t c = 0; c < chunks; ++c) {
         const uint32_t r0 = c * rows, nr = (M - r0 < rows) ? M - r0 : rows;
-        DUQ4_TRY(cudaStreamWaitEvent(st, ps->uploaded[c], 0));
-        rc = duq4_linear_w4a4_from_fp16(x_dev + (size_t)r0 * K * 2, W, nr, N, K, act_mode, clip_ratio, &dev_epi,
-                                        o_dev + (size_t)r0 * N * 2, ws, ws_bytes, stream);
+        if (x_on_host) DUQ4_TRY(cudaStreamWaitEvent(st, ps->uploaded[c], 0));
+        uint8_t *o_chunk = host_sink ? o_dev + (size_t)r0 * N * 2 : (uint8_t *)sink.peers[sink.self] + (size_t)r0 * ldo * 2;
+        rc = prelaid ? duq4_linear_w4a4_from_fp16_prelaid(x_dev + (size_t)r0 * K * 2, (const int8_t *)W, nr, N, K, act_mode, clip_ratio, &dev_epi,
+                                                          o_chunk, ws, ws_bytes, stream)
+                     : duq4_linear_w4a4_from_fp16(x_dev + (size_t)r0 * K * 2, (const uint8_t *)W, nr, N, K, act_mode, clip_ratio, &dev_epi, o_chunk,
+                                                  ws, ws_bytes, stream);
         if (rc) break;   // still join the helper streams below
         DUQ4_TRY(cudaEventRecord(ps->computed[c], st));
-        DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->computed[c], 0));
-        uint8_t *dst = (uint8_t *)out_host + (size_t)r0 * ldo * 2;
-        if (ldo == N)
-            DUQ4_TRY(cudaMemcpyAsync(dst, o_dev + (size_t)r0 * N * 2, (size_t)nr * N * 2, cudaMemcpyDeviceToHost, ps->down));
-        else
-            DUQ4_TRY(cudaMemcpy2DAsync(dst, ldo * 2, o_dev + (size_t)r0 * N * 2, (size_t)N * 2, (size_t)N * 2, nr,
-                                       cudaMemcpyDeviceToHost, ps->down));
+        if (host_sink) {
+            DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->computed[c], 0));
+            uint8_t *dst = (uint8_t *)sink.host + (size_t)r0 * ldo * 2;
+            if (ldo == N)
+                DUQ4_TRY(cudaMemcpyAsync(dst, o_chunk, (size_t)nr * N * 2, cudaMemcpyDeviceToHost, ps->down));
+            else
+                DUQ4_TRY(cudaMemcpy2DAsync(dst, ldo * 2, o_chunk, (size_t)N * 2, (size_t)N * 2, nr, cudaMemcpyDeviceToHost, ps->down));
+        } else {
+            // this chunk of the block to every other rank, starting with the next rank so that the ranks' copies fan
+            // out over different destinations at any one time
+            for (uint32_t k = 1; k < sink.n_peers; ++k) {
+                const uint32_t p = (sink.self + k) % sink.n_peers;
+                DUQ4_TRY(cudaStreamWaitEvent(ps->peer[p], ps->computed[c], 0));
+                DUQ4_TRY(cudaMemcpy2DAsync((uint8_t *)sink.peers[p] + (size_t)r0 * ldo * 2, ldo * 2, o_chunk, ldo * 2, (size_t)N * 2, nr,
+                                           cudaMemcpyDeviceToDevice, ps->peer[p]));
+            }
+        }
     }
-    // join: the caller's stream continues after the last download (and after every upload, which
-    // matters only on the error path -- on success each upload was already waited for)
-    DUQ4_TRY(cudaStreamWaitEvent(st, ps->uploaded[chunks - 1], 0));
-    DUQ4_TRY(cudaEventRecord(ps->join_down, ps->down));
-    DUQ4_TRY(cudaStreamWaitEvent(st, ps->join_down, 0));
+    // join: the caller's stream continues after the last copy (and after every upload, which matters only on the
+    // error path -- on success each upload was already waited for)
+    if (x_on_host) DUQ4_TRY(cudaStreamWaitEvent(st, ps->uploaded[chunks - 1], 0));
+    if (host_sink) {
+        DUQ4_TRY(cudaEventRecord(ps->join_down, ps->down));
+        DUQ4_TRY(cudaStreamWaitEvent(st, ps->join_down, 0));
+    } else {
+        for (uint32_t p = 0; p < sink.n_peers; ++p) {
+            if (p == sink.self) continue;
+            DUQ4_TRY(cudaEventRecord(ps->join_peer[p], ps->peer[p]));
+            DUQ4_TRY(cudaStreamWaitEvent(st, ps->join_peer[p], 0));
+        }
+    }
 #undef DUQ4_TRY
     return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t duq4_linear_host_staging_bytes(uint32_t M, uint32_t N, uint32_t K, uint32_t chunk_rows) {
+    if (M == 0 || N == 0 || K == 0) return 0;
+    return pipeline_staging_bytes(true, true, false, M, N, K, pick_chunk_rows(M, chunk_rows));
+}
+
+int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                    float clip_ratio, const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows, void *staging,
+                                    size_t staging_bytes, void *stream) {
+    if (!out_host) return DUQ4_ERR_NULL;
+    if (epi && epi->n_out_peers != 0) return DUQ4_ERR_MODE;   // the result goes to host memory, not to peers
+    Sink sink;
+    sink.host = out_host;
+    return run_pipeline(x_host, true, W, false, M, N, K, act_mode, clip_ratio, epi, sink, chunk_rows, staging, staging_bytes, stream);
+}
+
+size_t duq4_linear_pipeline_staging_bytes(int to_host, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, uint32_t chunk_rows) {
+    if (M == 0 || N == 0 || K == 0) return 0;
+    return pipeline_staging_bytes(false, to_host != 0, w_is_prelaid != 0, M, N, K, pick_chunk_rows(M, chunk_rows));
+}
+
+int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                       float clip_ratio, const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows, void *staging,
+                                       size_t staging_bytes, void *stream) {
+    if (!out_host) return DUQ4_ERR_NULL;
+    if (epi && epi->n_out_peers != 0) return DUQ4_ERR_MODE;
+    Sink sink;
+    sink.host = out_host;
+    return run_pipeline(x, false, W, w_is_prelaid != 0, M, N, K, act_mode, clip_ratio, epi, sink, chunk_rows, staging, staging_bytes, stream);
+}
+
+int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                        float clip_ratio, const duq4_epilogue *epi, uint32_t self_index, uint32_t chunk_rows, void *staging,
+                                        size_t staging_bytes, void *stream) {
+    if (!epi) return DUQ4_ERR_NULL;
+    if (epi->n_out_peers == 0 || epi->n_out_peers > DUQ4_MAX_OUT_PEERS) return DUQ4_ERR_SHAPE;
+    for (uint32_t i = 0; i < epi->n_out_peers; ++i)
+        if (!epi->out_peers[i]) return DUQ4_ERR_NULL;
+    Sink sink;
+    sink.peers = epi->out_peers;
+    sink.n_peers = epi->n_out_peers;
+    sink.self = self_index;
+    return run_pipeline(x, false, W, w_is_prelaid != 0, M, N, K, act_mode, clip_ratio, epi, sink, chunk_rows, staging, staging_bytes, stream);
 }
 
 }  // extern "C"

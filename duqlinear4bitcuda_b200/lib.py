@@ -83,6 +83,9 @@ SIGNATURES = {
     "duq4_linear_w4a4_gate_up_silu": [_vp, _i, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
     "duq4_linear_host_staging_bytes": [_u32, _u32, _u32, _u32],
     "duq4_linear_w4a4_from_fp16_host": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _u32, _vp, _sz, _vp],
+    "duq4_linear_pipeline_staging_bytes": [_i, _i, _u32, _u32, _u32, _u32],
+    "duq4_linear_w4a4_from_fp16_to_host": [_vp, _vp, _i, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _u32, _vp, _sz, _vp],
+    "duq4_linear_w4a4_from_fp16_to_peers": [_vp, _vp, _i, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _u32, _u32, _vp, _sz, _vp],
     "duq4_linear_w4a4_from_fp16_static": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp],
     "duq4_peer_barrier": [ctypes.POINTER(ctypes.c_void_p), _u32, _u32, ctypes.c_uint64, ctypes.c_uint64, _vp],
     "duq4_last_device_status": [_vp, ctypes.POINTER(ctypes.c_int32)],
@@ -90,7 +93,7 @@ SIGNATURES = {
 _RESTYPES = {"duq4_version": ctypes.c_char_p, "duq4_error_string": ctypes.c_char_p,
              "duq4_linear_from_fp16_workspace_bytes": ctypes.c_size_t, "duq4_gemm_split_scratch_bytes": ctypes.c_size_t,
              "duq4_linear_from_fp16_prelaid_workspace_bytes": ctypes.c_size_t,
-             "duq4_linear_host_staging_bytes": ctypes.c_size_t}
+             "duq4_linear_host_staging_bytes": ctypes.c_size_t, "duq4_linear_pipeline_staging_bytes": ctypes.c_size_t}
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

@@ -195,6 +195,8 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         self._ws = None
         self._peer = None
         self._staging = None
+        self._x_dev = self._x_slice = None
+        self._w8 = None
 
     @classmethod
     def from_full(cls, mode, weight, scales_1, zeros_1=None, scales_2=None, zeros_2=None, bias=None, clip_ratio=1.0,
@@ -232,14 +234,35 @@ class ColumnParallelLinear4bit(torch.nn.Module):
                        L.current_stream())
         return out
 
+    # Layers that see at least this many tokens run on a lazily built int8 re-layout of this rank's weight rows
+    # (no unpack in the GEMM); fewer tokens stream the packed rows. See nn/linear.py `weight_prelayout`.
+    weight_prelayout = True
+    prelayout_min_tokens = 256
+
+    def _weights_for(self, tokens, K):
+        """(device pointer argument, w_is_prelaid flag) for the pipeline entry points."""
+        from . import lib as L
+        if self.weight_prelayout and tokens >= self.prelayout_min_tokens and K % 128 == 0 and self.weight.shape[0] > 0:
+            w = self.weight
+            key = (w.data_ptr(), w._version)
+            if self._w8 is None or self._w8[0] != key:
+                w8 = torch.empty((w.shape[0], K), dtype=torch.int8, device=w.device)
+                with torch.cuda.device(w.device):
+                    L.call("duq4_weight_prelayout_i8", L.ptr(w), w.shape[0], K, L.ptr(w8), L.current_stream())
+                self._w8 = (key, w8)
+            return L.ptr(self._w8[1]), 1
+        return L.ptr(self.weight), 0
+
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0):
         """The layer for a job whose activations and result live in HOST memory that every rank maps
-        (`SharedHostTensor`; any pinned host tensor when world == 1): this rank uploads the activations,
-        computes its column block and delivers it into its column slice of `out_host` [M, n_out], all inside
-        one call of the host-buffer entry point of the C ABI (upload, arithmetic and download pipelined over
-        row chunks on this rank's own copy engines). No collective runs: the result is complete once every
-        rank's stream has finished (synchronize, then a host barrier). x_host fp16 [M, K]; out_host fp16
-        [M, n_out] row-major."""
+        (`SharedHostTensor`; any pinned host tensor when world == 1). PCIe is the scarce resource of such a job,
+        NVLink is idle, so every byte crosses PCIe once: rank r uploads rows [r*M/G, (r+1)*M/G) of the activations
+        over its own link, the row slices are all-gathered on the devices (NCCL over NVLink, the one exchange
+        step), every rank computes its column block and delivers it into its column slice of `out_host`
+        [M, n_out] with the download of a row chunk overlapping the arithmetic of the next
+        (duq4_linear_w4a4_from_fp16_to_host). One rank: upload, arithmetic and download pipelined by the
+        host-buffer entry point. The result is complete once every rank's stream has finished (synchronize, then
+        a host barrier). x_host fp16 [M, K]; out_host fp16 [M, n_out] row-major."""
         from . import lib as L
         if x_host.is_cuda or out_host.is_cuda:
             raise ValueError("forward_host takes host tensors")
@@ -249,17 +272,38 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         if tuple(out_host.shape) != (M, self.n_out):
             raise ValueError(f"out_host must be [{M}, {self.n_out}]")
         byte_off, ldo, n_local = host_result_slice(self.n_out, self.world, self.rank)
-        if n_local == 0 or M == 0:
+        if M == 0:
             return
         dev = self.weight.device
-        need = L.cdll.duq4_linear_host_staging_bytes(M, n_local, K, chunk_rows)
-        if self._staging is None or self._staging.numel() < need:
-            self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
         flat = lambda t: None if t is None else t.reshape(-1)
         epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
                               flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=ldo)
+        if self.world == 1:
+            need = L.cdll.duq4_linear_host_staging_bytes(M, n_local, K, chunk_rows)
+            if self._staging is None or self._staging.numel() < need:
+                self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
+                       float(self.clip_ratio), ctypes.byref(epi), out_host.data_ptr() + byte_off, chunk_rows, L.ptr(self._staging),
+                       self._staging.numel(), L.current_stream())
+            return
+        # rows of the activations this rank uploads; the gather needs equal slices, so the device copy is padded
+        per = -(-M // self.world)
+        r0, r1 = min(M, self.rank * per), min(M, (self.rank + 1) * per)
+        if self._x_dev is None or self._x_dev.shape != (per * self.world, K):
+            self._x_dev = torch.empty((per * self.world, K), dtype=torch.float16, device=dev)
+            self._x_slice = torch.zeros((per, K), dtype=torch.float16, device=dev)
+        if r1 > r0:
+            self._x_slice[: r1 - r0].copy_(x_host[r0:r1], non_blocking=True)
+        dist.all_gather_into_tensor(self._x_dev, self._x_slice, group=self.group)
+        if n_local == 0:
+            return
+        wptr, prelaid = self._weights_for(M, K)
+        need = L.cdll.duq4_linear_pipeline_staging_bytes(1, prelaid, M, n_local, K, chunk_rows)
+        if self._staging is None or self._staging.numel() < need:
+            self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
-            L.call("duq4_linear_w4a4_from_fp16_host", x_host.data_ptr(), L.ptr(self.weight), M, n_local, K, L.MODES[self.mode],
+            L.call("duq4_linear_w4a4_from_fp16_to_host", L.ptr(self._x_dev), wptr, prelaid, M, n_local, K, L.MODES[self.mode],
                    float(self.clip_ratio), ctypes.byref(epi), out_host.data_ptr() + byte_off, chunk_rows, L.ptr(self._staging),
                    self._staging.numel(), L.current_stream())
 
@@ -267,12 +311,41 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         """gather="nccl": compute the local block, then one NCCL all-gather (+ re-layout copy).
         gather="fused": the kernel's epilogue writes the block into every rank's result buffer over
         NVLink (one multicast store per row segment where the switch offers a multicast mapping, else one
-        store per peer; gather="fused_peer" forces the latter); two device-side barriers bracket the launch (peers finished reading
+        store per peer; gather="fused_peer" forces the latter; gather="copy": the epilogue writes the local buffer only
+        and copy engines push row chunks to the peers while the next chunk is computed); two device-side barriers
+        bracket the launch (peers finished reading
         the previous result / everybody finished writing this one). The returned tensor is a view
         of that shared buffer: it is overwritten by the next fused forward of the same shape."""
         x2d = x.reshape(-1, x.shape[-1]).contiguous()
         if self.world == 1:
             full = self.local_forward(x2d)
+        elif gather == "copy":
+            # the all-gather on the copy engines: the GEMM of a row chunk writes this rank's block into its own
+            # result buffer and 2-D peer copies push the previous chunk to the other ranks meanwhile
+            from . import lib as L
+            M, K = x2d.shape
+            if self._peer is None:
+                self._peer = {}
+            peer = self._peer.get((M, gather))
+            if peer is None:
+                peer = self._peer[(M, gather)] = PeerOutput(M, self.n_out, x2d.device, self.group, use_multicast=False)
+            n_local = self.col_end - self.col_begin
+            flat = lambda t: None if t is None else t.reshape(-1)
+            epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                                  flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=self.n_out,
+                                  out_peers=peer.column_ptrs(self.col_begin))
+            wptr, prelaid = self._weights_for(M, K)
+            need = L.cdll.duq4_linear_pipeline_staging_bytes(0, prelaid, M, max(n_local, 1), K, 0)
+            if self._staging is None or self._staging.numel() < need:
+                self._staging = torch.empty(need, dtype=torch.uint8, device=x2d.device)
+            peer.barrier()
+            if n_local:
+                with torch.cuda.device(x2d.device):
+                    L.call("duq4_linear_w4a4_from_fp16_to_peers", L.ptr(x2d), wptr, prelaid, M, n_local, K, L.MODES[self.mode],
+                           float(self.clip_ratio), ctypes.byref(epi), self.rank, 0, L.ptr(self._staging), self._staging.numel(),
+                           L.current_stream())
+            peer.barrier()
+            full = peer.buf
         elif gather in ("fused", "fused_peer"):
             M = x2d.shape[0]
             if self._peer is None:

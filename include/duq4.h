@@ -377,6 +377,27 @@ int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32
                                     const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows,
                                     void *staging, size_t staging_bytes, void *stream);
 
+/* Relatives of the host-buffer entry point, same chunked pipeline (no reference counterpart). W is the packed
+ * weight tensor (w_is_prelaid = 0) or the int8 re-layout of duq4_weight_prelayout_i8 (w_is_prelaid != 0).
+ * `staging`: device memory, 256-byte aligned, duq4_linear_pipeline_staging_bytes(to_host, w_is_prelaid, M, N, K,
+ * chunk_rows) bytes.
+ *   _to_host : x fp16 [M, K] is already on the DEVICE (e.g. each rank uploaded a row slice of a host-resident
+ *              input and the slices were all-gathered over NVLink), the result goes to HOST memory out_host
+ *              [M, epi->ldo or N]; the arithmetic of a chunk overlaps the download of the previous one.
+ *   _to_peers: N-sharded layer with a replicated result. epi->out_peers[0..n) are every rank's [M, epi->ldo]
+ *              device buffers at this shard's first column (as for the fused all-gather) and self_index names
+ *              the entry that is this rank's own buffer. The GEMM of a chunk writes the block into the OWN
+ *              buffer; copy engines then push the chunk to the other ranks (2-D peer copies on one helper
+ *              stream per peer) while the next chunk is computed. epi->out_multicast is ignored. The caller
+ *              brackets the call with duq4_peer_barrier as for the fused all-gather. */
+size_t duq4_linear_pipeline_staging_bytes(int to_host, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, uint32_t chunk_rows);
+int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K,
+                                       int act_mode, float clip_ratio, const duq4_epilogue *epi, void *out_host,
+                                       uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream);
+int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K,
+                                        int act_mode, float clip_ratio, const duq4_epilogue *epi, uint32_t self_index,
+                                        uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream);
+
 /* Device-side barrier across the ranks of an N-sharded layer, on `stream` (no reference counterpart; it
  * brackets the fused all-gather: "everybody has consumed the previous result" / "everybody's block has
  * landed"). flag_ptrs: HOST array of `world` device addresses, entry r = rank r's flag array of `world`

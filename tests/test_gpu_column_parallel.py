@@ -40,6 +40,8 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
         y_fused = layer(x, gather="fused").clone()   # epilogue stores (multicast where offered) instead of the collective
         y_fused2 = layer(x, gather="fused").clone()  # reuse of the shared buffer
         y_peer = layer(x, gather="fused_peer").clone()   # one plain store per peer
+        y_copy = layer(x, gather="copy").clone()         # local epilogue + copy-engine peer copies per row chunk
+        y_copy2 = layer(x, gather="copy").clone()
         torch.cuda.synchronize()
         status = ctypes.c_int32(-1)
         L.call("duq4_last_device_status", L.current_stream(), ctypes.byref(status))
@@ -52,6 +54,7 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
         ok = ok and torch.equal(y_fused.view(torch.int16), y1.view(torch.int16))
         ok = ok and torch.equal(y_fused2.view(torch.int16), y1.view(torch.int16))
         ok = ok and torch.equal(y_peer.view(torch.int16), y1.view(torch.int16)) and status.value == 0
+        ok = ok and torch.equal(y_copy.view(torch.int16), y1.view(torch.int16)) and torch.equal(y_copy2.view(torch.int16), y1.view(torch.int16))
         open(os.path.join(tmp, f"r{rank}"), "w").write(str(int(ok)))
     finally:
         dist.destroy_process_group()
@@ -167,11 +170,12 @@ def _host_worker(rank, world, port, mode, M, N, K, tmp):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 4096), ("asym", 700, 1040, 512), ("sym", 2048, 8192, 256)])
+@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 4096), ("asym", 701, 1040, 512), ("sym", 2048, 8192, 256)])
 def test_two_gpu_host_result_assembled_by_slices_matches_single_gpu(tmp_path, mode, M, N, K):
-    """Host-resident job on 2 GPUs: each rank uploads the activations from the one shared pinned host
-    input and delivers its column block into its slice of the one shared host result; the assembled
-    result equals the 1-GPU host entry point bit for bit."""
+    """Host-resident job on 2 GPUs: each rank uploads its row slice of the one shared pinned host input (ragged: 701
+    rows), the slices are all-gathered over NVLink, and each rank delivers its column block into its slice of the one
+    shared host result; the assembled result equals the 1-GPU host entry point bit for bit (packed weights at 8 tokens,
+    the pre-laid-out int8 copy from 256 tokens on)."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
