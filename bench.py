@@ -339,6 +339,57 @@ def time_mlp_block(torch, L, device):
             "ms_per_block_glue_kernel_variant": round(ms_glue, 4), "variants_bit_identical": same}
 
 
+def time_tp_mlp_block(torch, L, dist, device, rank, world):
+    """Tensor-parallel SiLU-gated MLP block of a random-init Llama-2-7B layer (hidden 4096, intermediate 11008) on
+    16384 tokens over `world` GPUs, column -> row: every rank holds the gate and up rows of its slice of the hidden
+    channels and the matching K slice of the down projection, so the block needs NO [T, I] all-gather:
+      quantize x -> gate/up GEMM with SiLU*mul in its epilogue (h slice [T, I/G]) -> row-parallel down projection
+      (slice statistics -> tiny all-reduce -> codes from the global statistics -> GEMM partial sums stored to the
+      owners of the row blocks -> owner's reduce + dequant, result to every rank).
+    Time = max over ranks, CUDA events, barrier on both sides; a checksum of the replicated result must agree on all ranks."""
+    from duqlinear4bitcuda_b200.parallel import RowParallelLinear4bit, k_shard_bounds
+    T, H, I = 32 * 512, 4096, 11008
+    kb, ke = k_shard_bounds(I, world, rank)
+    st = L.current_stream
+    x = synth_activations(torch, T, H, seed=3, pinned=False).to(device)
+    w_g, s_g = synth_weights(torch, I, H, seed=11, device=device)       # every rank synthesises the same full tensors, keeps its slice
+    w_u, s_u = synth_weights(torch, I, H, seed=13, device=device)
+    w_gu = torch.cat([w_g[kb:ke], w_u[kb:ke]]).contiguous(); s_gu = torch.cat([s_g[kb:ke], s_u[kb:ke]]).contiguous()
+    del w_g, w_u
+    w_dn, s_dn = synth_weights(torch, H, I, seed=12, device=device)
+    down = RowParallelLinear4bit.from_full("sym", w_dn, s_dn)
+    del w_dn
+    a8 = torch.empty((T, H), dtype=torch.int8, device=device); sa = torch.empty(T, dtype=torch.float16, device=device)
+    h = torch.empty((T, ke - kb), dtype=torch.float16, device=device)
+    e1 = L.make_epilogue("sym", sa, None, s_gu)
+
+    def block():
+        L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), T, H, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
+        L.call("duq4_linear_w4a4_gate_up_silu", L.ptr(a8), 1, L.ptr(w_gu), T, ke - kb, H, ctypes.byref(e1), L.ptr(h), st())
+        return down(h)
+
+    for _ in range(3):
+        y = block()
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        y = block()
+    e1_.record()
+    torch.cuda.synchronize(); dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1_) / reps], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    hsum = y.view(torch.int16).to(torch.int64).sum()
+    lo, hi = hsum.clone(), hsum.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    ops = 2.0 * T * H * 2 * I + 2.0 * T * I * H
+    return {"tokens": T, "hidden": H, "intermediate": I, "gpus": world, "ms_per_block": round(float(ms.item()), 4),
+            "tops": round(ops / (float(ms.item()) * 1e-3) / 1e12, 1), "replicated_result_checksum_equal": int(lo.item()) == int(hi.item()),
+            "pipeline": "quantize, column-parallel gate/up GEMM with SiLU*mul epilogue, row-parallel down projection "
+                        "(partial sums to row-block owners over NVLink, one dequant); no [T, I] gather"}
+
+
 def time_prefill_sweep(torch, L, device, Ms=(512, 2048, 4096, 8192)):
     """Whole layer (fused per-token quantizer + GEMM with the dequant in its epilogue, one C-ABI call:
     duq4_linear_w4a4_from_fp16_prelaid, weights re-laid out to int8 once outside the timed region)
@@ -817,6 +868,10 @@ def run_ours(args):
             line["prefill_sweep"] = time_prefill_sweep(torch, L, device)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()[0]
+    if world > 1 and args.tp_mlp:
+        tp = time_tp_mlp_block(torch, L, dist, device, rank, world)
+        if rank == 0:
+            line["tp_mlp_block"] = tp
     if world > 1:
         dist.barrier()
         for h in (shared_x, shared_out):
@@ -838,6 +893,7 @@ def main():
                          "'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--multicast", action="store_true", help="N>1, --gather fused: one multimem.st per row segment instead of one plain store per peer")
     ap.add_argument("--chunk-rows", type=int, default=0, help="N>1, --gather copy: rows per pipeline chunk (0 = M/16 rounded to 256)")
+    ap.add_argument("--tp-mlp", action="store_true", help="N>1: also time a tensor-parallel (column -> row) MLP block")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2-second back-to-back run")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

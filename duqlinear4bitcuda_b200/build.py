@@ -17,7 +17,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libduq4.so")
-SOURCES = ["quantize.cu", "dequant.cu", "gemv_decode.cu", "gemm_tc.cu", "gemm_tc2.cu", "abi.cu", "host_pipeline.cu", "peer.cu"]
+SOURCES = ["quantize.cu", "dequant.cu", "gemv_decode.cu", "gemm_tc.cu", "gemm_tc2.cu", "abi.cu", "host_pipeline.cu", "peer.cu", "row_parallel.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Wno-deprecated-gpu-targets",
          "-Xcompiler", "-fPIC"]

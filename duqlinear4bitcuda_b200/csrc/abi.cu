@@ -56,6 +56,19 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
         p->peers[i] = (__half *)e->out_peers[i];
     }
     p->mc_out = e->n_out_peers ? (__half *)e->out_multicast : nullptr;
+    if (e->n_acc_owners) {
+        if (e->n_acc_owners > DUQ4_MAX_OUT_PEERS || e->acc_rows_per_owner == 0 || e->acc_slot >= e->n_acc_owners || (N & 3u) != 0)
+            return DUQ4_ERR_SHAPE;
+        if (e->mode != DUQ4_MODE_NONE) return DUQ4_ERR_MODE;   // the dequant runs once, on the summed accumulators
+        p->n_acc_owners = e->n_acc_owners;
+        p->acc_rows_per_owner = e->acc_rows_per_owner;
+        p->acc_slot = e->acc_slot;
+        for (uint32_t i = 0; i < e->n_acc_owners; ++i) {
+            if (!e->acc_owners[i]) return DUQ4_ERR_NULL;
+            if ((reinterpret_cast<uintptr_t>(e->acc_owners[i]) & 15) != 0) return DUQ4_ERR_ALIGN;
+            p->acc_owners[i] = e->acc_owners[i];
+        }
+    }
     p->next_w = (const uint8_t *)e->next_weights;
     p->next_w_bytes = e->next_weights ? e->next_weights_bytes : 0;
     if (e->mode == DUQ4_MODE_NONE) return DUQ4_OK;
@@ -163,9 +176,10 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
     if (rc) return rc;
     if (!A_i8 || !W) return DUQ4_ERR_NULL;
     if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
-    if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
+    if (p.mode == DUQ4_MODE_NONE && !acc_out && !p.n_acc_owners) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0) return DUQ4_ERR_SHAPE;
+    if (p.n_acc_owners && (uint64_t)p.n_acc_owners * p.acc_rows_per_owner < M) return DUQ4_ERR_SHAPE;
     return gemm_tc_launch(2 /* A pre-unpacked int8, W packed int4 */, A_i8, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
 }
 
@@ -178,9 +192,10 @@ int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M,
     if (rc) return rc;
     if (!A_i8 || !W_i8) return DUQ4_ERR_NULL;
     if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
-    if (p.mode == DUQ4_MODE_NONE && !acc_out) return DUQ4_ERR_NULL;
+    if (p.mode == DUQ4_MODE_NONE && !acc_out && !p.n_acc_owners) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
+    if (p.n_acc_owners && (uint64_t)p.n_acc_owners * p.acc_rows_per_owner < M) return DUQ4_ERR_SHAPE;
     if (((reinterpret_cast<uintptr_t>(A_i8) | reinterpret_cast<uintptr_t>(W_i8)) & 15) != 0) return DUQ4_ERR_ALIGN;
     return gemm_tc2_launch_prelaid(A_i8, W_i8, M, N, K, p, out, acc_out, (cudaStream_t)stream, split_scratch, split_scratch_bytes);
 }

@@ -101,6 +101,9 @@ struct EpiParams {
     uint64_t next_w_bytes;
     // NVLS multicast address of the result buffer (see duq4_epilogue.out_multicast), or null
     __half *mc_out;
+    // K-sharded layers: int32 partial accumulators go to the owner of each row block (see duq4_epilogue.acc_owners)
+    uint32_t n_acc_owners, acc_rows_per_owner, acc_slot;
+    int32_t *acc_owners[DUQ4_MAX_OUT_PEERS];
 };
 
 // Output bases of a launch: the peer list if there is one, else the plain `out` pointer.

@@ -158,6 +158,14 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
     const bool asym = mode == DUQ4_MODE_ASYM || mode == DUQ4_MODE_ASYM_DUAL;
     const size_t ooff = ((size_t)b * a.M + m) * pb.ldo + n0;
     int32_t *arow = a.acc_out ? a.acc_out + ((size_t)b * a.M + m) * a.N + n0 : nullptr;
+    if (pb.n_acc_owners && row_ok) {   // K-sharded layer: the partial sums of row m go to the rank that owns row m
+        const uint32_t owner = m / pb.acc_rows_per_owner, r = m - owner * pb.acc_rows_per_owner;
+        int32_t *base = pb.acc_owners[0];
+#pragma unroll
+        for (int o = 1; o < DUQ4_MAX_OUT_PEERS; ++o)
+            if (owner == (uint32_t)o) base = pb.acc_owners[o];
+        arow = base + ((size_t)pb.acc_slot * pb.acc_rows_per_owner + r) * a.N + n0;
+    }
     const OutBases ob = out_bases(pb, a.out);
     uintptr_t obits = 0;
 #pragma unroll
@@ -165,7 +173,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
     const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
     __half *const mc = (STAGED && vec_ok && (reinterpret_cast<uintptr_t>(pb.mc_out) & 15u) == 0) ? pb.mc_out : nullptr;
-    const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);
+    const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);   // owner buffers: alignment checked by the host
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
     for (int ch = 0; ch < nch; ++ch) {
@@ -200,7 +208,35 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         const bool full = n0 + c0 + 16 <= n_end;
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> shift);
-        if (arow && row_ok && col_any) {
+        if (STAGED && pb.n_acc_owners) {
+            // K-sharded layer: partial sums to the owners of the rows. Staged like the fp16 output so that what crosses
+            // NVLink are 128-byte row segments: lane = row writes its 16 ints (64 bytes) of this chunk; after two chunks
+            // (32 columns) the warp reads the block back, four rows of 128 bytes per store instruction.
+            int4 *mine = reinterpret_cast<int4 *>(stg + lane * 144 + (ch & 1) * 64);
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) mine[j >> 2] = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+            if ((ch & 1) == 1 || ch == nch - 1) {
+                __syncwarp();
+                const uint32_t g0 = (uint32_t)(ch >> 1) * 32 + (lane & 7) * 4;   // first column of this lane's 4 ints (tile-relative)
+                const bool second_half = (lane & 7) >= 4;                        // columns of the odd chunk of the pair
+                const bool have = n0 + g0 + 4 <= n_end && !(second_half && (ch & 1) == 0);
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const uint32_t r = it * 4 + (lane >> 3);
+                    const uint32_t mr = m_base + quad * 32 + r;
+                    if (mr >= a.M || !have) continue;
+                    const uint32_t owner = mr / pb.acc_rows_per_owner, ro = mr - owner * pb.acc_rows_per_owner;
+                    int32_t *base = pb.acc_owners[0];
+#pragma unroll
+                    for (int o = 1; o < DUQ4_MAX_OUT_PEERS; ++o)
+                        if (owner == (uint32_t)o) base = pb.acc_owners[o];
+                    *reinterpret_cast<int4 *>(base + ((size_t)pb.acc_slot * pb.acc_rows_per_owner + ro) * a.N + n0 + g0) =
+                        *reinterpret_cast<const int4 *>(stg + r * 144 + (lane & 7) * 16);
+                }
+                __syncwarp();
+            }
+            if (mode == DUQ4_MODE_NONE) continue;
+        } else if (arow && row_ok && col_any) {
             if (full && avec_ok) {
 #pragma unroll
                 for (int j = 0; j < 16; j += 4)

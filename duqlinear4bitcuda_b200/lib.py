@@ -32,6 +32,10 @@ class Epilogue(ctypes.Structure):
         ("next_weights", ctypes.c_void_p),
         ("next_weights_bytes", ctypes.c_uint64),
         ("out_multicast", ctypes.c_void_p),
+        ("n_acc_owners", ctypes.c_uint32),
+        ("acc_rows_per_owner", ctypes.c_uint32),
+        ("acc_slot", ctypes.c_uint32),
+        ("acc_owners", ctypes.c_void_p * 8),
     ]
 
 
@@ -87,6 +91,9 @@ SIGNATURES = {
     "duq4_linear_w4a4_from_fp16_to_host": [_vp, _vp, _i, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _u32, _vp, _sz, _vp],
     "duq4_linear_w4a4_from_fp16_to_peers": [_vp, _vp, _i, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _u32, _u32, _vp, _sz, _vp],
     "duq4_linear_w4a4_from_fp16_static": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp],
+    "duq4_row_stats": [_i, _vp, _u32, _u32, _vp, _vp, _vp],
+    "duq4_quantize_i8_from_stats": [_i, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp],
+    "duq4_reduce_dequant_gather": [_vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
     "duq4_peer_barrier": [ctypes.POINTER(ctypes.c_void_p), _u32, _u32, ctypes.c_uint64, ctypes.c_uint64, _vp],
     "duq4_last_device_status": [_vp, ctypes.POINTER(ctypes.c_int32)],
 }
@@ -128,7 +135,8 @@ def current_stream():
 
 
 def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
-                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None, out_multicast=None):
+                  zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None, out_multicast=None,
+                  acc_owners=None, acc_rows_per_owner=0, acc_slot=0):
     """Fill a duq4_epilogue. `next_weights`: packed weight tensor of the layer that runs next on the
     stream (L2 prefetch hint of the small-M kernels; never read or written by this launch)."""
     e = Epilogue()
@@ -145,6 +153,12 @@ def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_
         e.n_out_peers = len(out_peers)
         for i, a in enumerate(out_peers):
             e.out_peers[i] = int(a)
+    if acc_owners:   # K-sharded layer: raw device addresses (ints) of every owner's int32 slab buffer
+        e.n_acc_owners = len(acc_owners)
+        e.acc_rows_per_owner = int(acc_rows_per_owner)
+        e.acc_slot = int(acc_slot)
+        for i, a in enumerate(acc_owners):
+            e.acc_owners[i] = int(a)
     if out_multicast:   # raw multicast address (int) of the same buffer, at this shard's first column
         e.out_multicast = int(out_multicast)
     if next_weights is not None:

@@ -459,10 +459,84 @@ class RowParallelLinear4bit(torch.nn.Module):
         b, e = k_shard_bounds(k_in, world, rank)
         return cls(mode, k_in, weight[:, b // 2: e // 2].contiguous(), scales, zeros, bias, clip_ratio, group)
 
-    def forward(self, x_slice: torch.Tensor):
+    def forward(self, x_slice: torch.Tensor, fused: bool = True):
+        """fused=True (default with more than one rank): the library's row-parallel pieces -- per-token statistics of
+        the slice (one kernel), their all-reduce over the ranks (tiny: one or two fp16 values per token), the fused
+        quantizer with the statistics given (one kernel, tensor-core-ready int8 codes), the GEMM whose epilogue stores
+        its int32 PARTIAL accumulators straight into the buffer of the rank that owns each block of M/G rows (peer
+        stores over NVLink), and after a rank barrier the owner's reduce + single dequant + bias, which stores the fp16
+        rows into every rank's result buffer. No int32 all-reduce, no separate quantize / dequant / bias launches.
+        fused=False: the same arithmetic composed from the reference-named operators and NCCL (int32 all-reduce)."""
+        if fused and self.world > 1 and x_slice.is_cuda:
+            return self._forward_fused(x_slice)
+        return self._forward_composed(x_slice)
+
+    def _forward_fused(self, x_slice: torch.Tensor):
+        import torch.distributed._symmetric_memory as symm
+        from . import lib as L
+        ks = x_slice.shape[-1]
+        M = 1
+        for d in x_slice.shape[:-1]:
+            M *= int(d)
+        x2d = x_slice.reshape(M, ks).contiguous()   # (an empty K slice cannot be reshaped with -1)
+        if ks != self.k_end - self.k_begin:
+            raise ValueError(f"activation slice has {ks} channels, this rank owns {self.k_end - self.k_begin}")
+        N, G, dev = self.weight.shape[0], self.world, x2d.device
+        if N % 8 != 0:
+            return self._forward_composed(x_slice)   # the owner's pass works on 16-byte row segments
+        rpo = -(-M // G)                              # rows per owner
+        st = self.__dict__.setdefault("_fstate", {}).get(M)
+        if st is None:
+            grp = self.group if self.group is not None else dist.group.WORLD
+            slabs = symm.empty((G, rpo, N), dtype=torch.int32, device=dev)
+            shdl = symm.rendezvous(slabs, grp)
+            st = self._fstate[M] = {
+                "peer": PeerOutput(M, N, dev, self.group, use_multicast=False),
+                "slabs": slabs, "slab_ptrs": [int(p) for p in shdl.buffer_ptrs], "shdl": shdl,
+                "stat_a": torch.empty(M, dtype=torch.float16, device=dev), "stat_b": torch.empty(M, dtype=torch.float16, device=dev),
+                "a8": torch.empty((M, max(ks, 64)), dtype=torch.int8, device=dev),
+                "scale": torch.empty(M, dtype=torch.float16, device=dev), "zeros": torch.empty(M, dtype=torch.float16, device=dev),
+            }
+        peer, mode_id, asym = st["peer"], L.MODES[self.mode], self.mode == "asym"
+        stream = L.current_stream
+        with torch.cuda.device(dev):
+            # 1. statistics of the slice, reduced over the ranks (exact: max / min of fp16 values)
+            if ks:
+                L.call("duq4_row_stats", mode_id, L.ptr(x2d), M, ks, L.ptr(st["stat_a"]), L.ptr(st["stat_b"]), stream())
+            else:   # an empty slice must not move the global statistics
+                st["stat_a"].fill_(float("inf") if asym else 0.0)
+                st["stat_b"].fill_(float("-inf"))
+            dist.all_reduce(st["stat_a"], op=dist.ReduceOp.MIN if asym else dist.ReduceOp.MAX, group=self.group)
+            if asym:
+                dist.all_reduce(st["stat_b"], op=dist.ReduceOp.MAX, group=self.group)
+            # 2. codes of the slice with the global scale (/ zero-point); every rank derives the same per-token terms
+            # (a rank without a K slice still derives the per-token terms: it owns rows of the result)
+            L.call("duq4_quantize_i8_from_stats", mode_id, L.ptr(x2d) if ks else None, M, ks, L.ptr(st["stat_a"]), L.ptr(st["stat_b"]),
+                   float(self.clip_ratio), L.ptr(st["a8"]) if ks else None, L.ptr(st["scale"]), L.ptr(st["zeros"]), stream())
+            # 3. partial accumulators to the owners of the row blocks
+            peer.barrier()   # the owners have consumed the previous forward's slabs
+            if ks:
+                epi = L.make_epilogue("none", acc_owners=st["slab_ptrs"], acc_rows_per_owner=rpo, acc_slot=self.rank)
+                L.call("duq4_linear_w4a4_preunpacked", L.ptr(st["a8"]), L.ptr(self.weight), M, N, ks, ctypes.byref(epi), None, None, stream())
+            peer.barrier()   # every rank's partial sums have landed
+            # 4. this rank's rows: sum of the slabs of the ranks that hold a K slice, one dequant, result to every rank
+            n_slabs = sum(1 for r in range(G) if k_shard_bounds(self.k_in, G, r)[1] > k_shard_bounds(self.k_in, G, r)[0])
+            row0 = min(M, self.rank * rpo)
+            rows = min(M, row0 + rpo) - row0
+            if rows:
+                epi2 = L.make_epilogue(self.mode, st["scale"], st["zeros"] if asym else None, self.scales, self.zeros if asym else None,
+                                       None, None, self.bias, ldo=N, out_peers=peer.ptrs)
+                L.call("duq4_reduce_dequant_gather", L.ptr(st["slabs"]), n_slabs, rpo, row0, rows, N, ctypes.byref(epi2), None, stream())
+            peer.barrier()   # every owner's rows are in every rank's buffer
+        return peer.buf.view(*x_slice.shape[:-1], N)
+
+    def _forward_composed(self, x_slice: torch.Tensor):
         from . import _CUDA
-        x2d = x_slice.reshape(-1, x_slice.shape[-1]).contiguous()
-        M, ks = x2d.shape
+        ks = x_slice.shape[-1]
+        M = 1
+        for d in x_slice.shape[:-1]:
+            M *= int(d)
+        x2d = x_slice.reshape(M, ks).contiguous()   # (an empty K slice cannot be reshaped with -1)
         if ks != self.k_end - self.k_begin:
             raise ValueError(f"activation slice has {ks} channels, this rank owns {self.k_end - self.k_begin}")
         n_out = self.weight.shape[0]

@@ -235,6 +235,16 @@ typedef struct duq4_epilogue {
      * replicates them into every rank's buffer, instead of one store per peer; ragged edges still go
      * through out_peers. NULL = plain peer stores. Tensor-core kernels only. */
     void *out_multicast;
+    /* K-sharded ("row-parallel") layers (optional, no reference counterpart): every rank computes int32 PARTIAL
+     * accumulators over its K slice; with n_acc_owners > 0 the tensor-core kernel stores the partial of row m
+     * into the buffer of the rank that owns row m -- acc_owners[m / acc_rows_per_owner], an int32 array
+     * [n_acc_owners][acc_rows_per_owner][N] (peer-mapped like out_peers, 16-byte aligned, N % 4 == 0), slab
+     * acc_slot = this rank -- instead of `acc_out`, with mode DUQ4_MODE_NONE. The owner then adds the slabs and
+     * dequantizes once (duq4_reduce_dequant_gather). Plain st.global over NVLink. */
+    uint32_t n_acc_owners;
+    uint32_t acc_rows_per_owner;
+    uint32_t acc_slot;
+    int32_t *acc_owners[8];
 } duq4_epilogue;
 
 /* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches
@@ -397,6 +407,30 @@ int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_pr
 int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K,
                                         int act_mode, float clip_ratio, const duq4_epilogue *epi, uint32_t self_index,
                                         uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream);
+
+/* ---- K-sharded (row-parallel) layer: pieces of one fused forward per rank (no reference counterpart) ----
+ * The column-parallel gate/up projection of a tensor-parallel MLP leaves each rank with its own K slice of the
+ * down projection's input. Bit-exactness with the unsharded layer: row statistics are exact reductions, the GEMM is
+ * an exact integer contraction, and ONE dequant runs on the summed accumulators.
+ *   duq4_row_stats             per-token statistics of this rank's slice x [rows, cols]: DUQ4_MODE_SYM -> stat_a =
+ *                              max|x| ; DUQ4_MODE_ASYM -> stat_a = min, stat_b = max (fp16 [rows]; NaNs skipped as
+ *                              in the fused quantizers). The caller reduces them over the ranks (max / min).
+ *   duq4_quantize_i8_from_stats  the fused quantizer with the statistics GIVEN (the reduced ones): scale (and
+ *                              zero-point) by the quantizer modules' formulas, codes of the slice as
+ *                              tensor-core-ready int8 (see duq4_quantize_fused_i8); writes scale_out / zeros_out.
+ *                              cols == 0 (a rank without a K slice) only derives the per-token terms.
+ *   (GEMM)                     duq4_linear_w4a4_preunpacked / _prelaid with epi->mode = DUQ4_MODE_NONE and
+ *                              epi->acc_owners: partial accumulators to the owners of the row blocks.
+ *   duq4_reduce_dequant_gather after a rank barrier: this rank adds the n_slabs partial slabs of the rows it owns
+ *                              ([n_slabs][rows_owned_max][N] int32, its own acc_owners buffer), dequantizes
+ *                              (epi->mode, scale_row / zeros_row indexed by GLOBAL row, per-channel vectors, bias)
+ *                              rows [row0, row0 + rows) and stores the fp16 result into every buffer of
+ *                              epi->out_peers ([M, epi->ldo], n_out_peers >= 1) or into `out`. */
+int duq4_row_stats(int mode, const void *x, uint32_t rows, uint32_t cols, void *stat_a, void *stat_b, void *stream);
+int duq4_quantize_i8_from_stats(int mode, const void *x, uint32_t rows, uint32_t cols, const void *stat_a, const void *stat_b,
+                                float clip_ratio, int8_t *q_i8, void *scale_out, void *zeros_out, void *stream);
+int duq4_reduce_dequant_gather(const int32_t *slabs, uint32_t n_slabs, uint32_t rows_per_slab, uint32_t row0, uint32_t rows,
+                               uint32_t N, const duq4_epilogue *epi, void *out, void *stream);
 
 /* Device-side barrier across the ranks of an N-sharded layer, on `stream` (no reference counterpart; it
  * brackets the fused all-gather: "everybody has consumed the previous result" / "everybody's block has

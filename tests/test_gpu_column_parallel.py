@@ -201,18 +201,21 @@ def _row_worker(rank, world, port, mode, M, N, K, tmp):
         bias = t(np.random.default_rng(15).standard_normal(N).astype(np.float16))
         layer = RowParallelLinear4bit.from_full(mode, qw, sc, zc if mode == "asym" else None, bias)
         b, e = k_shard_bounds(K, world, rank)
-        y = layer(x[:, b:e])
+        y = layer(x[:, b:e]).clone()                 # fused: library pieces, partial sums stored to the owners, one dequant
+        y_again = layer(x[:, b:e]).clone()           # the symmetric buffers are reused
+        y_comp = layer(x[:, b:e], fused=False)       # composed from the reference-named operators + int32 all-reduce
         torch.cuda.synchronize()
         single = ColumnParallelLinear4bit(mode, N, qw, sc, zc if mode == "asym" else None, None, None, bias, unsharded=True)
         y1 = single(x)
         torch.cuda.synchronize()
         ok = torch.equal(y.view(torch.int16), y1.view(torch.int16)) and tuple(y.shape) == (M, N)
+        ok = ok and torch.equal(y_again.view(torch.int16), y1.view(torch.int16)) and torch.equal(y_comp.view(torch.int16), y1.view(torch.int16))
         open(os.path.join(tmp, f"r{rank}"), "w").write(str(int(ok)))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 11008), ("asym", 300, 1040, 1024), ("sym", 512, 2048, 4096)])
+@pytest.mark.parametrize("mode,M,N,K", [("sym", 8, 4096, 11008), ("asym", 301, 1040, 1024), ("sym", 512, 2048, 4096), ("asym", 3, 264, 64)])
 def test_two_gpu_row_parallel_matches_single_gpu(tmp_path, mode, M, N, K):
     """K-sharded layer (int32 partial accumulators all-reduced before the dequant) == the whole layer
     on one GPU, bit for bit."""

@@ -504,6 +504,65 @@ def test_linear_from_fp16_prelaid_equals_packed_weight_entry(env, mode, M, N, K)
                                                      M * K, L.current_stream()) == -4
 
 
+@pytest.mark.parametrize("mode", ["sym", "asym"])
+@pytest.mark.parametrize("M,N,K,G", [(8, 264, 256, 2), (300, 520, 1024, 2), (1000, 1032, 768, 3), (2100, 2000, 512, 4)])
+def test_row_parallel_pieces_on_one_gpu_equal_unsharded_layer(env, mode, M, N, K, G):
+    """The K-sharded layer's pieces, with the G ranks emulated one after the other on one GPU (every 'rank' has its own
+    slab buffer; no kernel waits for another): per-slice statistics -> max / min over the ranks -> codes from the given
+    statistics -> GEMM partial accumulators stored into the owners' slabs -> owner's reduce + dequant + bias. The result
+    must equal the unsharded layer bit for bit (scales / zero-points and codes equal the fused quantizer's)."""
+    torch, L, o = env
+    asym = mode == "asym"
+    x = U.acts(M, K, 7 + M, mean=0.1 if asym else 0.0)
+    if M > 4:
+        x[1] = 0; x[2] = x[2, 0]
+    qw = U.rand_codes(N, K, 8); sc = U.rand_scales(N, 9); zc = U.rand_zeros(N, 10)
+    bias = np.random.default_rng(11).standard_normal(N).astype(np.float16)
+    dx, dqw, dsc, dzc, db = (dev(torch, v) for v in (x, qw, sc, zc, bias))
+    st = L.current_stream()
+    per = -(-(K // 64) // G) * 64
+    bounds = [(min(K, r * per), min(K, (r + 1) * per)) for r in range(G)]
+    # 1. statistics per slice, reduced
+    sa = [torch.zeros(M, dtype=torch.float16, device="cuda") for _ in range(G)]
+    sb = [torch.zeros(M, dtype=torch.float16, device="cuda") for _ in range(G)]
+    xs = [dx[:, b:e].contiguous() for b, e in bounds]
+    for r, (b, e) in enumerate(bounds):
+        if e > b:
+            L.call("duq4_row_stats", L.MODES[mode], L.ptr(xs[r]), M, e - b, L.ptr(sa[r]), L.ptr(sb[r]), st)
+        else:
+            sa[r].fill_(float("inf") if asym else 0.0); sb[r].fill_(float("-inf"))
+    ga = torch.stack(sa).amin(0) if asym else torch.stack(sa).amax(0)
+    gb = torch.stack(sb).amax(0)
+    # 2. + 3. codes with the global statistics, partial accumulators to the owners' slabs
+    rpo = -(-M // G)
+    slabs = [torch.full((G, rpo, N), 12345, dtype=torch.int32, device="cuda") for _ in range(G)]   # owner o's buffer
+    scale = torch.zeros(M, dtype=torch.float16, device="cuda"); zeros = torch.zeros(M, dtype=torch.float16, device="cuda")
+    n_slabs = 0
+    for r, (b, e) in enumerate(bounds):
+        if e == b:
+            continue
+        n_slabs += 1
+        a8 = torch.zeros((M, e - b), dtype=torch.int8, device="cuda")
+        L.call("duq4_quantize_i8_from_stats", L.MODES[mode], L.ptr(xs[r]), M, e - b, L.ptr(ga), L.ptr(gb), 1.0, L.ptr(a8), L.ptr(scale), L.ptr(zeros), st)
+        wk = dqw[:, b // 2: e // 2].contiguous()
+        epi = L.make_epilogue("none", acc_owners=[t.data_ptr() for t in slabs], acc_rows_per_owner=rpo, acc_slot=r)
+        L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(wk), M, N, e - b, ctypes.byref(epi), None, None, st)
+    # 4. every owner: reduce + dequant + bias into the one result
+    out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    for o_ in range(G):
+        row0 = min(M, o_ * rpo); rows = min(M, row0 + rpo) - row0
+        epi2 = L.make_epilogue(mode, scale, zeros if asym else None, dsc, dzc if asym else None, None, None, db, ldo=N)
+        L.call("duq4_reduce_dequant_gather", L.ptr(slabs[o_]), n_slabs, rpo, row0, rows, N, ctypes.byref(epi2), L.ptr(out), st)
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    # the unsharded layer: the fused quantizer's terms and codes (checked against the oracle), the oracle's GEMM + dequant
+    qa, s1, z1, _, _ = U.gpu_quantize(torch, L, mode, x)
+    assert U.f16_equal_nan(scale.cpu().numpy(), s1) and (not asym or U.f16_equal_nan(zeros.cpu().numpy(), z1))
+    _, want = o.linear_w4a4(mode, qa, qw, s1, z1 if asym else None, sc, zc if asym else None, None, None, bias)
+    assert U.f16_equal_nan(out.cpu().numpy(), want)
+    assert L.cdll.duq4_row_stats(L.MODE_SYM_DUAL, L.ptr(xs[0]), M, 64, L.ptr(sa[0]), None, st) == -3   # dual schemes do not commute with a K split
+
+
 @pytest.mark.parametrize("K", [512, 4096])
 def test_decode_static_weights_overlap_keeps_stream_order(env, K):
     """With duq4_set_static_weights(1) the small-M kernels start streaming weights before the
