@@ -20,6 +20,8 @@ int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_
 int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
                             int32_t *acc_out, cudaStream_t st, void *sk_scratch = nullptr, size_t sk_bytes = 0);
 size_t gemm_tc2_split_scratch_bytes();
+int gemm_tc2_launch_gate_up_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t inter, uint32_t K, const EpiParams &p, void *h_out,
+                                    cudaStream_t st);
 int tc_status_read(cudaStream_t st, int32_t *out);
 int gemv_status_read(int32_t *out);
 int peer_status_read(int32_t *out);
@@ -211,6 +213,20 @@ int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W
     if (M == 0 || inter == 0) return DUQ4_OK;
     if (K == 0 || K % 64 != 0 || inter > 0x7FFFFFFFu) return DUQ4_ERR_SHAPE;
     return gemm_tc2_launch_gate_up(a_is_int8 == 0, A, W, M, inter, K, p, h_out, (cudaStream_t)stream);
+}
+
+int duq4_linear_w4a4_gate_up_silu_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t inter, uint32_t K,
+                                          const duq4_epilogue *epi, void *h_out, void *stream) {
+    if (!A_i8 || !W_i8 || !epi) return DUQ4_ERR_NULL;
+    if (epi->mode != DUQ4_MODE_SYM && epi->mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;
+    EpiParams p;
+    int rc = check_epi(epi, inter, true, &p);
+    if (rc) return rc;
+    if (!h_out && !p.n_peers) return DUQ4_ERR_NULL;
+    if (M == 0 || inter == 0) return DUQ4_OK;
+    if (K == 0 || K % 128 != 0 || inter > 0x7FFFFFFFu) return DUQ4_ERR_SHAPE;
+    if (((reinterpret_cast<uintptr_t>(A_i8) | reinterpret_cast<uintptr_t>(W_i8)) & 15) != 0) return DUQ4_ERR_ALIGN;
+    return gemm_tc2_launch_gate_up_prelaid(A_i8, W_i8, M, inter, K, p, h_out, (cudaStream_t)stream);
 }
 
 // Scratch layout of duq4_linear_w4a4_from_fp16: activation codes, then four fp16 vectors [M]

@@ -508,12 +508,13 @@ Tensor weight_prelayout_i8(const Tensor &W) {
 // (new) SiLU-gated gate/up projection in one launch: W packed [2*I, K/2] = gate rows then up rows, `scale_col` /
 // `zeros_col` / `bias` with 2*I entries; returns h fp16 [M, I] equal to F.silu(y[:, :I]) * y[:, I:] for
 // y = linear_w4a4(mode, A, W, ...), without writing y. A: packed int4 uint8 [M, K/2] or the tensor-core-ready int8
-// [M, K] of silu_mul_quantize_fused. mode: "sym" or "asym".
+// [M, K] of silu_mul_quantize_fused. mode: "sym" or "asym". `W_prelaid`: optional int8 [2*I, K] made once from W by
+// weight_prelayout_i8; read instead of W when A is int8 and M > 128 (same bits, less work per tile).
 Tensor linear_w4a4_gate_up_silu(const std::string &mode, const Tensor &A, const Tensor &W, const Tensor &scale_row, const OptTensor &zeros_row,
-                                const OptTensor &scale_col, const OptTensor &zeros_col, const OptTensor &bias) {
+                                const OptTensor &scale_col, const OptTensor &zeros_col, const OptTensor &bias, const OptTensor &W_prelaid) {
     const char *fn = "linear_w4a4_gate_up_silu";
     check_tensors(fn, {{&A, "A"}, {&W, "W"}, {&scale_row, "scale_row"}, {opt(zeros_row), "zeros_row"}, {opt(scale_col), "scale_col"},
-                       {opt(zeros_col), "zeros_col"}, {opt(bias), "bias"}});
+                       {opt(zeros_col), "zeros_col"}, {opt(bias), "bias"}, {opt(W_prelaid), "W_prelaid"}});
     TORCH_CHECK(mode == "sym" || mode == "asym", fn, ": mode must be 'sym' or 'asym'");
     TORCH_CHECK(A.scalar_type() == torch::kInt8 || A.scalar_type() == torch::kUInt8, fn, ": A must be uint8 (packed) or int8 (tensor-core-ready)");
     check_dtype(fn, W, "W", torch::kUInt8);
@@ -527,7 +528,14 @@ Tensor linear_w4a4_gate_up_silu(const std::string &mode, const Tensor &A, const 
     duq4_epilogue e = make_epi(fn, mode, 2 * inter, scale_row, zeros_row, scale_col, zeros_col, std::nullopt, std::nullopt, bias, 0, 0);
     auto h = empty_like_dev(A, {M, inter}, torch::kFloat16);
     Launch l(A);
-    ok(fn, duq4_linear_w4a4_gate_up_silu(A.data_ptr(), a_is_int8 ? 1 : 0, W.data_ptr<uint8_t>(), M, inter, K, &e, h.data_ptr(), l.stream));
+    if (opt(W_prelaid)) {
+        check_dtype(fn, *W_prelaid, "W_prelaid", torch::kInt8);
+        TORCH_CHECK(W_prelaid->dim() == 2 && W_prelaid->size(0) == 2 * inter && W_prelaid->size(1) == K, fn, ": W_prelaid must be int8 [2*I, K]");
+    }
+    if (opt(W_prelaid) && a_is_int8 && M > 128)
+        ok(fn, duq4_linear_w4a4_gate_up_silu_prelaid(A.data_ptr<int8_t>(), W_prelaid->data_ptr<int8_t>(), M, inter, K, &e, h.data_ptr(), l.stream));
+    else
+        ok(fn, duq4_linear_w4a4_gate_up_silu(A.data_ptr(), a_is_int8 ? 1 : 0, W.data_ptr<uint8_t>(), M, inter, K, &e, h.data_ptr(), l.stream));
     return h;
 }
 
@@ -595,7 +603,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("clip_ratio") = 1.0, py::arg("act_mode") = py::none(), py::arg("W_prelaid") = py::none());
     m.def("weight_prelayout_i8", &weight_prelayout_i8, py::arg("W"));
     m.def("linear_w4a4_gate_up_silu", &linear_w4a4_gate_up_silu, py::arg("mode"), py::arg("A"), py::arg("W"), py::arg("scale_row"),
-          py::arg("zeros_row") = py::none(), py::arg("scale_col") = py::none(), py::arg("zeros_col") = py::none(), py::arg("bias") = py::none());
+          py::arg("zeros_row") = py::none(), py::arg("scale_col") = py::none(), py::arg("zeros_col") = py::none(), py::arg("bias") = py::none(),
+          py::arg("W_prelaid") = py::none());
     m.def("linear_w4a4_batched", &linear_w4a4_batched, py::arg("mode"), py::arg("A"), py::arg("W"), py::arg("scale_row"),
           py::arg("zeros_row") = py::none(), py::arg("scale_col_1") = py::none(), py::arg("zeros_col_1") = py::none(),
           py::arg("scale_col_2") = py::none(), py::arg("zeros_col_2") = py::none());

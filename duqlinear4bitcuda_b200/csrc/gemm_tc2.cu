@@ -65,8 +65,8 @@ struct Cfg2 {
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
     static constexpr int NPK = WI8 ? 1 : (GU ? (APK ? 3 : 5) : (APK ? 4 : 5));
-    static constexpr int NUP = WI8 ? 6 : ((APK || GU) ? 4 : 5);
-    static constexpr int kPackedStage = (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB
+    static constexpr int NUP = WI8 ? (GU ? 5 : 6) : ((APK || GU) ? 4 : 5);
+    static constexpr int kPackedStage = WI8 ? 0 : (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB; none without an unpack
     static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
 };
@@ -230,7 +230,7 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
 template <bool APK, bool GU, bool WI8>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
-    static_assert(!WI8 || (!APK && !GU), "pre-laid-out weights go with int8 activations and the plain epilogue");
+    static_assert(!WI8 || !APK, "pre-laid-out weights go with int8 activations");
     using C2 = Cfg2<APK, GU, WI8>;
     constexpr int NPK = C2::NPK, NUP = C2::NUP, kPackedStage = C2::kPackedStage;
     constexpr int EPI = C2::EPI, UW = C2::UWN, kColTerms = C2::kColTerms;
@@ -335,7 +335,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (WI8) {   // this CTA's half of the int8 W block straight into the MMA ring, credited to the leader
                         const uint32_t u = it % NUP, uph = (it / NUP) & 1;
                         if (!(ok = mbar_wait(up_empty(u), uph ^ 1, abortp, &g_tc2_status, 1))) break;
-                        tma_load_3d_pair(up0 + u * kUnpackedStage + BMH * BKE, &tmB, mapa(up_full(u), 0), ks * BKE, tn * bn + rank * bnh, b);
+                        // gate/up mode: the leader's half comes from the gate rows, the partner's from the up rows
+                        const uint32_t wrow8 = a.gate_up ? (rank ? a.gate_up : 0u) + tn * 128u : tn * bn + rank * bnh;
+                        tma_load_3d_pair(up0 + u * kUnpackedStage + BMH * BKE, &tmB, mapa(up_full(u), 0), ks * BKE, wrow8, b);
                         continue;
                     }
                     const uint32_t s = it % NPK, ph = (it / NPK) & 1;
@@ -621,7 +623,7 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     int rc = APK ? tma_map_bytes_3d(A, K / 2, M, batch, BKE / 2, BMH, false, &ma, cache_maps)
                  : tma_map_bytes_3d(A, K, M, batch, BKE, BMH, true, &ma, cache_maps);
     if (rc) return rc;
-    rc = WI8 ? tma_map_bytes_3d(B, K, N, batch, BKE, a.bn / 2, true, &mb, cache_maps)
+    rc = WI8 ? tma_map_bytes_3d(B, K, gate_up ? 2ull * N : N, batch, BKE, a.bn / 2, true, &mb, cache_maps)
              : tma_map_bytes_3d(B, K / 2, gate_up ? 2ull * N : N, batch, BKE / 2, a.bn / 2, false, &mb, cache_maps);
     if (rc) return rc;
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
@@ -692,6 +694,12 @@ int gemm_tc2_launch_gate_up(bool a_packed, const void *A, const void *W, uint32_
                             const EpiParams &p, void *h_out, cudaStream_t st) {
     return a_packed ? launch2<true, true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter)
                     : launch2<false, true>(A, W, M, inter, K, 1, p, h_out, nullptr, st, inter);
+}
+
+// The same on pre-laid-out int8 weights (W_i8 [2*I, K], see duq4_weight_prelayout_i8) and int8 activations.
+int gemm_tc2_launch_gate_up_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t inter, uint32_t K, const EpiParams &p, void *h_out,
+                                    cudaStream_t st) {
+    return launch2<false, true, true>(A, W_i8, M, inter, K, 1, p, h_out, nullptr, st, inter);
 }
 
 int tc2_status_read(int32_t *out) {

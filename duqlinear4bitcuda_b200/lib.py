@@ -85,6 +85,7 @@ SIGNATURES = {
     "duq4_linear_from_fp16_prelaid_workspace_bytes": [_u32, _u32],
     "duq4_linear_w4a4_from_fp16": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _vp, _sz, _vp],
     "duq4_linear_w4a4_gate_up_silu": [_vp, _i, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
+    "duq4_linear_w4a4_gate_up_silu_prelaid": [_vp, _vp, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
     "duq4_linear_host_staging_bytes": [_u32, _u32, _u32, _u32],
     "duq4_linear_w4a4_from_fp16_host": [_vp, _vp, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _vp, _u32, _vp, _sz, _vp],
     "duq4_linear_pipeline_staging_bytes": [_i, _i, _u32, _u32, _u32, _u32],

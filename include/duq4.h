@@ -368,6 +368,11 @@ int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W
                                   uint32_t inter, uint32_t K, const duq4_epilogue *epi,
                                   void *h_out, void *stream);
 
+/* The same on pre-laid-out weights: W_i8 int8 [2*inter, K] = duq4_weight_prelayout_i8 of the fused gate/up weight,
+ * A_i8 the tensor-core-ready activations; K % 128 == 0. Same results. */
+int duq4_linear_w4a4_gate_up_silu_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t inter, uint32_t K,
+                                          const duq4_epilogue *epi, void *h_out, void *stream);
+
 /* The same layer with the activations and the result in HOST memory (what a caller holds when
  * the reference module is fed from the CPU side; ref: src/module/linear.cu:108-153 moves nothing
  * itself, torch's .to(device) / .cpu() around it do). x_host [M, K] fp16 and out_host

@@ -327,3 +327,14 @@ def test_gate_up_silu_epilogue_equals_unfused_composition(mode, M, inter, K, int
     assert torch.equal(h.view(torch.int16), want.contiguous().view(torch.int16))
     with pytest.raises(RuntimeError):
         ops.linear_w4a4_gate_up_silu("sym_dual", A, qw, sa.reshape(-1), None, sc)
+    if int8_acts and K % 128 == 0:   # the same on the pre-laid-out int8 copy of the fused gate/up weight
+        import ctypes
+        w8 = ops.weight_prelayout_i8(qw)
+        h8 = torch.full((M, inter), float("nan"), dtype=torch.float16, device="cuda")
+        epi = L.make_epilogue(mode, sa.reshape(-1), None if za is None else za.reshape(-1), sc, zc if mode == "asym" else None, None, None, bias)
+        L.call("duq4_linear_w4a4_gate_up_silu_prelaid", L.ptr(A), L.ptr(w8), M, inter, K, ctypes.byref(epi), L.ptr(h8), L.current_stream())
+        torch.cuda.synchronize()
+        assert torch.equal(h8.view(torch.int16), want.contiguous().view(torch.int16))
+        hb = ops.linear_w4a4_gate_up_silu(mode, A, qw, sa.reshape(-1), None if za is None else za.reshape(-1), sc,
+                                          zc if mode == "asym" else None, bias, W_prelaid=w8)
+        assert torch.equal(hb.view(torch.int16), want.contiguous().view(torch.int16))
