@@ -28,10 +28,18 @@ using OptTensor = std::optional<Tensor>;
 struct Arg {
     const Tensor *t;
     const char *name;
+    torch::ScalarType dtype = torch::ScalarType::Undefined;   // required element type, when the operator fixes one
 };
 
-// What the reference's checkAllContiguous + checkDeviceType + checkAllSameGPU do, on defined tensors only.
+// What the reference's checkAllContiguous + checkDeviceType + checkAllSameGPU do, on defined tensors only, after the
+// element types the operator fixes (a kernel reads every vector as the type it was written for: an fp32 scale
+// vector handed over as fp16 would give wrong numbers, not an error). Types are checked first, so a wrong type is
+// reported on any machine.
 void check_tensors(const char *fn, std::initializer_list<Arg> args) {
+    for (const Arg &a : args)
+        if (a.t && a.t->defined() && a.dtype != torch::ScalarType::Undefined)
+            TORCH_CHECK(a.t->scalar_type() == a.dtype, fn, ": expected ", a.name, " to have dtype ", c10::toString(a.dtype), ", got ",
+                        c10::toString(a.t->scalar_type()));
     const Tensor *first = nullptr;
     for (const Arg &a : args) {
         if (!a.t || !a.t->defined()) continue;
@@ -198,7 +206,7 @@ Tensor row_vec(const Tensor &x, uint32_t rows) { return empty_like_dev(x, {rows}
 // (new) x fp16 [rows, K] -> (codes uint8 [rows, K/2], scales fp16 [rows]): one kernel for SymQuantizer's
 // abs/max/div/mul torch ops plus sym_quant (qlinear4bit/nn/quantizer.py:10-16).
 std::tuple<Tensor, Tensor> quantize_sym_fused(const Tensor &x, double clip_ratio) {
-    check_tensors("quantize_sym_fused", {{&x, "x"}});
+    check_tensors("quantize_sym_fused", {{&x, "x", torch::kFloat16}});
     auto o = quant_out("quantize_sym_fused", x);
     auto s = row_vec(x, o.rows);
     Launch l(x);
@@ -207,7 +215,7 @@ std::tuple<Tensor, Tensor> quantize_sym_fused(const Tensor &x, double clip_ratio
 }
 // (new) -> (codes, scales, zeros); AsymQuantizer (qlinear4bit/nn/quantizer.py:24-35) in one kernel.
 std::tuple<Tensor, Tensor, Tensor> quantize_asym_fused(const Tensor &x) {
-    check_tensors("quantize_asym_fused", {{&x, "x"}});
+    check_tensors("quantize_asym_fused", {{&x, "x", torch::kFloat16}});
     auto o = quant_out("quantize_asym_fused", x);
     auto s = row_vec(x, o.rows), z = row_vec(x, o.rows);
     Launch l(x);
@@ -216,7 +224,7 @@ std::tuple<Tensor, Tensor, Tensor> quantize_asym_fused(const Tensor &x) {
 }
 // (new) dual-uniform: one scale for columns < get_dual_quant_col_k(), one for the rest.
 std::tuple<Tensor, Tensor, Tensor> quantize_sym_dual_fused(const Tensor &x, double clip_ratio) {
-    check_tensors("quantize_sym_dual_fused", {{&x, "x"}});
+    check_tensors("quantize_sym_dual_fused", {{&x, "x", torch::kFloat16}});
     auto o = quant_out("quantize_sym_dual_fused", x);
     auto s1 = row_vec(x, o.rows), s2 = row_vec(x, o.rows);
     Launch l(x);
@@ -226,7 +234,7 @@ std::tuple<Tensor, Tensor, Tensor> quantize_sym_dual_fused(const Tensor &x, doub
 }
 // (new) -> (codes, scale_1, zeros_1, scale_2, zeros_2)
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> quantize_asym_dual_fused(const Tensor &x) {
-    check_tensors("quantize_asym_dual_fused", {{&x, "x"}});
+    check_tensors("quantize_asym_dual_fused", {{&x, "x", torch::kFloat16}});
     auto o = quant_out("quantize_asym_dual_fused", x);
     auto s1 = row_vec(x, o.rows), z1 = row_vec(x, o.rows), s2 = row_vec(x, o.rows), z2 = row_vec(x, o.rows);
     Launch l(x);
@@ -239,7 +247,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> quantize_asym_dual_fused(cons
 // without storing h: (codes, scales) for "sym", (codes, scales, zeros) for "asym". Codes are packed uint8
 // [rows, I/2], or int8 [rows, I] in the GEMM's tensor-core-ready layout when requested.
 py::object silu_mul_quantize_fused(const Tensor &gate_up, const std::string &mode, double clip_ratio, bool tensor_core_ready) {
-    check_tensors("silu_mul_quantize_fused", {{&gate_up, "gate_up"}});
+    check_tensors("silu_mul_quantize_fused", {{&gate_up, "gate_up", torch::kFloat16}});
     TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0 && gate_up.scalar_type() == torch::kFloat16,
                 "silu_mul_quantize_fused: expected fp16 [rows, 2*I]");
     TORCH_CHECK(mode == "sym" || mode == "asym", "silu_mul_quantize_fused: mode must be 'sym' or 'asym'");
@@ -403,8 +411,10 @@ py::object linear_w4a4(const std::string &mode, const Tensor &A, const Tensor &W
                        const OptTensor &zeros_col_2, const OptTensor &bias, int64_t col_offset, const OptTensor &out_, bool return_acc,
                        const OptTensor &next_weights) {
     const char *fn = "linear_w4a4";
-    check_tensors(fn, {{&A, "A"}, {&W, "W"}, {&scale_row, "scale_row"}, {opt(zeros_row), "zeros_row"}, {opt(scale_col_1), "scale_col_1"},
-                       {opt(zeros_col_1), "zeros_col_1"}, {opt(scale_col_2), "scale_col_2"}, {opt(zeros_col_2), "zeros_col_2"}, {opt(bias), "bias"}});
+    constexpr auto F16 = torch::kFloat16;
+    check_tensors(fn, {{&A, "A", torch::kUInt8}, {&W, "W", torch::kUInt8}, {&scale_row, "scale_row", F16}, {opt(zeros_row), "zeros_row", F16},
+                       {opt(scale_col_1), "scale_col_1", F16}, {opt(zeros_col_1), "zeros_col_1", F16}, {opt(scale_col_2), "scale_col_2", F16},
+                       {opt(zeros_col_2), "zeros_col_2", F16}, {opt(bias), "bias", F16}});
     check_dtype(fn, A, "A", torch::kUInt8);
     check_dtype(fn, W, "W", torch::kUInt8);
     TORCH_CHECK(A.dim() == 2 && W.dim() == 2 && W.size(1) == A.size(1), fn, ": A and W disagree on K");
@@ -466,8 +476,10 @@ Tensor linear_w4a4_from_fp16(const std::string &mode, const Tensor &x, const Ten
                              const OptTensor &scale_col_2, const OptTensor &zeros_col_2, const OptTensor &bias, double clip_ratio,
                              const std::optional<std::string> &act_mode_, const OptTensor &W_prelaid) {
     const char *fn = "linear_w4a4_from_fp16";
-    check_tensors(fn, {{&x, "x"}, {&W, "W"}, {&scale_col_1, "scale_col_1"}, {opt(zeros_col_1), "zeros_col_1"}, {opt(scale_col_2), "scale_col_2"},
-                       {opt(zeros_col_2), "zeros_col_2"}, {opt(bias), "bias"}, {opt(W_prelaid), "W_prelaid"}});
+    constexpr auto F16 = torch::kFloat16;
+    check_tensors(fn, {{&x, "x", F16}, {&W, "W", torch::kUInt8}, {&scale_col_1, "scale_col_1", F16}, {opt(zeros_col_1), "zeros_col_1", F16},
+                       {opt(scale_col_2), "scale_col_2", F16}, {opt(zeros_col_2), "zeros_col_2", F16}, {opt(bias), "bias", F16},
+                       {opt(W_prelaid), "W_prelaid", torch::kInt8}});
     TORCH_CHECK(x.scalar_type() == torch::kFloat16 && x.dim() == 2, fn, ": x must be fp16 [M, K]");
     check_dtype(fn, W, "W", torch::kUInt8);
     const int64_t M = x.size(0), K = x.size(1), N = W.size(0);
@@ -513,8 +525,10 @@ Tensor weight_prelayout_i8(const Tensor &W) {
 Tensor linear_w4a4_gate_up_silu(const std::string &mode, const Tensor &A, const Tensor &W, const Tensor &scale_row, const OptTensor &zeros_row,
                                 const OptTensor &scale_col, const OptTensor &zeros_col, const OptTensor &bias, const OptTensor &W_prelaid) {
     const char *fn = "linear_w4a4_gate_up_silu";
-    check_tensors(fn, {{&A, "A"}, {&W, "W"}, {&scale_row, "scale_row"}, {opt(zeros_row), "zeros_row"}, {opt(scale_col), "scale_col"},
-                       {opt(zeros_col), "zeros_col"}, {opt(bias), "bias"}, {opt(W_prelaid), "W_prelaid"}});
+    constexpr auto F16 = torch::kFloat16;
+    check_tensors(fn, {{&A, "A"}, {&W, "W", torch::kUInt8}, {&scale_row, "scale_row", F16}, {opt(zeros_row), "zeros_row", F16},
+                       {opt(scale_col), "scale_col", F16}, {opt(zeros_col), "zeros_col", F16}, {opt(bias), "bias", F16},
+                       {opt(W_prelaid), "W_prelaid", torch::kInt8}});
     TORCH_CHECK(mode == "sym" || mode == "asym", fn, ": mode must be 'sym' or 'asym'");
     TORCH_CHECK(A.scalar_type() == torch::kInt8 || A.scalar_type() == torch::kUInt8, fn, ": A must be uint8 (packed) or int8 (tensor-core-ready)");
     check_dtype(fn, W, "W", torch::kUInt8);
@@ -544,8 +558,10 @@ Tensor linear_w4a4_gate_up_silu(const std::string &mode, const Tensor &A, const 
 Tensor linear_w4a4_batched(const std::string &mode, const Tensor &A, const Tensor &W, const Tensor &scale_row, const OptTensor &zeros_row,
                            const OptTensor &scale_col_1, const OptTensor &zeros_col_1, const OptTensor &scale_col_2, const OptTensor &zeros_col_2) {
     const char *fn = "linear_w4a4_batched";
-    check_tensors(fn, {{&A, "A"}, {&W, "W"}, {&scale_row, "scale_row"}, {opt(zeros_row), "zeros_row"}, {opt(scale_col_1), "scale_col_1"},
-                       {opt(zeros_col_1), "zeros_col_1"}, {opt(scale_col_2), "scale_col_2"}, {opt(zeros_col_2), "zeros_col_2"}});
+    constexpr auto F16 = torch::kFloat16;
+    check_tensors(fn, {{&A, "A", torch::kUInt8}, {&W, "W", torch::kUInt8}, {&scale_row, "scale_row", F16}, {opt(zeros_row), "zeros_row", F16},
+                       {opt(scale_col_1), "scale_col_1", F16}, {opt(zeros_col_1), "zeros_col_1", F16}, {opt(scale_col_2), "scale_col_2", F16},
+                       {opt(zeros_col_2), "zeros_col_2", F16}});
     check_dtype(fn, A, "A", torch::kUInt8);
     check_dtype(fn, W, "W", torch::kUInt8);
     TORCH_CHECK(A.dim() == 3 && W.dim() == 3 && W.size(0) == A.size(0) && W.size(2) == A.size(2), fn, ": expected A [b,M,K/2] and W [b,N,K/2]");
