@@ -864,11 +864,12 @@ def run_ours(args):
             "roofline": {"kernel": "gemm_tc2_kernel<WI8> (CTA pairs, 256x256x128 tiles, tcgen05.mma.cta_group::2.kind::i8; A int8 from the fused quantizer, W int8 pre-laid-out, both straight from TMA into the MMA ring)", "bound": "tensor",
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
                          "frac": round(gemm_tops / int8_peak, 4),
-                         # dram read+write bytes per launch: the ncu capture of the reduced case
-                         # (profiles/gemm_tc2_kernel_pair_M2048_K8192_N8192.md: 57.0 MB for 2.75e11 ops) scaled by ops
-                         "traffic": round(100.1e6 * (2.0 * M * Ns * K) / 2.749e11),
-                         "traffic_note": "ncu dram__bytes_read+write of the M=2048,N=8192 capture (84.4 MB read + 15.7 MB written; part of the output "
-                                         "was still in L2 when the capture ended) scaled by ops; algorithmic bytes "
+                         # dram read+write bytes per launch: ncu capture of this kernel at the bench's own size
+                         # (profiles/bench_launch_list_M4096_K8192_N28672.md: 349.2 MB read + 218.7 MB written), scaled
+                         # by this rank's share of the columns when the layer is sharded
+                         "traffic": round(567.9e6 * Ns / N),
+                         "traffic_note": "ncu dram__bytes_read+write of one full-size launch (M=4096, K=8192, N=28672: 349.2 MB read + 218.7 MB "
+                                         "written; the tail of the result was still in L2 when the launch ended); algorithmic bytes "
                                          f"{M * K + Ns * K + 2 * M * Ns} (int8 activations + int8 weights + fp16 out)",
                          "avg_launch_ms": round(gemm_avg_ms, 4),
                          "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({peaks['source']}); no int8 entry there",
