@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "duq_common.cuh"
+#include "trace_range.h"
 
 namespace duq4 {
 int gemv_w4a4_launch(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch,
@@ -128,6 +129,7 @@ int duq4_set_static_weights(int on) {
 }
 
 int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
+    DUQ4_TRACE();
     EpiParams p{};
     p.mode = DUQ4_MODE_NONE;
     p.ldo = N;
@@ -135,6 +137,7 @@ int duq4_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N,
 }
 
 int duq4_matmul_8bit(const int8_t *A, const int8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C, void *stream) {
+    DUQ4_TRACE();
     if (!A || !B || !C) return DUQ4_ERR_NULL;
     if (M == 0 || N == 0) return DUQ4_OK;
     if (K == 0 || K % 16 != 0) return DUQ4_ERR_SHAPE;
@@ -146,6 +149,7 @@ int duq4_matmul_8bit(const int8_t *A, const int8_t *B, uint32_t M, uint32_t N, u
 
 int duq4_batch_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint32_t N, uint32_t K, int32_t *C,
                            uint32_t batch_count, void *stream) {
+    DUQ4_TRACE();
     EpiParams p{};
     p.mode = DUQ4_MODE_NONE;
     p.ldo = N;
@@ -154,6 +158,7 @@ int duq4_batch_matmul_4bit(const uint8_t *A, const uint8_t *B, uint32_t M, uint3
 
 int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, const duq4_epilogue *epi,
                      void *out, int32_t *acc_out, void *stream) {
+    DUQ4_TRACE();
     EpiParams p;
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
@@ -162,6 +167,7 @@ int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
 
 int duq4_linear_w4a4_batched(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, uint32_t batch_count,
                              const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream) {
+    DUQ4_TRACE();
     EpiParams p;
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
@@ -173,6 +179,7 @@ int duq4_linear_w4a4_batched(const uint8_t *A, const uint8_t *W, uint32_t M, uin
 
 int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K,
                                  const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream) {
+    DUQ4_TRACE();
     EpiParams p;
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
@@ -189,6 +196,7 @@ size_t duq4_gemm_split_scratch_bytes(void) { return gemm_tc2_split_scratch_bytes
 
 int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, const duq4_epilogue *epi,
                              void *out, int32_t *acc_out, void *split_scratch, size_t split_scratch_bytes, void *stream) {
+    DUQ4_TRACE();
     EpiParams p;
     int rc = check_epi(epi, N, true, &p);
     if (rc) return rc;
@@ -204,6 +212,7 @@ int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M,
 
 int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W, uint32_t M, uint32_t inter, uint32_t K,
                                   const duq4_epilogue *epi, void *h_out, void *stream) {
+    DUQ4_TRACE();
     if (!A || !W || !epi) return DUQ4_ERR_NULL;
     if (epi->mode != DUQ4_MODE_SYM && epi->mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;   // the dual selectors go by output column
     EpiParams p;
@@ -217,6 +226,7 @@ int duq4_linear_w4a4_gate_up_silu(const void *A, int a_is_int8, const uint8_t *W
 
 int duq4_linear_w4a4_gate_up_silu_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M, uint32_t inter, uint32_t K,
                                           const duq4_epilogue *epi, void *h_out, void *stream) {
+    DUQ4_TRACE();
     if (!A_i8 || !W_i8 || !epi) return DUQ4_ERR_NULL;
     if (epi->mode != DUQ4_MODE_SYM && epi->mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;
     EpiParams p;
@@ -245,6 +255,7 @@ size_t duq4_linear_from_fp16_workspace_bytes(uint32_t M, uint32_t K) {
 int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
                                size_t workspace_bytes, void *stream) {
+    DUQ4_TRACE();
     if (!x || !W || !epi || (!out && !epi->n_out_peers)) return DUQ4_ERR_NULL;
     if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
     if (M == 0 || N == 0) return DUQ4_OK;
@@ -281,6 +292,7 @@ size_t duq4_linear_from_fp16_prelaid_workspace_bytes(uint32_t M, uint32_t K);
 int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                        float clip_ratio, const duq4_epilogue *epi, void *out, void *workspace,
                                        size_t workspace_bytes, void *stream) {
+    DUQ4_TRACE();
     if (!x || !W_i8 || !epi || (!out && !epi->n_out_peers)) return DUQ4_ERR_NULL;
     if (act_mode < DUQ4_MODE_SYM || act_mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
     if (M == 0 || N == 0) return DUQ4_OK;

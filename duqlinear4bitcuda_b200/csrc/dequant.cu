@@ -5,6 +5,7 @@
 // src/kernels/quant.cu:64-97 (sym), :150-188 (asym), :191-239 (batched asym), :282-323
 // (fp32 "hprec"); src/kernels/quant2.cu:63-98 (sym dual), :159-208 (asym dual).
 #include "duq_common.cuh"
+#include "trace_range.h"
 
 namespace duq4 {
 
@@ -120,28 +121,33 @@ extern "C" {
 
 int duq4_sym_dequant(const int32_t *q, const void *scale_row, const void *scale_col, uint32_t rows, uint32_t cols, void *x,
                      void *stream) {
+    DUQ4_TRACE();
     return dequant_launch(q, make(DUQ4_MODE_SYM, scale_row, nullptr, scale_col, nullptr, nullptr, nullptr), 1, rows, cols, x,
                           (cudaStream_t)stream);
 }
 int duq4_sym_dual_dequant(const int32_t *q, const void *scale_row, const void *scale_col_1, const void *scale_col_2,
                           uint32_t rows, uint32_t cols, void *x, void *stream) {
+    DUQ4_TRACE();
     return dequant_launch(q, make(DUQ4_MODE_SYM_DUAL, scale_row, nullptr, scale_col_1, nullptr, scale_col_2, nullptr), 1, rows,
                           cols, x, (cudaStream_t)stream);
 }
 int duq4_asym_dequant(const int32_t *q, const void *scale_row, const void *zeros_row, const void *scale_col,
                       const void *zeros_col, uint32_t rows, uint32_t cols, void *x, void *stream) {
+    DUQ4_TRACE();
     return dequant_launch(q, make(DUQ4_MODE_ASYM, scale_row, zeros_row, scale_col, zeros_col, nullptr, nullptr), 1, rows, cols,
                           x, (cudaStream_t)stream);
 }
 int duq4_asym_dual_dequant(const int32_t *q, const void *scale_row, const void *zeros_row, const void *scale_col_1,
                            const void *zeros_col_1, const void *scale_col_2, const void *zeros_col_2, uint32_t rows,
                            uint32_t cols, void *x, void *stream) {
+    DUQ4_TRACE();
     return dequant_launch(q, make(DUQ4_MODE_ASYM_DUAL, scale_row, zeros_row, scale_col_1, zeros_col_1, scale_col_2, zeros_col_2),
                           1, rows, cols, x, (cudaStream_t)stream);
 }
 int duq4_asym_batch_dequant(const int32_t *q, const void *scale_row, const void *zeros_row, const void *scale_col,
                             const void *zeros_col, uint32_t batches, uint32_t rows, uint32_t cols, void *x,
                             void *stream) {
+    DUQ4_TRACE();
     EpiParams p = make(DUQ4_MODE_ASYM, scale_row, zeros_row, scale_col, zeros_col, nullptr, nullptr);
     p.row_vec_stride = rows;
     p.col_vec_stride = cols;
@@ -149,6 +155,7 @@ int duq4_asym_batch_dequant(const int32_t *q, const void *scale_row, const void 
 }
 int duq4_asym_dequant_hprec(const int32_t *q, const float *scale_row, const float *zeros_row, const float *scale_col,
                             const float *zeros_col, uint32_t rows, uint32_t cols, float *x, void *stream) {
+    DUQ4_TRACE();
     if (!q || !scale_row || !zeros_row || !scale_col || !zeros_col || !x) return DUQ4_ERR_NULL;
     if (rows == 0 || cols == 0) return DUQ4_OK;
     dequant_hprec_kernel<<<grid_for((size_t)rows * cols), 256, 0, (cudaStream_t)stream>>>(q, scale_row, zeros_row, scale_col,

@@ -26,6 +26,7 @@
 #include <mutex>
 
 #include "../../include/duq4.h"
+#include "trace_range.h"
 
 namespace {
 
@@ -229,6 +230,7 @@ size_t duq4_linear_host_staging_bytes(uint32_t M, uint32_t N, uint32_t K, uint32
 int duq4_linear_w4a4_from_fp16_host(const void *x_host, const uint8_t *W, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                     float clip_ratio, const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows, void *staging,
                                     size_t staging_bytes, void *stream) {
+    DUQ4_TRACE();
     if (!out_host) return DUQ4_ERR_NULL;
     if (epi && epi->n_out_peers != 0) return DUQ4_ERR_MODE;   // the result goes to host memory, not to peers
     Sink sink;
@@ -244,6 +246,7 @@ size_t duq4_linear_pipeline_staging_bytes(int to_host, int w_is_prelaid, uint32_
 int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                        float clip_ratio, const duq4_epilogue *epi, void *out_host, uint32_t chunk_rows, void *staging,
                                        size_t staging_bytes, void *stream) {
+    DUQ4_TRACE();
     if (!out_host) return DUQ4_ERR_NULL;
     if (epi && epi->n_out_peers != 0) return DUQ4_ERR_MODE;
     Sink sink;
@@ -254,6 +257,7 @@ int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_pr
 int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
                                         float clip_ratio, const duq4_epilogue *epi, uint32_t self_index, uint32_t chunk_rows, void *staging,
                                         size_t staging_bytes, void *stream) {
+    DUQ4_TRACE();
     if (!epi) return DUQ4_ERR_NULL;
     if (epi->n_out_peers == 0 || epi->n_out_peers > DUQ4_MAX_OUT_PEERS) return DUQ4_ERR_SHAPE;
     for (uint32_t i = 0; i < epi->n_out_peers; ++i)

@@ -12,6 +12,7 @@
 // fused kernels a CTA owns one token and keeps it in registers between the reduction and
 // the coding pass, so x is read from HBM exactly once.
 #include "duq_common.cuh"
+#include "trace_range.h"
 #include "quant_device.cuh"
 
 namespace duq4 {
@@ -363,23 +364,28 @@ extern "C" {
 
 int duq4_sym_quant(const void *x, const void *scale, uint32_t rows, uint32_t colsSrc, uint32_t colsDst, uint8_t *q,
                    void *stream) {
+    DUQ4_TRACE();
     return launch_given<QSYM>(x, scale, nullptr, nullptr, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
 }
 int duq4_sym_dual_quant(const void *x, const void *scale_1, const void *scale_2, uint32_t rows, uint32_t colsSrc,
                         uint32_t colsDst, uint8_t *q, void *stream) {
+    DUQ4_TRACE();
     return launch_given<QSYM_DUAL>(x, scale_1, nullptr, scale_2, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
 }
 int duq4_asym_quant(const void *x, const void *scale, const void *zeros, uint32_t rows, uint32_t colsSrc,
                     uint32_t colsDst, uint8_t *q, void *stream) {
+    DUQ4_TRACE();
     return launch_given<QASYM>(x, scale, zeros, nullptr, nullptr, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
 }
 int duq4_asym_dual_quant(const void *x, const void *scale_1, const void *zeros_1, const void *scale_2,
                          const void *zeros_2, uint32_t rows, uint32_t colsSrc, uint32_t colsDst, uint8_t *q,
                          void *stream) {
+    DUQ4_TRACE();
     return launch_given<QASYM_DUAL>(x, scale_1, zeros_1, scale_2, zeros_2, rows, colsSrc, colsDst, q, (cudaStream_t)stream);
 }
 int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros, uint32_t rows, uint32_t cols,
                          int8_t *q, void *stream) {
+    DUQ4_TRACE();
     if (!x || !scale || !zeros || !q) return DUQ4_ERR_NULL;
     if (rows == 0 || cols == 0) return DUQ4_OK;
     asym_quant8_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, zeros, rows, cols, q);
@@ -387,6 +393,7 @@ int duq4_asym_quant_8bit(const float *x, const float *scale, const float *zeros,
 }
 
 int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W_i8, void *stream) {
+    DUQ4_TRACE();
     if (!W || !W_i8) return DUQ4_ERR_NULL;
     if (N == 0) return DUQ4_OK;
     if (K == 0 || K % 128 != 0) return DUQ4_ERR_SHAPE;
@@ -397,6 +404,7 @@ int duq4_weight_prelayout_i8(const uint8_t *W, uint32_t N, uint32_t K, int8_t *W
 
 int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols, float clip_ratio, int8_t *q_i8,
                            void *scale_1_out, void *zeros_1_out, void *scale_2_out, void *zeros_2_out, void *stream) {
+    DUQ4_TRACE();
     return quantize_fused_dispatch(mode, x, rows, cols, clip_ratio, (uint8_t *)q_i8, scale_1_out, zeros_1_out, scale_2_out,
                                    zeros_2_out, (cudaStream_t)stream, true);
 }
@@ -404,6 +412,7 @@ int duq4_quantize_fused_i8(int mode, const void *x, uint32_t rows, uint32_t cols
 int duq4_silu_mul_quantize_fused(int mode, const void *gate_up, uint32_t rows, uint32_t inter, uint32_t ld,
                                  uint32_t up_offset, float clip_ratio, void *q, int q_is_int8, void *scale_out,
                                  void *zeros_out, void *stream) {
+    DUQ4_TRACE();
     cudaStream_t st = (cudaStream_t)stream;
     if (mode == QSYM)
         return launch_silu<QSYM>(gate_up, rows, inter, ld, up_offset, clip_ratio, (uint8_t *)q, scale_out, nullptr, st, q_is_int8 != 0);
@@ -414,19 +423,23 @@ int duq4_silu_mul_quantize_fused(int mode, const void *gate_up, uint32_t rows, u
 
 int duq4_quantize_sym_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q, void *scale_out,
                             void *stream) {
+    DUQ4_TRACE();
     return launch_fused<QSYM>(x, rows, cols, clip_ratio, q, scale_out, nullptr, nullptr, nullptr, (cudaStream_t)stream);
 }
 int duq4_quantize_asym_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q, void *scale_out, void *zeros_out,
                              void *stream) {
+    DUQ4_TRACE();
     return launch_fused<QASYM>(x, rows, cols, 1.0f, q, scale_out, zeros_out, nullptr, nullptr, (cudaStream_t)stream);
 }
 int duq4_quantize_sym_dual_fused(const void *x, uint32_t rows, uint32_t cols, float clip_ratio, uint8_t *q,
                                  void *scale_1_out, void *scale_2_out, void *stream) {
+    DUQ4_TRACE();
     return launch_fused<QSYM_DUAL>(x, rows, cols, clip_ratio, q, scale_1_out, nullptr, scale_2_out, nullptr,
                                    (cudaStream_t)stream);
 }
 int duq4_quantize_asym_dual_fused(const void *x, uint32_t rows, uint32_t cols, uint8_t *q, void *scale_1_out,
                                   void *zeros_1_out, void *scale_2_out, void *zeros_2_out, void *stream) {
+    DUQ4_TRACE();
     return launch_fused<QASYM_DUAL>(x, rows, cols, 1.0f, q, scale_1_out, zeros_1_out, scale_2_out, zeros_2_out,
                                     (cudaStream_t)stream);
 }

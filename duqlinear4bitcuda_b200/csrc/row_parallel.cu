@@ -4,6 +4,7 @@
 // 10-16, :24-35), quantize kernels (src/kernels/quant.cu:12-45, :100-132) and dequant kernels (:64-81, :150-169), so
 // that the sharded layer equals the unsharded one bit for bit.
 #include "duq_common.cuh"
+#include "trace_range.h"
 #include "quant_device.cuh"
 
 namespace duq4 {
@@ -138,6 +139,7 @@ using namespace duq4;
 extern "C" {
 
 int duq4_row_stats(int mode, const void *x, uint32_t rows, uint32_t cols, void *stat_a, void *stat_b, void *stream) {
+    DUQ4_TRACE();
     if (!x || !stat_a || (mode == DUQ4_MODE_ASYM && !stat_b)) return DUQ4_ERR_NULL;
     if (mode != DUQ4_MODE_SYM && mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;
     if (rows == 0) return DUQ4_OK;
@@ -153,6 +155,7 @@ int duq4_row_stats(int mode, const void *x, uint32_t rows, uint32_t cols, void *
 
 int duq4_quantize_i8_from_stats(int mode, const void *x, uint32_t rows, uint32_t cols, const void *stat_a, const void *stat_b,
                                 float clip_ratio, int8_t *q_i8, void *scale_out, void *zeros_out, void *stream) {
+    DUQ4_TRACE();
     // cols == 0 (a rank without a K slice): only the per-token terms are derived; x and q_i8 may then be NULL
     if ((cols && (!x || !q_i8)) || !stat_a || !scale_out || (mode == DUQ4_MODE_ASYM && (!stat_b || !zeros_out))) return DUQ4_ERR_NULL;
     if (mode != DUQ4_MODE_SYM && mode != DUQ4_MODE_ASYM) return DUQ4_ERR_MODE;
@@ -173,6 +176,7 @@ int duq4_quantize_i8_from_stats(int mode, const void *x, uint32_t rows, uint32_t
 
 int duq4_reduce_dequant_gather(const int32_t *slabs, uint32_t n_slabs, uint32_t rows_per_slab, uint32_t row0, uint32_t rows, uint32_t N,
                                const duq4_epilogue *epi, void *out, void *stream) {
+    DUQ4_TRACE();
     if (!slabs || !epi) return DUQ4_ERR_NULL;
     if (epi->mode < DUQ4_MODE_SYM || epi->mode > DUQ4_MODE_ASYM_DUAL) return DUQ4_ERR_MODE;
     if (rows == 0 || N == 0) return DUQ4_OK;

@@ -21,6 +21,9 @@
  *     duq4_set_static_weights flag, the scratch array of the _static entry point (shared by all
  *     its calls on a GPU -- see there), and two helper streams per device that the _host entry
  *     point creates on first use.
+ *   - tracing: every entry point that can launch work (all but the _static one and the metadata
+ *     getters) opens an NVTX range named after itself in the NVTX domain "duq4" for the duration of
+ *     the host call; a timeline tool attached through NVTX sees one range per call.
  */
 #ifndef DUQ4_H_
 #define DUQ4_H_
