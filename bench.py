@@ -709,7 +709,7 @@ def run_ours(args):
     # on one GPU (output pitch N, pointer at the shard's first column), no device-side gather, no collective.
     shared_x = shared_out = None
     if world == 1:
-        e2e_x, e2e_out, e2e_out_ptr = x_host, out_host, out_host.data_ptr()
+        e2e_x, e2e_out = x_host, out_host
     else:
         from duqlinear4bitcuda_b200.parallel import SharedHostTensor
         tag = os.environ.get("MASTER_PORT", "0")
@@ -723,30 +723,13 @@ def run_ours(args):
             shared_x = SharedHostTensor(f"duq4_bench_{tag}_x", (M, K), torch.float16, create=False)
             shared_out = SharedHostTensor(f"duq4_bench_{tag}_out", (M, N), torch.float16, create=False)
         e2e_x, e2e_out = shared_x.tensor, shared_out.tensor
-        e2e_out_ptr = e2e_out.data_ptr() + 2 * rank * Ns
-    epi_host = L.make_epilogue("sym", None, None, sw, col_offset=rank * Ns, ldo=N)
-    if world == 1:
-        staging_bytes = L.cdll.duq4_linear_host_staging_bytes(M, Ns, K, 0)
-    else:
-        staging_bytes = L.cdll.duq4_linear_pipeline_staging_bytes(1, 1, M, Ns, K, 0)
-        rows_per = -(-M // world)
-        x_gather = torch.empty((rows_per * world, K), dtype=torch.float16, device=device)
-        x_slice = torch.zeros((rows_per, K), dtype=torch.float16, device=device)
-        r0, r1 = min(M, rank * rows_per), min(M, (rank + 1) * rows_per)
-    staging = torch.empty(staging_bytes, dtype=torch.uint8, device=device)
+    # the public API of a host-resident job: ColumnParallelLinear4bit.forward_host (one GPU: the host-buffer entry
+    # point; G GPUs: row-sharded upload, NVLink all-gather of the activations, then per --e2e-delivery)
+    from duqlinear4bitcuda_b200.parallel import ColumnParallelLinear4bit
+    host_layer = ColumnParallelLinear4bit("sym", N, qw, sw, unsharded=(world == 1))
 
     def step_e2e():
-        if world == 1:
-            L.call("duq4_linear_w4a4_from_fp16_host", e2e_x.data_ptr(), L.ptr(qw), M, Ns, K, L.MODE_SYM, 1.0,
-                   ctypes.byref(epi_host), e2e_out_ptr, 0, L.ptr(staging), staging_bytes, st())
-            return
-        # every byte crosses PCIe once: this rank uploads its row slice of the one host input over its own link, the
-        # slices are all-gathered over NVLink (the path's one exchange step), the rank computes its column block and
-        # delivers it into its column slice of the one host result, download overlapped with the arithmetic
-        x_slice[: r1 - r0].copy_(e2e_x[r0:r1], non_blocking=True)
-        dist.all_gather_into_tensor(x_gather, x_slice)
-        L.call("duq4_linear_w4a4_from_fp16_to_host", L.ptr(x_gather), L.ptr(w8), 1, M, Ns, K, L.MODE_SYM, 1.0,
-               ctypes.byref(epi_host), e2e_out_ptr, 0, L.ptr(staging), staging_bytes, st())
+        host_layer.forward_host(e2e_x, e2e_out, delivery=args.e2e_delivery)
 
     def barrier():
         if world > 1:
@@ -852,11 +835,15 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": round(e2e_tops, 2), "unit": "TOPS", "ms_per_step": round(e2e_ms / args.steps, 4),
                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
-                    "api": ("duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, copies pipelined with the arithmetic over row chunks)"
-                            if world == 1 else
-                            "one input and one result in shared pinned host memory; each rank uploads its row slice of the activations over its own "
-                            "PCIe link, NCCL all-gather of the slices over NVLink, duq4_linear_w4a4_from_fp16_to_host (C ABI) per rank delivers its "
-                            "[M, N/G] column block into its column slice of the one host result, download overlapped with the arithmetic")},
+                    "api": ("ColumnParallelLinear4bit.forward_host -> duq4_linear_w4a4_from_fp16_host (C ABI; pinned host activations in, pinned host result out, "
+                            "copies pipelined with the arithmetic over row chunks)" if world == 1 else
+                            "ColumnParallelLinear4bit.forward_host: one input and one result in shared pinned host memory; each rank uploads its row slice "
+                            "of the activations over its own PCIe link, NCCL all-gather of the slices over NVLink, then "
+                            + ("duq4_linear_w4a4_from_fp16_to_host_rows (C ABI): per row chunk the GEMM epilogue stores each row into the exchange buffer of "
+                               "the rank that owns it (NVLink), a rank barrier, and every rank downloads the contiguous rows it owns while the next chunk is computed"
+                               if args.e2e_delivery == "rows" else
+                               "duq4_linear_w4a4_from_fp16_to_host (C ABI) per rank delivers its [M, N/G] column block into its column slice of the one host "
+                               "result, download overlapped with the arithmetic"))},
             "checks": checks,
             "sustained": sustained,
             "gpu_launches": args.steps * ((2 * -(-M // max(256, -(-(args.chunk_rows or (M + 15) // 16) // 256) * 256)) + 2) if (peer is not None and args.gather == "copy")
@@ -910,6 +897,9 @@ def main():
                          "'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
     ap.add_argument("--multicast", action="store_true", help="N>1, --gather fused: one multimem.st per row segment instead of one plain store per peer")
     ap.add_argument("--chunk-rows", type=int, default=0, help="N>1, --gather copy: rows per pipeline chunk (0 = M/16 rounded to 256)")
+    ap.add_argument("--e2e-delivery", default="rows", choices=["rows", "columns"],
+                    help="N>1, host-resident job: 'rows' = rows exchanged over NVLink by the epilogue, each rank downloads contiguous rows; "
+                         "'columns' = each rank downloads its column block into its column slice of the host result")
     ap.add_argument("--tp-mlp", action="store_true", help="N>1: also time a tensor-parallel (column -> row) MLP block")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2-second back-to-back run")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")

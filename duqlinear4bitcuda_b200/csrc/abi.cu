@@ -33,7 +33,9 @@ int quantize_fused_dispatch(int mode, const void *x, uint32_t rows, uint32_t col
 
 constexpr uint32_t kSmallM = 16;  // at or below this many tokens the layer is weight-bandwidth bound
 
-static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParams *p) {
+// `rows`: row count of the call when the entry point supports row routing of the fused gather
+// (out_rows_per_owner), -1 when it does not.
+static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParams *p, int64_t rows = -1) {
     *p = EpiParams{};
     if (!e) {
         p->mode = DUQ4_MODE_NONE;
@@ -59,6 +61,11 @@ static int check_epi(const duq4_epilogue *e, uint32_t N, bool need_row, EpiParam
         p->peers[i] = (__half *)e->out_peers[i];
     }
     p->mc_out = e->n_out_peers ? (__half *)e->out_multicast : nullptr;
+    if (e->out_rows_per_owner) {
+        if (e->n_out_peers == 0 || e->out_multicast || rows < 0) return DUQ4_ERR_MODE;
+        if ((int64_t)e->n_out_peers * e->out_rows_per_owner < rows) return DUQ4_ERR_SHAPE;
+        p->out_rows_per_owner = e->out_rows_per_owner;
+    }
     if (e->n_acc_owners) {
         if (e->n_acc_owners > DUQ4_MAX_OUT_PEERS || e->acc_rows_per_owner == 0 || e->acc_slot >= e->n_acc_owners || (N & 3u) != 0)
             return DUQ4_ERR_SHAPE;
@@ -160,7 +167,7 @@ int duq4_linear_w4a4(const uint8_t *A, const uint8_t *W, uint32_t M, uint32_t N,
                      void *out, int32_t *acc_out, void *stream) {
     DUQ4_TRACE();
     EpiParams p;
-    int rc = check_epi(epi, N, true, &p);
+    int rc = check_epi(epi, N, true, &p, M);
     if (rc) return rc;
     return linear_dispatch(A, W, M, N, K, 1, p, out, acc_out, (cudaStream_t)stream);
 }
@@ -181,7 +188,7 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
                                  const duq4_epilogue *epi, void *out, int32_t *acc_out, void *stream) {
     DUQ4_TRACE();
     EpiParams p;
-    int rc = check_epi(epi, N, true, &p);
+    int rc = check_epi(epi, N, true, &p, M);
     if (rc) return rc;
     if (!A_i8 || !W) return DUQ4_ERR_NULL;
     if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
@@ -198,7 +205,7 @@ int duq4_linear_w4a4_prelaid(const int8_t *A_i8, const int8_t *W_i8, uint32_t M,
                              void *out, int32_t *acc_out, void *split_scratch, size_t split_scratch_bytes, void *stream) {
     DUQ4_TRACE();
     EpiParams p;
-    int rc = check_epi(epi, N, true, &p);
+    int rc = check_epi(epi, N, true, &p, M);
     if (rc) return rc;
     if (!A_i8 || !W_i8) return DUQ4_ERR_NULL;
     if (p.mode != DUQ4_MODE_NONE && !out && !p.n_peers) return DUQ4_ERR_NULL;
@@ -264,7 +271,7 @@ int duq4_linear_w4a4_from_fp16(const void *x, const uint8_t *W, uint32_t M, uint
         workspace_bytes < duq4_linear_from_fp16_workspace_bytes(M, K))
         return DUQ4_ERR_WORKSPACE;
     EpiParams p;
-    int rc = check_epi(epi, N, false, &p);
+    int rc = check_epi(epi, N, false, &p, M);
     if (rc) return rc;
     if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
     uint8_t *ws = (uint8_t *)workspace;
@@ -302,7 +309,7 @@ int duq4_linear_w4a4_from_fp16_prelaid(const void *x, const int8_t *W_i8, uint32
         return DUQ4_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(W_i8) & 15) != 0) return DUQ4_ERR_ALIGN;
     EpiParams p;
-    int rc = check_epi(epi, N, false, &p);
+    int rc = check_epi(epi, N, false, &p, M);
     if (rc) return rc;
     if (p.mode == DUQ4_MODE_NONE) return DUQ4_ERR_MODE;
     const bool epi_asym = p.mode == DUQ4_MODE_ASYM || p.mode == DUQ4_MODE_ASYM_DUAL;

@@ -104,7 +104,13 @@ struct EpiParams {
     // K-sharded layers: int32 partial accumulators go to the owner of each row block (see duq4_epilogue.acc_owners)
     uint32_t n_acc_owners, acc_rows_per_owner, acc_slot;
     int32_t *acc_owners[DUQ4_MAX_OUT_PEERS];
+    // fused gather with row routing: > 0 = row m of the launch is stored only into peers[m / out_rows_per_owner]
+    uint32_t out_rows_per_owner;
 };
+// Does row m of a launch go to output buffer pi? (every buffer without row routing)
+__device__ __forceinline__ bool row_goes_to(const EpiParams &p, uint32_t m, int pi) {
+    return p.out_rows_per_owner == 0 || m / p.out_rows_per_owner == (uint32_t)pi;
+}
 
 // Output bases of a launch: the peer list if there is one, else the plain `out` pointer.
 struct OutBases {

@@ -261,6 +261,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
 #pragma unroll
             for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
                 if (pi >= ob.n) break;
+                if (!row_goes_to(pb, m, pi)) continue;
                 __half *orow = ob.base[pi] + ooff;
                 if (full && vec_ok) {
                     *reinterpret_cast<uint4 *>(orow + c0) = *reinterpret_cast<const uint4 *>(&o[0]);
@@ -294,6 +295,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
 #pragma unroll
             for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi) {
                 if (pi >= ob.n) break;
+                if (!row_goes_to(pb, mr, pi)) continue;
                 if (seg_full && vec_ok) {
                     *reinterpret_cast<uint4 *>(ob.base[pi] + off) = seg;
                 } else {

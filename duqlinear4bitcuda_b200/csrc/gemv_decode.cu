@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_w4a4_kernel(const uint8_
             } else {   // fused all-gather: the same element into every rank's buffer
 #pragma unroll
                 for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                    if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+                    if (pi < (int)p.n_peers && row_goes_to(p, m, pi)) p.peers[pi][off] = v;
             }
         }
     }
@@ -457,7 +457,7 @@ gemv_w4a4_tma_kernel(const __grid_constant__ CUtensorMap tmW, const uint8_t *__r
                     } else {
 #pragma unroll
                         for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                            if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+                            if (pi < (int)p.n_peers && row_goes_to(p, m, pi)) p.peers[pi][off] = v;
                     }
                 }
             }
@@ -682,7 +682,7 @@ gemv_w4a4_persist_kernel(const uint8_t *__restrict__ A, const uint8_t *__restric
                     } else {
 #pragma unroll
                         for (int pi = 0; pi < DUQ4_MAX_OUT_PEERS; ++pi)
-                            if (pi < (int)p.n_peers) p.peers[pi][off] = v;
+                            if (pi < (int)p.n_peers && row_goes_to(p, m, pi)) p.peers[pi][off] = v;
                     }
                 }
             }

@@ -21,6 +21,13 @@
 //                                        copy engines push chunk c-1 to the other ranks' buffers (2-D peer copies over
 //                                        NVLink, one helper stream per peer) -- the all-gather runs on the copy
 //                                        engines, overlapped with the arithmetic, instead of as stores of the epilogue.
+//
+// duq4_linear_w4a4_from_fp16_to_host_rows (run_rows_pipeline) is the N-sharded job whose result goes back to ONE host
+// buffer: concurrent downloads of the ranks' column blocks interleave 1/G-row pieces of every host row, which the host
+// side of this machine class takes at about half the rate of contiguous rows. So the ranks first exchange over NVLink
+// (idle in such a job): the epilogue of each rank's GEMM stores row m of a chunk only into the buffer of the rank that
+// owns row m (out_rows_per_owner), a rank barrier makes the chunk complete, and every rank downloads the contiguous
+// full-width rows it owns while the next chunk is computed.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -218,6 +225,70 @@ int run_pipeline(const void *x, bool x_on_host, const void *W, bool prelaid, uin
     return rc;
 }
 
+// See the file comment. `bases[i]`: row 0, column 0 of rank i's [M, ldo] exchange buffer.
+int run_rows_pipeline(const void *x, const void *W, bool prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode, float clip_ratio,
+                      const duq4_epilogue *epi, uint32_t col_begin, uint32_t self, const void *const *flags, uint64_t *epoch_io,
+                      uint64_t timeout_ns, void *out_host, uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream) {
+    if (!x || !epi || !flags || !epoch_io || !out_host || (N && !W)) return DUQ4_ERR_NULL;
+    const uint32_t G = epi->n_out_peers;
+    if (G == 0 || G > (uint32_t)kMaxPeers || self >= G) return DUQ4_ERR_SHAPE;
+    for (uint32_t i = 0; i < G; ++i)
+        if (!epi->out_peers[i] || !flags[i]) return DUQ4_ERR_NULL;
+    if (epi->out_multicast || epi->out_rows_per_owner) return DUQ4_ERR_MODE;   // the routing is chosen here, per chunk
+    const uint64_t ldo = epi->ldo;
+    if (ldo == 0 || (uint64_t)col_begin + N > ldo) return DUQ4_ERR_SHAPE;
+    if (M == 0) return DUQ4_OK;
+    if (K == 0 || K % 64 != 0 || (prelaid && K % 128 != 0)) return DUQ4_ERR_SHAPE;
+    const uint32_t rows = pick_chunk_rows(M, chunk_rows);
+    const size_t ws_bytes = N == 0 ? 0 : (prelaid ? duq4_linear_from_fp16_prelaid_workspace_bytes(rows, K) : duq4_linear_from_fp16_workspace_bytes(rows, K));
+    if (N && (!staging || (reinterpret_cast<uintptr_t>(staging) & 255) != 0 || staging_bytes < ws_bytes)) return DUQ4_ERR_WORKSPACE;
+    PipeState *ps = nullptr;
+    int rc = pipe_state(&ps);
+    if (rc) return rc;
+    const uint32_t chunks = (M + rows - 1) / rows;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    uint64_t epoch = *epoch_io;
+    std::lock_guard<std::mutex> enqueue_lock(g_call_mu);
+#define DUQ4_TRY(call)                       \
+    do {                                     \
+        e = (call);                          \
+        if (e != cudaSuccess) { *epoch_io = epoch; return (int)e; } \
+    } while (0)
+    // every rank has finished with the previous contents of the exchange buffers (its own download included: that
+    // joined the caller's stream) before anybody stores into them
+    if ((rc = duq4_peer_barrier(flags, G, self, ++epoch, timeout_ns, stream)) != 0) { *epoch_io = epoch; return rc; }
+    DUQ4_TRY(cudaEventRecord(ps->fork, st));
+    DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->fork, 0));
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const uint32_t r0 = c * rows, nr = (M - r0 < rows) ? M - r0 : rows;
+        const uint32_t sub = (nr + G - 1) / G;   // rows of this chunk per owner
+        if (N && rc == 0) {
+            duq4_epilogue ce = *epi;
+            for (uint32_t i = 0; i < G; ++i) ce.out_peers[i] = (uint8_t *)epi->out_peers[i] + ((size_t)r0 * ldo + col_begin) * 2;
+            ce.out_rows_per_owner = sub;
+            const uint8_t *xc = (const uint8_t *)x + (size_t)r0 * K * 2;
+            rc = prelaid ? duq4_linear_w4a4_from_fp16_prelaid(xc, (const int8_t *)W, nr, N, K, act_mode, clip_ratio, &ce, nullptr, staging, ws_bytes, stream)
+                         : duq4_linear_w4a4_from_fp16(xc, (const uint8_t *)W, nr, N, K, act_mode, clip_ratio, &ce, nullptr, staging, ws_bytes, stream);
+        }
+        // the barriers are kept on the error path too, so that the other ranks are not left waiting for this one
+        const int brc = duq4_peer_barrier(flags, G, self, ++epoch, timeout_ns, stream);
+        if (brc && !rc) rc = brc;
+        if (rc) continue;
+        const uint64_t m0 = (uint64_t)r0 + (uint64_t)self * sub, m1 = (m0 + sub < (uint64_t)r0 + nr) ? m0 + sub : (uint64_t)r0 + nr;
+        if (m1 <= m0) continue;
+        DUQ4_TRY(cudaEventRecord(ps->computed[c], st));
+        DUQ4_TRY(cudaStreamWaitEvent(ps->down, ps->computed[c], 0));
+        DUQ4_TRY(cudaMemcpyAsync((uint8_t *)out_host + m0 * ldo * 2, (const uint8_t *)epi->out_peers[self] + m0 * ldo * 2, (m1 - m0) * ldo * 2,
+                                 cudaMemcpyDeviceToHost, ps->down));
+    }
+    DUQ4_TRY(cudaEventRecord(ps->join_down, ps->down));
+    DUQ4_TRY(cudaStreamWaitEvent(st, ps->join_down, 0));
+#undef DUQ4_TRY
+    *epoch_io = epoch;
+    return rc;
+}
+
 }  // namespace
 
 extern "C" {
@@ -267,6 +338,15 @@ int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_p
     sink.n_peers = epi->n_out_peers;
     sink.self = self_index;
     return run_pipeline(x, false, W, w_is_prelaid != 0, M, N, K, act_mode, clip_ratio, epi, sink, chunk_rows, staging, staging_bytes, stream);
+}
+
+int duq4_linear_w4a4_from_fp16_to_host_rows(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K, int act_mode,
+                                            float clip_ratio, const duq4_epilogue *epi, uint32_t col_begin, uint32_t self_index,
+                                            const void *const *barrier_flags, uint64_t *barrier_epoch, uint64_t barrier_timeout_ns,
+                                            void *out_host, uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream) {
+    DUQ4_TRACE();
+    return run_rows_pipeline(x, W, w_is_prelaid != 0, M, N, K, act_mode, clip_ratio, epi, col_begin, self_index, barrier_flags, barrier_epoch,
+                             barrier_timeout_ns, out_host, chunk_rows, staging, staging_bytes, stream);
 }
 
 }  // extern "C"

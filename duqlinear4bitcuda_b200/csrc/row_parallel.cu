@@ -188,6 +188,7 @@ int duq4_reduce_dequant_gather(const int32_t *slabs, uint32_t n_slabs, uint32_t 
         return DUQ4_ERR_NULL;
     if (!out && !epi->n_out_peers) return DUQ4_ERR_NULL;
     if (epi->n_out_peers > DUQ4_MAX_OUT_PEERS) return DUQ4_ERR_SHAPE;
+    if (epi->out_rows_per_owner) return DUQ4_ERR_MODE;   // this entry point replicates the rows it owns
     EpiParams p{};
     p.mode = epi->mode;
     p.col_offset = epi->col_offset;

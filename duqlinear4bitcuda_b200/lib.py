@@ -36,6 +36,7 @@ class Epilogue(ctypes.Structure):
         ("acc_rows_per_owner", ctypes.c_uint32),
         ("acc_slot", ctypes.c_uint32),
         ("acc_owners", ctypes.c_void_p * 8),
+        ("out_rows_per_owner", ctypes.c_uint32),
     ]
 
 
@@ -95,6 +96,8 @@ SIGNATURES = {
     "duq4_row_stats": [_i, _vp, _u32, _u32, _vp, _vp, _vp],
     "duq4_quantize_i8_from_stats": [_i, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp],
     "duq4_reduce_dequant_gather": [_vp, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(Epilogue), _vp, _vp],
+    "duq4_linear_w4a4_from_fp16_to_host_rows": [_vp, _vp, _i, _u32, _u32, _u32, _i, _f32, ctypes.POINTER(Epilogue), _u32, _u32,
+                                                ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint64, _vp, _u32, _vp, _sz, _vp],
     "duq4_peer_barrier": [ctypes.POINTER(ctypes.c_void_p), _u32, _u32, ctypes.c_uint64, ctypes.c_uint64, _vp],
     "duq4_last_device_status": [_vp, ctypes.POINTER(ctypes.c_int32)],
 }
@@ -137,7 +140,7 @@ def current_stream():
 
 def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_col_1=None, scale_col_2=None,
                   zeros_col_2=None, bias=None, col_offset=0, ldo=0, out_peers=None, next_weights=None, out_multicast=None,
-                  acc_owners=None, acc_rows_per_owner=0, acc_slot=0):
+                  acc_owners=None, acc_rows_per_owner=0, acc_slot=0, out_rows_per_owner=0):
     """Fill a duq4_epilogue. `next_weights`: packed weight tensor of the layer that runs next on the
     stream (L2 prefetch hint of the small-M kernels; never read or written by this launch)."""
     e = Epilogue()
@@ -160,6 +163,7 @@ def make_epilogue(mode, scale_row=None, zeros_row=None, scale_col_1=None, zeros_
         e.acc_slot = int(acc_slot)
         for i, a in enumerate(acc_owners):
             e.acc_owners[i] = int(a)
+    e.out_rows_per_owner = int(out_rows_per_owner)   # > 0: row m only to out_peers[m // out_rows_per_owner]
     if out_multicast:   # raw multicast address (int) of the same buffer, at this shard's first column
         e.out_multicast = int(out_multicast)
     if next_weights is not None:

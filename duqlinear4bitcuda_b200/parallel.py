@@ -253,16 +253,21 @@ class ColumnParallelLinear4bit(torch.nn.Module):
             return L.ptr(self._w8[1]), 1
         return L.ptr(self.weight), 0
 
-    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0):
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0, delivery: str = "rows"):
         """The layer for a job whose activations and result live in HOST memory that every rank maps
         (`SharedHostTensor`; any pinned host tensor when world == 1). PCIe is the scarce resource of such a job,
-        NVLink is idle, so every byte crosses PCIe once: rank r uploads rows [r*M/G, (r+1)*M/G) of the activations
-        over its own link, the row slices are all-gathered on the devices (NCCL over NVLink, the one exchange
-        step), every rank computes its column block and delivers it into its column slice of `out_host`
-        [M, n_out] with the download of a row chunk overlapping the arithmetic of the next
-        (duq4_linear_w4a4_from_fp16_to_host). One rank: upload, arithmetic and download pipelined by the
-        host-buffer entry point. The result is complete once every rank's stream has finished (synchronize, then
-        a host barrier). x_host fp16 [M, K]; out_host fp16 [M, n_out] row-major."""
+        NVLink is idle, so every byte crosses PCIe once and in contiguous pieces: rank r uploads rows
+        [r*M/G, (r+1)*M/G) of the activations over its own link, the row slices are all-gathered on the devices
+        (NCCL over NVLink), and every rank computes its column block row chunk by row chunk. delivery="rows"
+        (default): the GEMM epilogue stores each row of a chunk into the exchange buffer of the rank that owns the
+        row (an all-to-all over NVLink written by the epilogue), a rank barrier completes the chunk and every rank
+        downloads the contiguous full-width rows it owns while the next chunk is computed
+        (duq4_linear_w4a4_from_fp16_to_host_rows). delivery="columns": every rank downloads its own [M, N/G]
+        column block into its column slice of `out_host` (duq4_linear_w4a4_from_fp16_to_host): no exchange, but
+        the ranks' writes interleave within every host row, which the host takes at about half the rate.
+        One rank: upload, arithmetic and download pipelined by the host-buffer entry point. The result is
+        complete once every rank's stream has finished (synchronize, then a host barrier). x_host fp16 [M, K];
+        out_host fp16 [M, n_out] row-major."""
         from . import lib as L
         if x_host.is_cuda or out_host.is_cuda:
             raise ValueError("forward_host takes host tensors")
@@ -296,6 +301,30 @@ class ColumnParallelLinear4bit(torch.nn.Module):
         if r1 > r0:
             self._x_slice[: r1 - r0].copy_(x_host[r0:r1], non_blocking=True)
         dist.all_gather_into_tensor(self._x_dev, self._x_slice, group=self.group)
+        if delivery == "rows":
+            if self._peer is None:
+                self._peer = {}
+            peer = self._peer.get((M, "host_rows"))
+            if peer is None:
+                peer = self._peer[(M, "host_rows")] = PeerOutput(M, self.n_out, dev, self.group, use_multicast=False)
+            epi = L.make_epilogue(self.mode, None, None, flat(self.scales_1), flat(self.zeros_1), flat(self.scales_2),
+                                  flat(self.zeros_2), self.bias, col_offset=self.col_begin, ldo=self.n_out, out_peers=peer.ptrs)
+            wptr, prelaid = self._weights_for(M, K) if n_local else (None, 0)
+            need = max(256, L.cdll.duq4_linear_pipeline_staging_bytes(0, prelaid, M, max(n_local, 1), K, chunk_rows))
+            if self._staging is None or self._staging.numel() < need:
+                self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
+            epoch = ctypes.c_uint64(peer.epoch)
+            try:
+                with torch.cuda.device(dev):
+                    L.call("duq4_linear_w4a4_from_fp16_to_host_rows", L.ptr(self._x_dev), wptr, prelaid, M, n_local, K, L.MODES[self.mode],
+                           float(self.clip_ratio), ctypes.byref(epi), self.col_begin, self.rank, peer._flag_ptrs, ctypes.byref(epoch),
+                           peer.barrier_timeout_ns, out_host.data_ptr(), chunk_rows, L.ptr(self._staging), self._staging.numel(),
+                           L.current_stream())
+            finally:
+                peer.epoch = int(epoch.value)
+            return
+        if delivery != "columns":
+            raise ValueError("delivery must be 'rows' or 'columns'")
         if n_local == 0:
             return
         wptr, prelaid = self._weights_for(M, K)

@@ -248,6 +248,13 @@ typedef struct duq4_epilogue {
     uint32_t acc_rows_per_owner;
     uint32_t acc_slot;
     int32_t *acc_owners[8];
+    /* Row routing of the fused gather (optional, with n_out_peers > 0): 0 = every row goes to every buffer of
+     * out_peers (the replicated result above). R > 0 = row m of this call is stored ONLY into
+     * out_peers[m / R] (n_out_peers * R >= M): after all ranks' launches, buffer o holds rows [o*R, (o+1)*R) of the
+     * full-width result and nothing else -- an all-to-all written by the epilogue, which is what a job needs whose
+     * result leaves the GPUs again (each rank downloads the contiguous rows it owns; see
+     * duq4_linear_w4a4_from_fp16_to_host_rows). out_multicast must be NULL. */
+    uint32_t out_rows_per_owner;
 } duq4_epilogue;
 
 /* out[M,N] fp16 = dequant(A[M,K/2] x W[N,K/2]^T) (+ bias); replaces the three launches
@@ -415,6 +422,25 @@ int duq4_linear_w4a4_from_fp16_to_host(const void *x, const void *W, int w_is_pr
 int duq4_linear_w4a4_from_fp16_to_peers(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K,
                                         int act_mode, float clip_ratio, const duq4_epilogue *epi, uint32_t self_index,
                                         uint32_t chunk_rows, void *staging, size_t staging_bytes, void *stream);
+
+/* N-sharded layer whose activations are on the device and whose ONE result [M, epi->ldo] lives in HOST memory
+ * that every rank can write (no reference counterpart). Rank `self_index` of G = epi->n_out_peers holds the
+ * weights of columns [col_begin, col_begin + N) (N may be 0: the rank then only takes part in the exchange).
+ * epi->out_peers[i] is row 0, column 0 of rank i's [M, epi->ldo] device exchange buffer (peer-mapped, as for the
+ * fused all-gather; epi->ldo is the full width and must be given; out_multicast NULL). Per row chunk: quantize +
+ * GEMM + dequant, whose epilogue stores row m only into the buffer of the rank that owns it (1/G of the chunk's
+ * rows each, out_rows_per_owner) -- the column blocks cross NVLink instead of interleaving on the host --, a rank
+ * barrier (duq4_peer_barrier on `barrier_flags`, epochs *barrier_epoch + 1 ... ; the last epoch used is written
+ * back), then the download of the contiguous full-width rows this rank owns into out_host, overlapped with the
+ * next chunk. Every rank calls it with the same M, K, epi->ldo, chunk_rows. The call joins its helper stream
+ * into `stream` before it returns; the host result is complete when every rank's stream has finished.
+ * `staging`: duq4_linear_pipeline_staging_bytes(0, w_is_prelaid, M, N, K, chunk_rows) bytes of device memory.
+ * Same bits as the unsharded layer. A rank whose barrier wait runs out records status 301. */
+int duq4_linear_w4a4_from_fp16_to_host_rows(const void *x, const void *W, int w_is_prelaid, uint32_t M, uint32_t N, uint32_t K,
+                                            int act_mode, float clip_ratio, const duq4_epilogue *epi, uint32_t col_begin,
+                                            uint32_t self_index, const void *const *barrier_flags, uint64_t *barrier_epoch,
+                                            uint64_t barrier_timeout_ns, void *out_host, uint32_t chunk_rows, void *staging,
+                                            size_t staging_bytes, void *stream);
 
 /* ---- K-sharded (row-parallel) layer: pieces of one fused forward per rank (no reference counterpart) ----
  * The column-parallel gate/up projection of a tensor-parallel MLP leaves each rank with its own K slice of the

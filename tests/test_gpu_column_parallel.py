@@ -127,8 +127,10 @@ def test_two_gpu_peer_barrier_times_out_instead_of_hanging(tmp_path, monkeypatch
 
 
 def _host_worker(rank, world, port, mode, M, N, K, tmp):
+    import ctypes
     import torch
     import torch.distributed as dist
+    import duqlinear4bitcuda_b200.lib as L
     from duqlinear4bitcuda_b200.parallel import ColumnParallelLinear4bit, SharedHostTensor
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
@@ -151,16 +153,27 @@ def _host_worker(rank, world, port, mode, M, N, K, tmp):
         if rank != 0:
             xh = SharedHostTensor(f"duq4_test_{port}_x", (M, K), torch.float16, create=False)
             oh = SharedHostTensor(f"duq4_test_{port}_o", (M, N), torch.float16, create=False)
-        for _ in range(2):   # twice: staging area and helper streams are reused
-            layer.forward_host(xh.tensor, oh.tensor, chunk_rows=256)
-            torch.cuda.synchronize()
-            dist.barrier()
         # the whole layer on this GPU alone through the same host entry point
         single = ColumnParallelLinear4bit(mode, N, qw, sc1, zc1 if asym else None, None, None, bias, unsharded=True)
         want = torch.empty((M, N), dtype=torch.float16).pin_memory()
         single.forward_host(xh.tensor, want)
         torch.cuda.synchronize()
-        ok = torch.equal(oh.tensor.view(torch.int16), want.view(torch.int16))
+        ok = True
+        # "rows": rows exchanged over NVLink by the epilogue, each rank downloads the contiguous rows it owns;
+        # "columns": each rank downloads its column block. Twice each: staging, exchange buffers, flags and helper
+        # streams are reused.
+        for delivery, chunk in (("rows", 256), ("rows", 0), ("columns", 256), ("rows", 256)):
+            if rank == 0:
+                oh.tensor.fill_(-3.0)
+            dist.barrier()
+            layer.forward_host(xh.tensor, oh.tensor, chunk_rows=chunk, delivery=delivery)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ok = ok and torch.equal(oh.tensor.view(torch.int16), want.view(torch.int16))
+            dist.barrier()
+        status = ctypes.c_int32(-1)
+        L.call("duq4_last_device_status", L.current_stream(), ctypes.byref(status))
+        ok = ok and status.value == 0
         open(os.path.join(tmp, f"r{rank}"), "w").write(str(int(ok)))
         dist.barrier()
     finally:
@@ -174,8 +187,9 @@ def _host_worker(rank, world, port, mode, M, N, K, tmp):
 def test_two_gpu_host_result_assembled_by_slices_matches_single_gpu(tmp_path, mode, M, N, K):
     """Host-resident job on 2 GPUs: each rank uploads its row slice of the one shared pinned host input (ragged: 701
     rows), the slices are all-gathered over NVLink, and each rank delivers its column block into its slice of the one
-    shared host result; the assembled result equals the 1-GPU host entry point bit for bit (packed weights at 8 tokens,
-    the pre-laid-out int8 copy from 256 tokens on)."""
+    shared host result -- as contiguous rows after an exchange over NVLink written by the GEMM epilogue (default), or
+    as its own column block; the assembled result equals the 1-GPU host entry point bit for bit (packed weights at 8
+    tokens, the pre-laid-out int8 copy from 256 tokens on)."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:

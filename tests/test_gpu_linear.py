@@ -563,6 +563,87 @@ def test_row_parallel_pieces_on_one_gpu_equal_unsharded_layer(env, mode, M, N, K
     assert L.cdll.duq4_row_stats(L.MODE_SYM_DUAL, L.ptr(xs[0]), M, 64, L.ptr(sa[0]), None, st) == -3   # dual schemes do not commute with a K split
 
 
+@pytest.mark.parametrize("mode,M,N,K,G,R", [("sym", 700, 520, 512, 3, 256), ("asym_dual", 1000, 1032, 256, 4, 250), ("sym", 100, 392, 256, 2, 64),
+                                            ("asym", 12, 264, 512, 3, 4), ("sym_dual", 16, 136, 128, 8, 2), ("sym", 2048, 2048, 1024, 8, 256)])
+def test_fused_gather_row_routing_delivers_each_row_to_its_owner_only(env, mode, M, N, K, G, R):
+    """duq4_epilogue.out_rows_per_owner: row m of a launch is stored only into out_peers[m // R]. With G buffers on
+    one GPU (NaN-filled) each buffer must end up holding exactly its block of rows of the ordinary result and NaN
+    elsewhere -- through every kernel family: the CTA-pair kernel on pre-laid-out and on packed weights, the narrow-tile
+    kernel (M <= 128) and the small-M kernels (M <= 16)."""
+    torch, L, o = env
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    x = U.acts(M, K, 21 + M, mean=0.1 if asym else 0.0)
+    qw = U.rand_codes(N, K, 22); sc1 = U.rand_scales(N, 23); zc1 = U.rand_zeros(N, 24); sc2 = U.rand_scales(N, 25); zc2 = U.rand_zeros(N, 26)
+    bias = np.random.default_rng(27).standard_normal(N).astype(np.float16)
+    dx, dqw, dsc1, dzc1, dsc2, dzc2, db = (dev(torch, v) for v in (x, qw, sc1, zc1, sc2, zc2, bias))
+    st = L.current_stream()
+    vecs = (dsc1, dzc1 if asym else None, dsc2 if dual else None, dzc2 if mode == "asym_dual" else None, db)
+    ws = torch.empty(max(L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K), L.cdll.duq4_linear_from_fp16_prelaid_workspace_bytes(M, K)),
+                     dtype=torch.uint8, device="cuda")
+    want = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 1.0,
+           ctypes.byref(L.make_epilogue(mode, None, None, *vecs)), L.ptr(want), L.ptr(ws), ws.numel(), st)
+    routes = ["packed"] + (["prelaid"] if K % 128 == 0 and M > 16 else [])
+    for route in routes:
+        bufs = [torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda") for _ in range(G)]
+        epi = L.make_epilogue(mode, None, None, *vecs, ldo=N, out_peers=[b.data_ptr() for b in bufs], out_rows_per_owner=R)
+        if route == "packed":
+            L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), None, L.ptr(ws), ws.numel(), st)
+        else:
+            w8 = torch.empty((N, K), dtype=torch.int8, device="cuda")
+            L.call("duq4_weight_prelayout_i8", L.ptr(dqw), N, K, L.ptr(w8), st)
+            L.call("duq4_linear_w4a4_from_fp16_prelaid", L.ptr(dx), L.ptr(w8), M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), None, L.ptr(ws), ws.numel(), st)
+        torch.cuda.synchronize()
+        assert tc_status(L) == 0
+        for g, b in enumerate(bufs):
+            lo, hi = min(M, g * R), min(M, (g + 1) * R)
+            assert torch.equal(b[lo:hi].view(torch.int16), want[lo:hi].view(torch.int16)), (route, g)
+            rest = torch.cat([b[:lo], b[hi:]])
+            assert bool(torch.isnan(rest).all()), (route, g)
+    # too few owners for the rows, multicast together with routing, an entry point without routing
+    bad = L.make_epilogue(mode, None, None, *vecs, ldo=N, out_peers=[want.data_ptr()], out_rows_per_owner=max(1, M - 1))
+    if M > 1:
+        assert L.cdll.duq4_linear_w4a4_from_fp16(L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(bad), None, L.ptr(ws), ws.numel(), st) == -2
+    bad2 = L.make_epilogue(mode, None, None, *vecs, ldo=N, out_rows_per_owner=R)
+    assert L.cdll.duq4_linear_w4a4_from_fp16(L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 1.0, ctypes.byref(bad2), L.ptr(want), L.ptr(ws), ws.numel(), st) == -3
+
+
+@pytest.mark.parametrize("mode,M,N,K,chunk", [("sym", 700, 520, 512, 256), ("asym", 40, 264, 256, 0), ("sym_dual", 2048, 1024, 1024, 512)])
+def test_host_rows_pipeline_with_one_rank_equals_device_entry(env, mode, M, N, K, chunk):
+    """duq4_linear_w4a4_from_fp16_to_host_rows with a single rank (its exchange is then a plain store into the rank's own
+    buffer and its barrier has nobody to wait for): chunked arithmetic, barrier epochs and the download of the owned rows
+    give the same bits as the device entry point; a second call reuses buffers and continues the epochs."""
+    torch, L, o = env
+    asym, dual = mode.startswith("asym"), mode.endswith("dual")
+    x = U.acts(M, K, 31 + M, mean=0.1 if asym else 0.0)
+    qw = U.rand_codes(N, K, 32); sc1 = U.rand_scales(N, 33); zc1 = U.rand_zeros(N, 34); sc2 = U.rand_scales(N, 35); zc2 = U.rand_zeros(N, 36)
+    dx, dqw, dsc1, dzc1, dsc2, dzc2 = (dev(torch, v) for v in (x, qw, sc1, zc1, sc2, zc2))
+    st = L.current_stream()
+    vecs = (dsc1, dzc1 if asym else None, dsc2 if dual else None, dzc2 if mode == "asym_dual" else None, None)
+    ws = torch.empty(L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K), dtype=torch.uint8, device="cuda")
+    want = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    L.call("duq4_linear_w4a4_from_fp16", L.ptr(dx), L.ptr(dqw), M, N, K, L.MODES[mode], 1.0,
+           ctypes.byref(L.make_epilogue(mode, None, None, *vecs)), L.ptr(want), L.ptr(ws), ws.numel(), st)
+    ldo, col_begin = N + 64, 32   # the block sits inside a wider result
+    buf = torch.zeros((M, ldo), dtype=torch.float16, device="cuda")
+    flags = torch.zeros(1, dtype=torch.int64, device="cuda")
+    flag_ptrs = (ctypes.c_void_p * 1)(flags.data_ptr())
+    out_host = torch.full((M, ldo), -3.0, dtype=torch.float16).pin_memory()
+    staging = torch.empty(max(256, L.cdll.duq4_linear_pipeline_staging_bytes(0, 0, M, N, K, chunk)), dtype=torch.uint8, device="cuda")
+    epi = L.make_epilogue(mode, None, None, *vecs, ldo=ldo, out_peers=[buf.data_ptr()])
+    epoch = ctypes.c_uint64(0)
+    for call in range(2):
+        L.call("duq4_linear_w4a4_from_fp16_to_host_rows", L.ptr(dx), L.ptr(dqw), 0, M, N, K, L.MODES[mode], 1.0, ctypes.byref(epi), col_begin, 0,
+               flag_ptrs, ctypes.byref(epoch), 0, out_host.data_ptr(), chunk, L.ptr(staging), staging.numel(), st)
+        torch.cuda.synchronize()
+        assert tc_status(L) == 0
+        assert torch.equal(out_host[:, col_begin:col_begin + N].contiguous().view(torch.int16), want.cpu().view(torch.int16))
+        assert bool((out_host[:, :col_begin] == 0).all()) and bool((out_host[:, col_begin + N:] == 0).all())   # the rest of the owned rows as the buffer had it
+        out_host.fill_(-3.0)
+    rows = chunk if chunk else max(256, -(-((M + 15) // 16) // 256) * 256)
+    assert epoch.value == 2 * (1 + -(-M // min(M, rows)))
+
+
 @pytest.mark.parametrize("K", [512, 4096])
 def test_decode_static_weights_overlap_keeps_stream_order(env, K):
     """With duq4_set_static_weights(1) the small-M kernels start streaming weights before the
