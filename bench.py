@@ -559,9 +559,10 @@ def run_profile_case(args):
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         for _ in range(4):
             L.call("duq4_linear_w4a4_preunpacked", L.ptr(a8), L.ptr(qw), M, N, K, ctypes.byref(epi), L.ptr(y), None, st())
-    elif args.profile_case in ("gemm_prelaid", "gemm_headline"):
-        # gemm_headline: the bench's own shape, with the K-split of the last round of tiles (0.6 GB on the device)
-        M, N, K = (2048, 8192, 8192) if args.profile_case == "gemm_prelaid" else (M_TOK, N_OUT, K_IN)
+    elif args.profile_case in ("gemm_prelaid", "gemm_headline", "gemm_m512"):
+        # gemm_headline: the bench's own shape, with the K-split of the last round of tiles (0.6 GB on the device);
+        # gemm_m512: the 512-token point of the prefill sweep (two row blocks: every weight tile is used by two pairs only)
+        M, N, K = {"gemm_prelaid": (2048, 8192, 8192), "gemm_headline": (M_TOK, N_OUT, K_IN), "gemm_m512": (512, N_OUT, K_IN)}[args.profile_case]
         x = torch.randn((M, K), device=dev).half()
         qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev)
         a8 = torch.empty((M, K), dtype=torch.int8, device=dev); w8 = torch.empty((N, K), dtype=torch.int8, device=dev)
@@ -570,7 +571,7 @@ def run_profile_case(args):
         epi = L.make_epilogue("sym", sa, None, sw)
         L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(sa), None, None, None, st())
         L.call("duq4_weight_prelayout_i8", L.ptr(qw), N, K, L.ptr(w8), st())
-        sk = torch.empty(L.cdll.duq4_gemm_split_scratch_bytes() if args.profile_case == "gemm_headline" else 0, dtype=torch.uint8, device=dev)
+        sk = torch.empty(L.cdll.duq4_gemm_split_scratch_bytes() if args.profile_case != "gemm_prelaid" else 0, dtype=torch.uint8, device=dev)
         for _ in range(4):
             L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(epi), L.ptr(y), None, L.ptr(sk) if sk.numel() else None, sk.numel(), st())
     elif args.profile_case in ("decode", "decode16", "decode_layer"):
@@ -904,7 +905,7 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2-second back-to-back run")
     ap.add_argument("--no-decode", action="store_true", help="skip the M<=16 decode sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_prelaid", "gemm_headline", "decode", "decode16", "decode_layer", "quantize", "silu", "skinny"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_prelaid", "gemm_headline", "gemm_m512", "decode", "decode16", "decode_layer", "quantize", "silu", "skinny"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -296,7 +296,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // when the launch splits its last, partly filled round along K -- one K range of one of the remaining tiles.
     struct Work {
         uint32_t tile, k0, k1;
-        int sk_rank;        // -1: whole tile; 0: K-split tile, this pair owns the result; > 0: contributes a partial
+        int sk_rank;        // -1: whole tile; >= 0: K-split tile, this pair's place in the group that shares it
         uint32_t sk_slot;
     };
     const uint32_t dp_tiles = num_tiles - a.sk_tiles;
@@ -453,25 +453,37 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                          stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
             else {
-                // K-split tile. Partial slabs: [tile slot][contributor][CTA of the pair][128 rows][BN] int32.
-                const uint32_t G = a.sk_group;
+                // K-split tile: the G pairs of the group hold partial sums over their K ranges. Reduce-scatter through
+                // L2: the first R = min(G, 4) pairs each own a range of the tile's 16-column chunks (multiples of four
+                // chunks, so that the output staging below flushes whole 64-column groups). Phase 1: every pair writes
+                // the chunks it does not own to its slab -- [tile slot][pair of the group][CTA of the pair][128 rows][BN]
+                // int32 -- and arrives. Phase 2: an owning pair waits for the whole group, adds the other pairs' slabs to
+                // its own accumulators for its chunks, dequantizes and stores them. The adds are exact, so the result
+                // does not depend on the split.
+                const uint32_t G = a.sk_group, R = G < 4 ? G : 4;
+                const int nch = (int)(bn >> 4);
+                const int cpr = 4 * ((nch + 4 * (int)R - 1) / (4 * (int)R));
+                const int r = w.sk_rank;
+                const int own_b = r < (int)R ? min(nch, r * cpr) : 0, own_e = r < (int)R ? min(nch, (r + 1) * cpr) : 0;
                 const size_t slab = (size_t)BMH * BN;
-                int32_t *slot0 = a.sk_scratch + (size_t)w.sk_slot * (G - 1) * 2 * slab;
-                if (w.sk_rank > 0) {
-                    epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                             stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), nullptr, 0, 0,
-                                             slot0 + ((size_t)(w.sk_rank - 1) * 2 + rank) * slab);
-                    __threadfence();   // this lane's partial sums are visible device-wide before the arrival below
-                    __syncwarp();
-                    if (lane == 0) atomicAdd(a.sk_counters + w.sk_slot, 1u);
-                } else {
-                    // bounded wait for the 2 x EPI epilogue warps of each of the G - 1 contributing pairs
-                    const unsigned int want = (G - 1) * 2 * EPI;
+                int32_t *slot0 = a.sk_scratch + (size_t)w.sk_slot * G * 2 * slab;
+                tc::SplitK p1;
+                p1.out = slot0 + ((size_t)r * 2 + rank) * slab;
+                p1.keep_b = own_b; p1.keep_e = own_e;
+                epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                                         stage_out + (warp - 2) * kStageOutWarp, nch, p1);
+                __threadfence();   // this lane's partial sums are visible device-wide before the arrival below
+                __syncwarp();
+                unsigned int *cw = a.sk_counters + w.sk_slot;
+                if (lane == 0) atomicAdd(cw, 1u);
+                if (own_e > own_b) {
+                    // bounded wait for the 2 x EPI epilogue warps of each of the G pairs
+                    const unsigned int want = G * 2 * EPI;
                     bool arrived = false;
                     uint64_t t0 = 0;
                     for (uint32_t spin = 1; !arrived; ++spin) {
                         unsigned int v;
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sk_counters + w.sk_slot) : "memory");
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cw) : "memory");
                         arrived = v >= want;
                         if (arrived || (spin & 0x3Fu) != 0) continue;
                         if (*abortp) break;
@@ -484,9 +496,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         }
                     }
                     if (!(ok = arrived)) break;
+                    tc::SplitK p2;
+                    p2.add = slot0 + (size_t)rank * slab;
+                    p2.n = G; p2.skip = r; p2.stride = 2 * slab;
+                    p2.ch_b = own_b; p2.ch_e = own_e;
                     epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                             stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), slot0 + (size_t)rank * slab, G - 1,
-                                             2 * slab);
+                                             stage_out + (warp - 2) * kStageOutWarp, nch, p2);
                 }
             }
             tc_fence_before();
@@ -629,9 +644,10 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     const uint32_t tiles = a.tiles_m * a.tiles_n * batch;
     uint32_t pairs = tiles < (uint32_t)max_pairs ? tiles : (uint32_t)max_pairs;
     // K-split of the last, partly filled round (needs caller scratch): T tiles are left after the full rounds; when
-    // they occupy at most half of the pairs, each is computed by G pairs, a K range each, and the group's first pair
-    // adds the partial sums of the others before its epilogue. The round then costs about 1/G of a tile (plus the
-    // partial tiles' trip through L2) instead of a whole one: 8192 -> 28672 at 512 tokens is 224 tiles on 74 pairs,
+    // they occupy at most half of the pairs, each is computed by G pairs, a K range each, and up to four pairs of the
+    // group each add the others' partial sums for a quarter of the tile's columns before their epilogue (a
+    // reduce-scatter through L2). The round then costs about 1/G of a tile (plus the partial tiles' trip through L2)
+    // instead of a whole one: 8192 -> 28672 at 512 tokens is 224 tiles on 74 pairs,
     // 3 rounds + 2 tiles; the 2 tiles are split eight ways instead of taking a fourth round.
     a.sk_tiles = a.sk_group = 0;
     if (!GU && sk_scratch && (reinterpret_cast<uintptr_t>(sk_scratch) & 255) == 0) {
@@ -640,7 +656,7 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
         if (G > 8) G = 8;
         const uint32_t ksteps = cdiv(K, (uint32_t)BKE);
         while (G >= 2 && ksteps < 4 * G) --G;   // every K range keeps at least four pipeline stages of work
-        const size_t need = kSkCounterBytes + (size_t)T * (G > 1 ? G - 1 : 0) * 256 * 256 * sizeof(int32_t);
+        const size_t need = kSkCounterBytes + (size_t)T * G * 256 * 256 * sizeof(int32_t);
         if (T && G >= 2 && T * sizeof(unsigned int) <= kSkCounterBytes && need <= sk_bytes) {
             a.sk_tiles = T;
             a.sk_group = G;

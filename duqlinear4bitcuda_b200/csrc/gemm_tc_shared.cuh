@@ -90,8 +90,8 @@ struct Args {
     uint32_t a_rows;          // rows of the A buffer the tensor map may read (>= M; the extra rows are never stored)
     uint32_t gate_up;         // CTA-pair kernel only: 0, or I = width of a SiLU-gated gate/up projection (W has 2*I rows)
     // CTA-pair kernel only, K-split of the last, partly filled round of tiles: the last sk_tiles tiles are each
-    // computed by sk_group pairs (a K range each); pair 0 of a group adds the others' int32 partial tiles (sk_scratch)
-    // to its own before the dequant, the others signal sk_counters[tile slot] once per epilogue warp.
+    // computed by sk_group pairs (a K range each); the pairs exchange int32 partial tiles through sk_scratch and signal
+    // sk_counters[tile slot] once per epilogue warp; up to four of them reduce and store a column range each.
     uint32_t sk_tiles, sk_group;
     int32_t *sk_scratch;
     unsigned int *sk_counters;
@@ -133,17 +133,24 @@ __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb,
 // One warp's 32 rows of a 128-row accumulator slab: TMEM -> (>> shift) -> optional int32 store ->
 // fp16 dequant (+ bias) -> global / peer memory. `m_base` is the global row of the slab's first
 // row, `tmem_acc` the TMEM address (lane 0) of the accumulator's first column.
+// K-split of a tile over a group of CTA pairs (see the pair kernel): what one call of epi_store_tile does with the
+// partial-sum slabs. A slab (128 x BN int32) is private to the warps that exchange it -- the same lane quadrant of
+// the same CTA of each pair of the group -- so it is laid out for their access pattern: element (chunk ch, group of
+// four columns j4, lane, 4 ints), i.e. every 128-bit access of a warp covers 512 contiguous bytes.
+struct SplitK {
+    int32_t *out = nullptr;        // phase 1: the raw accumulators of every chunk OUTSIDE [keep_b, keep_e) go to this slab; nothing else happens
+    int keep_b = 0, keep_e = 0;
+    const int32_t *add = nullptr;  // phase 2: slabs add + c * stride, c in [0, n) except `skip`, are added to the accumulators
+    uint32_t n = 0;
+    int skip = -1;
+    size_t stride = 0;
+    int ch_b = 0, ch_e = -1;       // phase 2 handles the chunks [ch_b, ch_e) only (ch_e < 0: up to the tile's end)
+};
+
 template <int BN, bool STAGED>
 __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &pb, uint32_t b, uint32_t m_base, uint32_t n0,
                                    uint32_t tmem_acc, int quad, int lane, uint32_t shift, const __half *cs,
-                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16,
-                                   const int32_t *sk_add = nullptr, uint32_t sk_n = 0, size_t sk_stride = 0, int32_t *sk_out = nullptr) {
-    // sk_out: this CTA only contributes a K range of the tile -- its raw accumulators go to the slab sk_out and nothing
-    // else happens. sk_add / sk_n / sk_stride: sk_n such slabs (sk_stride ints apart) are added to the accumulators
-    // before they are used. A slab (128 x BN int32) is private to the two warps that exchange it -- the same lane
-    // quadrant of the same CTA of the contributing and of the owning pair -- so it is laid out for their access
-    // pattern: element (chunk ch, group of four columns j4, lane, 4 ints), i.e. every 128-bit access of a warp
-    // covers 512 contiguous bytes.
+                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16, const SplitK sk = SplitK()) {
     // nch: 16-column chunks of the accumulator that belong to this tile (tiles narrower than BN)
     const uint32_t n_end = min(a.N, n0 + 16u * (uint32_t)nch);   // first column not written by this tile
     const int mode = a.epi.mode;
@@ -175,23 +182,28 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
     __half *const mc = (STAGED && vec_ok && (reinterpret_cast<uintptr_t>(pb.mc_out) & 15u) == 0) ? pb.mc_out : nullptr;
     const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);   // owner buffers: alignment checked by the host
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
+    const int ch_first = sk.out ? 0 : sk.ch_b, ch_last = (sk.out || sk.ch_e < 0 || sk.ch_e > nch) ? nch : sk.ch_e;
 #pragma unroll 1
-    for (int ch = 0; ch < nch; ++ch) {
+    for (int ch = ch_first; ch < ch_last; ++ch) {
+        if (sk.out && ch >= sk.keep_b && ch < sk.keep_e) continue;   // this pair reduces these chunks itself
         uint32_t v[16];
         __syncwarp();  // tcgen05.ld is warp-collective
         tmem_ld16(taddr + ch * 16, v);
         tmem_ld_wait();
         const uint32_t c0 = ch * 16;
-        if (sk_out) {   // contributor of a K-split tile: raw accumulators to the scratch slab
-            int4 *dst = reinterpret_cast<int4 *>(sk_out) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
+        if (sk.out) {   // K-split tile, phase 1: raw accumulators to the scratch slab
+            int4 *dst = reinterpret_cast<int4 *>(sk.out) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
 #pragma unroll
             for (int j = 0; j < 16; j += 4) dst[(j >> 2) * 32] = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
             continue;
         }
-        for (uint32_t c = 0; c < sk_n; c += 2) {   // owner of a K-split tile: add the other pairs' partial sums, two slabs at a time
-            const int4 *s0 = reinterpret_cast<const int4 *>(sk_add + c * sk_stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
-            const bool two = c + 1 < sk_n;
-            const int4 *s1 = two ? reinterpret_cast<const int4 *>(sk_add + (c + 1) * sk_stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane : s0;
+        for (uint32_t c = 0; c < sk.n;) {   // K-split tile, phase 2: add the other pairs' partial sums, two slabs at a time
+            if ((int)c == sk.skip) { ++c; continue; }
+            uint32_t c1 = c + 1;
+            if ((int)c1 == sk.skip) ++c1;
+            const bool two = c1 < sk.n;
+            const int4 *s0 = reinterpret_cast<const int4 *>(sk.add + c * sk.stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
+            const int4 *s1 = two ? reinterpret_cast<const int4 *>(sk.add + c1 * sk.stride) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane : s0;
             int4 t0[4], t1[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -203,6 +215,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
                 v[4 * q] += (uint32_t)(t0[q].x + t1[q].x); v[4 * q + 1] += (uint32_t)(t0[q].y + t1[q].y);
                 v[4 * q + 2] += (uint32_t)(t0[q].z + t1[q].z); v[4 * q + 3] += (uint32_t)(t0[q].w + t1[q].w);
             }
+            c = c1 + 1;
         }
         const bool col_any = n0 + c0 < n_end;
         const bool full = n0 + c0 + 16 <= n_end;
@@ -215,7 +228,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
             int4 *mine = reinterpret_cast<int4 *>(stg + lane * 144 + (ch & 1) * 64);
 #pragma unroll
             for (int j = 0; j < 16; j += 4) mine[j >> 2] = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
-            if ((ch & 1) == 1 || ch == nch - 1) {
+            if ((ch & 1) == 1 || ch == ch_last - 1) {
                 __syncwarp();
                 const uint32_t g0 = (uint32_t)(ch >> 1) * 32 + (lane & 7) * 4;   // first column of this lane's 4 ints (tile-relative)
                 const bool second_half = (lane & 7) >= 4;                        // columns of the odd chunk of the pair
@@ -277,7 +290,7 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         // reads the block back as 128-byte row segments, four rows per store instruction
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
-        if ((ch & 3) != 3 && ch != nch - 1) continue;   // flush every 64 columns and at the tile's end
+        if ((ch & 3) != 3 && ch != ch_last - 1) continue;   // flush every 64 columns and at the end of the range
         __syncwarp();
         const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first column of this lane's 8 (tile-relative)
         const bool seg_full = n0 + g0 + 8 <= n_end;
