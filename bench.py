@@ -660,7 +660,8 @@ def run_ours(args):
     if world > 1 and args.gather in ("fused", "copy"):
         try:
             from duqlinear4bitcuda_b200.parallel import PeerOutput
-            peer = PeerOutput(M, N, device, use_multicast=args.multicast and args.gather == "fused")
+            use_mc = args.gather == "fused" and (args.multicast == "on" or (args.multicast == "auto" and world >= 8))
+            peer = PeerOutput(M, N, device, use_multicast=use_mc)
             epi_f = L.make_epilogue("sym", sa, None, sw, col_offset=rank * Ns, ldo=N, out_peers=peer.column_ptrs(rank * Ns),
                                     out_multicast=peer.multicast_column_ptr(rank * Ns))
             gather_mode = "fused, multimem.st through the NVLink switch" if peer.multicast_ptr else "fused, one st.global per peer"
@@ -896,9 +897,12 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["copy", "fused", "nccl"],
                     help="N>1: 'copy' = local epilogue + copy-engine peer copies per row chunk, overlapped with the next chunk's GEMM; "
                          "'fused' = GEMM epilogue stores into every rank's result buffer over NVLink; 'nccl' = all-gather")
-    ap.add_argument("--multicast", action="store_true", help="N>1, --gather fused: one multimem.st per row segment instead of one plain store per peer")
+    ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"], nargs="?", const="on",
+                    help="N>1, --gather fused: one multimem.st per row segment through the NVLink switch instead of one plain store per peer; "
+                         "auto = from 8 GPUs on (measured: plain stores win at 2 and 4 GPUs, where a rank's ingress is the limit; "
+                         "multicast wins at 8, where its egress is)")
     ap.add_argument("--chunk-rows", type=int, default=0, help="N>1, --gather copy: rows per pipeline chunk (0 = M/16 rounded to 256)")
-    ap.add_argument("--e2e-delivery", default="rows", choices=["rows", "columns"],
+    ap.add_argument("--e2e-delivery", default="columns", choices=["rows", "columns"],
                     help="N>1, host-resident job: 'rows' = rows exchanged over NVLink by the epilogue, each rank downloads contiguous rows; "
                          "'columns' = each rank downloads its column block into its column slice of the host result")
     ap.add_argument("--tp-mlp", action="store_true", help="N>1: also time a tensor-parallel (column -> row) MLP block")

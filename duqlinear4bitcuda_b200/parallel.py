@@ -253,18 +253,19 @@ class ColumnParallelLinear4bit(torch.nn.Module):
             return L.ptr(self._w8[1]), 1
         return L.ptr(self.weight), 0
 
-    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0, delivery: str = "rows"):
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunk_rows: int = 0, delivery: str = "columns"):
         """The layer for a job whose activations and result live in HOST memory that every rank maps
         (`SharedHostTensor`; any pinned host tensor when world == 1). PCIe is the scarce resource of such a job,
         NVLink is idle, so every byte crosses PCIe once and in contiguous pieces: rank r uploads rows
         [r*M/G, (r+1)*M/G) of the activations over its own link, the row slices are all-gathered on the devices
-        (NCCL over NVLink), and every rank computes its column block row chunk by row chunk. delivery="rows"
-        (default): the GEMM epilogue stores each row of a chunk into the exchange buffer of the rank that owns the
-        row (an all-to-all over NVLink written by the epilogue), a rank barrier completes the chunk and every rank
-        downloads the contiguous full-width rows it owns while the next chunk is computed
-        (duq4_linear_w4a4_from_fp16_to_host_rows). delivery="columns": every rank downloads its own [M, N/G]
-        column block into its column slice of `out_host` (duq4_linear_w4a4_from_fp16_to_host): no exchange, but
-        the ranks' writes interleave within every host row, which the host takes at about half the rate.
+        (NCCL over NVLink), and every rank computes its column block row chunk by row chunk. delivery="columns"
+        (default): every rank downloads its own [M, N/G] column block into its column slice of `out_host`
+        (duq4_linear_w4a4_from_fp16_to_host); the ranks' writes interleave within every host row. delivery="rows":
+        the GEMM epilogue stores each row of a chunk into the exchange buffer of the rank that owns the row (an
+        all-to-all over NVLink written by the epilogue), a rank barrier completes the chunk and every rank downloads
+        the contiguous full-width rows it owns while the next chunk is computed
+        (duq4_linear_w4a4_from_fp16_to_host_rows). Measured on 4 and 8 GPUs the two deliver at the same rate: the
+        host's aggregate write rate is the limit, not the interleaving.
         One rank: upload, arithmetic and download pipelined by the host-buffer entry point. The result is
         complete once every rank's stream has finished (synchronize, then a host barrier). x_host fp16 [M, K];
         out_host fp16 [M, n_out] row-major."""
@@ -339,8 +340,10 @@ class ColumnParallelLinear4bit(torch.nn.Module):
     def forward(self, x: torch.Tensor, gather: str = "nccl"):
         """gather="nccl": compute the local block, then one NCCL all-gather (+ re-layout copy).
         gather="fused": the kernel's epilogue writes the block into every rank's result buffer over
-        NVLink (one multicast store per row segment where the switch offers a multicast mapping, else one
-        store per peer; gather="fused_peer" forces the latter; gather="copy": the epilogue writes the local buffer only
+        NVLink: one plain store per peer up to 4 ranks, one multicast store per row segment through the switch from
+        8 ranks on, where the switch offers a multicast mapping (measured: a rank's ingress limits the step at 2 and 4
+        GPUs and multicast adds the rank's own block to it; at 8 its egress does, which multicast cuts eightfold);
+        gather="fused_peer" / "fused_multicast" force one or the other; gather="copy": the epilogue writes the local buffer only
         and copy engines push row chunks to the peers while the next chunk is computed); two device-side barriers
         bracket the launch (peers finished reading
         the previous result / everybody finished writing this one). The returned tensor is a view
@@ -375,7 +378,7 @@ class ColumnParallelLinear4bit(torch.nn.Module):
                            L.current_stream())
             peer.barrier()
             full = peer.buf
-        elif gather in ("fused", "fused_peer"):
+        elif gather in ("fused", "fused_peer", "fused_multicast"):
             M = x2d.shape[0]
             if self._peer is None:
                 self._peer = {}
@@ -385,7 +388,7 @@ class ColumnParallelLinear4bit(torch.nn.Module):
                 # alternates between a few token counts neither re-allocates (a collective rendezvous) nor
                 # frees memory a slower rank may still be storing into
                 peer = self._peer[(M, gather)] = PeerOutput(M, self.n_out, x2d.device, self.group,
-                                                            use_multicast=(gather == "fused"))
+                                                            use_multicast=(gather == "fused_multicast" or (gather == "fused" and self.world >= 8)))
             peer.barrier()
             self.local_forward(x2d, peer)
             peer.barrier()

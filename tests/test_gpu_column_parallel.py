@@ -37,7 +37,8 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
                                                    zc2 if mode == "asym_dual" else None, bias)
         y = layer(x)
         torch.cuda.synchronize()
-        y_fused = layer(x, gather="fused").clone()   # epilogue stores (multicast where offered) instead of the collective
+        y_fused = layer(x, gather="fused").clone()   # epilogue stores instead of the collective
+        y_mc = layer(x, gather="fused_multicast").clone()   # one multimem.st per row segment where the switch offers a multicast mapping
         y_fused2 = layer(x, gather="fused").clone()  # reuse of the shared buffer
         y_peer = layer(x, gather="fused_peer").clone()   # one plain store per peer
         y_copy = layer(x, gather="copy").clone()         # local epilogue + copy-engine peer copies per row chunk
@@ -51,7 +52,7 @@ def _worker(rank, world, port, mode, M, N, K, tmp):
         y1 = single(x)
         torch.cuda.synchronize()
         ok = torch.equal(y.view(torch.int16), y1.view(torch.int16)) and tuple(y.shape) == (M, N)
-        ok = ok and torch.equal(y_fused.view(torch.int16), y1.view(torch.int16))
+        ok = ok and torch.equal(y_fused.view(torch.int16), y1.view(torch.int16)) and torch.equal(y_mc.view(torch.int16), y1.view(torch.int16))
         ok = ok and torch.equal(y_fused2.view(torch.int16), y1.view(torch.int16))
         ok = ok and torch.equal(y_peer.view(torch.int16), y1.view(torch.int16)) and status.value == 0
         ok = ok and torch.equal(y_copy.view(torch.int16), y1.view(torch.int16)) and torch.equal(y_copy2.view(torch.int16), y1.view(torch.int16))
