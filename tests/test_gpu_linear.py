@@ -382,6 +382,48 @@ def test_full_size_property_prefill(env):
     assert np.array_equal(C[idx].cpu().numpy(), sub)
 
 
+@pytest.mark.parametrize("M", [4096, 512])
+def test_full_size_headline_route_equals_packed_route(env, M):
+    """The route bench.py times at the benchmark size (K=8192, N=28672; 4096 tokens, and 512 where the last round of
+    tiles is split along K over eight CTA pairs): fused quantizer to tensor-core-ready int8 codes, weights pre-laid-out
+    to int8, CTA-pair GEMM with the K-split. Its int32 accumulators must equal those of duq4_matmul_4bit on the packed
+    codes of the same tokens in every one of the M x N elements, and their row sums must equal codes * (sum of the
+    weight rows) computed in fp64 from the packed tensors."""
+    torch, L, o = env
+    N, K = 28672, 8192
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = (torch.randn((M, K), device="cuda", generator=g) * (1 + 19 * (torch.rand(K, device="cuda", generator=g) < 0.01))).half()
+    qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    st = L.current_stream()
+    qa = torch.empty((M, K // 2), dtype=torch.uint8, device="cuda"); s_p = torch.empty(M, dtype=torch.float16, device="cuda")
+    a8 = torch.empty((M, K), dtype=torch.int8, device="cuda"); s_8 = torch.empty(M, dtype=torch.float16, device="cuda")
+    L.call("duq4_quantize_sym_fused", L.ptr(x), M, K, 1.0, L.ptr(qa), L.ptr(s_p), st)
+    L.call("duq4_quantize_fused_i8", L.MODE_SYM, L.ptr(x), M, K, 1.0, L.ptr(a8), L.ptr(s_8), None, None, None, st)
+    w8 = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    L.call("duq4_weight_prelayout_i8", L.ptr(qw), N, K, L.ptr(w8), st)
+    sk = torch.empty(L.cdll.duq4_gemm_split_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    C = torch.full((M, N), -7, dtype=torch.int32, device="cuda"); C_ref = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(L.make_epilogue("none")), None, L.ptr(C), L.ptr(sk), sk.numel(), st)
+    L.call("duq4_matmul_4bit", L.ptr(qa), L.ptr(qw), M, N, K, L.ptr(C_ref), st)
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert torch.equal(s_p.view(torch.int16), s_8.view(torch.int16))
+    assert torch.equal(C, C_ref)
+
+    def unpack(q):
+        lo = (q & 0xF).to(torch.int16); hi = (q >> 4).to(torch.int16)
+        lo = torch.where(lo >= 8, lo - 16, lo); hi = torch.where(hi >= 8, hi - 16, hi)
+        return torch.stack([lo, hi], -1).reshape(q.shape[0], -1)
+
+    wsum = torch.zeros(K, dtype=torch.float64, device="cuda")
+    for i in range(0, N, 4096):
+        wsum += unpack(qw[i:i + 4096]).to(torch.float64).sum(0)
+    want = torch.zeros(M, dtype=torch.float64, device="cuda")
+    for i in range(0, M, 1024):
+        want[i:i + 1024] = unpack(qa[i:i + 1024]).to(torch.float64) @ wsum
+    assert torch.equal(C.to(torch.float64).sum(1), want)
+
+
 @pytest.mark.parametrize("mode", ["sym", "sym_dual", "asym", "asym_dual"])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (130, 264, 192), (512, 1024, 2048),
                                    # up to 128 tokens: narrow-tile launches (tile width picked by N: 160 / 128 / 96 / 64)
