@@ -209,7 +209,7 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------
-def time_decode(torch, L, device, peaks, Ms=(1, 16)):
+def time_decode(torch, L, device, peaks, Ms=(1, 2, 4, 8, 16)):
     """us/layer at M <= 16 tokens on the Llama-2-7B shapes with COLD weights: a CUDA graph walks over enough
     distinct weight buffers to exceed L2 (126 MB) before reusing one. Two kinds of rows:
       what = "layer"             the whole W4A4 linear, fp16 activations in -> fp16 out, through
@@ -217,7 +217,9 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
       what = "gemv+dequant only" pre-quantized codes in -> fp16 out through duq4_linear_w4a4 (the quantizer is NOT
                                  in the timed region)
     each with the serving options on (weights declared static so consecutive layers overlap their weight
-    streaming, next-layer L2 hint) and, for the layer rows, also with both off ("plain")."""
+    streaming, next-layer L2 hint) and, for the layer rows, also with both off ("plain"). 1 and 16 tokens get all
+    three rows, 2 / 4 / 8 tokens the first. us_per_layer is the median over ten graph replays of >= 100 layers each;
+    p10 / p90 are given beside it."""
     out = []
     for (K, N) in DECODE_SHAPES:
         wbytes = N * K // 2
@@ -232,7 +234,8 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
             ws_bytes = L.cdll.duq4_linear_from_fp16_workspace_bytes(M, K)
             ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=device)
             passes = -(-100 // ncopy)   # at least 100 layer invocations per graph replay
-            for what, serving in (("layer", True), ("layer", False), ("gemv+dequant only", True)):
+            kinds = (("layer", True), ("layer", False), ("gemv+dequant only", True)) if M in (1, 16) else (("layer", True),)
+            for what, serving in kinds:
                 if os.environ.get("DUQ4_BENCH_NO_PDL") and serving:
                     continue
                 # one epilogue per layer: each names the NEXT layer's weights (L2 prefetch hint), as a model
@@ -262,21 +265,25 @@ def time_decode(torch, L, device, peaks, Ms=(1, 16)):
                     for _ in range(3):
                         g.replay()
                     torch.cuda.synchronize()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     reps = 10
-                    e0.record(s)
-                    for _ in range(reps):
+                    evs = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+                    evs[0].record(s)
+                    for i in range(reps):
                         g.replay()
-                    e1.record(s)
+                        evs[i + 1].record(s)
                     torch.cuda.synchronize()
                 L.cdll.duq4_set_static_weights(prev)
-                us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy * passes)
+                per = sorted(evs[i].elapsed_time(evs[i + 1]) * 1e3 / (ncopy * passes) for i in range(reps))
+                us = 0.5 * (per[reps // 2 - 1] + per[reps // 2])
                 gbs = wbytes / (us * 1e-6) / 1e9
                 out.append({"K": K, "N": N, "M": M, "what": what, "options": "static weights + next-layer hint" if serving else "plain",
-                            "us_per_layer": round(us, 3), "weight_GBps": round(gbs, 1),
+                            "us_per_layer": round(us, 3), "us_p10": round(per[1], 3), "us_p90": round(per[-2], 3), "weight_GBps": round(gbs, 1),
                             "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
                             "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4), "cold_weight_buffers": ncopy,
-                            "layers_per_graph": ncopy * passes, "launches_per_layer": 1})
+                            "layers_per_graph": ncopy * passes,
+                            # fp16 tokens in: one launch at one token (the kernel quantizes the token itself), else the
+                            # fused quantizer + the small-M kernel, the second launched programmatically behind the first
+                            "launches_per_layer": 2 if (what == "layer" and M > 1) else 1})
                 del g
         del W
     return out
