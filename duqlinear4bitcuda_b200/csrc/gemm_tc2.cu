@@ -57,15 +57,20 @@ constexpr int kStageOutWarp = 32 * 144;
 // in-kernel unpack.
 template <bool APK, bool GU = false, bool WI8 = false>
 struct Cfg2 {
-    static constexpr int EPI = GU ? 8 : 4;    // epilogue warps
-    static constexpr int UWN = GU ? 4 : 8;    // unpack warps
+    // Epilogue warps / unpack warps. A tile's epilogue on FOUR warps (one per TMEM lane quadrant, alone on its
+    // scheduler, every TMEM load -> dequant -> store chain exposed) takes 13 us -- measured with one-k-step problems --
+    // against 17.7 us of MMA work per tile at K = 8192 and 8.8 us at K = 4096: hidden at the first, the limit at the
+    // second. Where the unpack warps have little or nothing to do (gate/up variant, pre-laid-out weights) eight
+    // warps share the epilogue, two per quadrant, half of the tile's columns each.
+    static constexpr int EPI = (GU || WI8) ? 8 : 4;
+    static constexpr int UWN = (GU || WI8) ? 4 : 8;
     static constexpr int kColTerms = EPI * 3 * BN * 2;
     // Ring depths. A packed stage is refilled by a TMA copy that takes about a microsecond to land
     // (L2 / HBM latency) while a k-step of MMA work takes 0.3-0.4 us, so the packed ring has to
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
     static constexpr int NPK = WI8 ? 1 : (GU ? (APK ? 3 : 5) : (APK ? 4 : 5));
-    static constexpr int NUP = WI8 ? (GU ? 5 : 6) : ((APK || GU) ? 4 : 5);
+    static constexpr int NUP = WI8 ? 5 : ((APK || GU) ? 4 : 5);
     static constexpr int kPackedStage = WI8 ? 0 : (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB; none without an unpack
     static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
@@ -428,6 +433,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t n0 = tn * bn;
             EpiParams pb = a.epi;
             __half *cs = colterms + (warp - 2) * 3 * BN, *cz = cs + BN, *cb = cz + BN;
+            // with eight epilogue warps the two warps of a lane quadrant take the chunks [0, 8) and [8, end) of the tile
+            const int wch_lo = (EPI == 8 && warp >= 6) ? 8 : 0, wch_hi = (EPI == 8 && warp < 6) ? 8 : -1;
             if (GU) {
                 // per-channel terms of the tile's 128 gate columns, then of its 128 up columns
                 __syncwarp();
@@ -442,7 +449,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 __syncwarp();
             } else {
-                epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb);
+                epi_stage_colterms<BN>(a, pb, b, n0, lane, cs, cz, cb, wch_lo * 16, wch_hi < 0 ? BN : wch_hi * 16);
             }
             if (!(ok = mbar_wait(acc_full(buf), aph, abortp, &g_tc2_status, 4))) break;
             tc_fence_after();
@@ -451,7 +458,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                        stage_out + (warp - 2) * kStageOutWarp, ((warp - 2) >> 2) * 4, ((warp - 2) >> 2) * 4 + 4);
             else if (w.sk_rank < 0)
                 epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                         stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4));
+                                         stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), tc::SplitK(), wch_lo, wch_hi);
             else {
                 // K-split tile: the G pairs of the group hold partial sums over their K ranges. Reduce-scatter through
                 // L2: the first R = min(G, 4) pairs each own a range of the tile's 16-column chunks (multiples of four
@@ -471,7 +478,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 p1.out = slot0 + ((size_t)r * 2 + rank) * slab;
                 p1.keep_b = own_b; p1.keep_e = own_e;
                 epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                         stage_out + (warp - 2) * kStageOutWarp, nch, p1);
+                                         stage_out + (warp - 2) * kStageOutWarp, nch, p1, wch_lo, wch_hi);
                 __threadfence();   // this lane's partial sums are visible device-wide before the arrival below
                 __syncwarp();
                 unsigned int *cw = a.sk_counters + w.sk_slot;
@@ -501,7 +508,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     p2.n = G; p2.skip = r; p2.stride = 2 * slab;
                     p2.ch_b = own_b; p2.ch_e = own_e;
                     epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
-                                             stage_out + (warp - 2) * kStageOutWarp, nch, p2);
+                                             stage_out + (warp - 2) * kStageOutWarp, nch, p2, wch_lo, wch_hi);
                 }
             }
             tc_fence_before();

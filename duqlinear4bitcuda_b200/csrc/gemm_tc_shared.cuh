@@ -107,7 +107,8 @@ struct Args {
 // `pb` comes in as the launch's parameters and leaves adjusted to batch `b`.
 template <int BN>
 __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb, uint32_t b, uint32_t n0, int lane, __half *cs,
-                                                   __half *cz, __half *cb) {
+                                                   __half *cz, __half *cb, int c_lo = 0, int c_hi = BN) {
+    // c_lo / c_hi: the tile columns the calling warp will use (a warp that shares a tile by columns stages its part only)
     const int mode = a.epi.mode;
     __syncwarp();  // previous tile's readers are done
     if (mode != DUQ4_MODE_NONE) {
@@ -117,14 +118,24 @@ __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb,
         if (pb.s_col2) pb.s_col2 += co;
         if (pb.z_col2) pb.z_col2 += co;
         if (pb.bias) pb.bias += co;
-        for (int c = lane; c < BN; c += 32) {
-            uint32_t n = n0 + c;
-            ColTerms t;
-            t.s = t.z = t.b = __ushort_as_half(0);
-            if (n < a.N) t = load_col_terms(pb, n);
-            cs[c] = t.s;
-            cz[c] = t.z;
-            cb[c] = t.b;
+        // all loads first, then the stores: with a store between them every load would wait for the one before it
+        // (a chain of BN/32 trips to L2 per tile, on the critical path of a tile's epilogue)
+        ColTerms t[BN / 32];
+#pragma unroll
+        for (int i = 0; i < BN / 32; ++i) {
+            const int c = lane + 32 * i;
+            const uint32_t n = n0 + c;
+            t[i].s = t[i].z = t[i].b = __ushort_as_half(0);
+            if (c >= c_lo && c < c_hi && n < a.N) t[i] = load_col_terms(pb, n);
+        }
+#pragma unroll
+        for (int i = 0; i < BN / 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c >= c_lo && c < c_hi) {
+                cs[c] = t[i].s;
+                cz[c] = t[i].z;
+                cb[c] = t[i].b;
+            }
         }
     }
     __syncwarp();
@@ -150,7 +161,10 @@ struct SplitK {
 template <int BN, bool STAGED>
 __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &pb, uint32_t b, uint32_t m_base, uint32_t n0,
                                    uint32_t tmem_acc, int quad, int lane, uint32_t shift, const __half *cs,
-                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16, const SplitK sk = SplitK()) {
+                                   const __half *cz, const __half *cb, uint8_t *stg, int nch = BN / 16, const SplitK sk = SplitK(),
+                                   int ch_lo = 0, int ch_hi = -1) {
+    // ch_lo / ch_hi: the chunks [ch_lo, ch_hi) of the tile that the calling warp handles (a multiple of four chunks at the
+    // lower end; ch_hi < 0: up to the tile's end) -- several warps of one TMEM lane quadrant can share a tile by columns
     // nch: 16-column chunks of the accumulator that belong to this tile (tiles narrower than BN)
     const uint32_t n_end = min(a.N, n0 + 16u * (uint32_t)nch);   // first column not written by this tile
     const int mode = a.epi.mode;
@@ -182,14 +196,33 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
     __half *const mc = (STAGED && vec_ok && (reinterpret_cast<uintptr_t>(pb.mc_out) & 15u) == 0) ? pb.mc_out : nullptr;
     const bool avec_ok = ((a.N & 3u) == 0) && ((reinterpret_cast<uintptr_t>(a.acc_out) & 15u) == 0);   // owner buffers: alignment checked by the host
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
-    const int ch_first = sk.out ? 0 : sk.ch_b, ch_last = (sk.out || sk.ch_e < 0 || sk.ch_e > nch) ? nch : sk.ch_e;
-#pragma unroll 1
-    for (int ch = ch_first; ch < ch_last; ++ch) {
-        if (sk.out && ch >= sk.keep_b && ch < sk.keep_e) continue;   // this pair reduces these chunks itself
-        uint32_t v[16];
+    const int w_hi = (ch_hi < 0 || ch_hi > nch) ? nch : ch_hi;
+    const int ch_first = sk.out ? ch_lo : max(ch_lo, sk.ch_b), ch_last = (sk.out || sk.ch_e < 0) ? w_hi : min(w_hi, sk.ch_e);
+    // first chunk at or after `c` that this call handles (phase 1 of a K-split skips the chunks the pair reduces itself)
+    auto next_chunk = [&](int c) {
+        if (sk.out && c >= sk.keep_b && c < sk.keep_e) c = sk.keep_e;
+        return c < ch_last ? c : ch_last;
+    };
+    // the TMEM load of a chunk is issued while the chunk before it is processed
+    uint32_t vn[16];
+    int ch = next_chunk(ch_first);
+    if (ch < ch_last) {
         __syncwarp();  // tcgen05.ld is warp-collective
-        tmem_ld16(taddr + ch * 16, v);
+        tmem_ld16(taddr + ch * 16, vn);
+    }
+#pragma unroll 1
+    for (; ch < ch_last; ch = next_chunk(ch + 1)) {
+        uint32_t v[16];
         tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = vn[j];
+        {
+            const int nx = next_chunk(ch + 1);
+            if (nx < ch_last) {
+                __syncwarp();
+                tmem_ld16(taddr + nx * 16, vn);
+            }
+        }
         const uint32_t c0 = ch * 16;
         if (sk.out) {   // K-split tile, phase 1: raw accumulators to the scratch slab
             int4 *dst = reinterpret_cast<int4 *>(sk.out) + ((size_t)(ch * 4 + quad) * 4) * 32 + lane;
