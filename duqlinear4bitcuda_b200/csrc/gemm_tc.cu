@@ -444,6 +444,7 @@ int gemm_tc_launch(int mode, const void *A, const void *B, uint32_t M, uint32_t 
     a.out = (__half *)out;
     a.acc_out = acc_out;
     a.tiles_m = cdiv(M, BM);
+    a.acc_fits_22 = (uint64_t)K * (mode == MODE_I8 ? 16384u : 64u) <= (1u << 22) ? 1u : 0u;   // |term| <= 128 * 128 or 8 * 8
     // 256-wide tiles halve the A-operand shared-memory traffic per MMA; fall back to 128
     // when that would leave most SMs without a tile.
     const bool wide = (uint64_t)a.tiles_m * cdiv(N, 256) * batch >= 120 || N > 128 * 148;

@@ -635,6 +635,7 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     a.out = (__half *)out;
     a.acc_out = acc_out;
     a.tiles_m = cdiv(M, 256);
+    a.acc_fits_22 = (uint64_t)K * 64 <= (1u << 22) ? 1u : 0u;   // |int4 x int4| <= 64 per term
     a.gate_up = gate_up;   // N is then the width I of h; W has 2*I rows, tiles are 256 rows x 128 hidden channels
     // 256-wide tiles for peer output too: a 224-wide tile starts on a 448-byte boundary, so its 128-byte row
     // segments straddle 128-byte lines of the destination -- harmless in local HBM (whole 32-byte sectors),

@@ -88,6 +88,7 @@ struct Args {
     uint32_t tiles_m, tiles_n;
     uint32_t bn;              // CTA-pair kernel only: accumulator columns per tile (multiple of 32, <= 256)
     uint32_t a_rows;          // rows of the A buffer the tensor map may read (>= M; the extra rows are never stored)
+    uint32_t acc_fits_22;     // 1 = every accumulator of this launch is at most 2^22 in magnitude (see dequant16)
     uint32_t gate_up;         // CTA-pair kernel only: 0, or I = width of a SiLU-gated gate/up projection (W has 2*I rows)
     // CTA-pair kernel only, K-split of the last, partly filled round of tiles: the last sk_tiles tiles are each
     // computed by sk_group pairs (a K range each); the pairs exchange int32 partial tiles through sk_scratch and signal
@@ -144,6 +145,47 @@ __device__ __forceinline__ void epi_stage_colterms(const Args &a, EpiParams &pb,
 // One warp's 32 rows of a 128-row accumulator slab: TMEM -> (>> shift) -> optional int32 store ->
 // fp16 dequant (+ bias) -> global / peer memory. `m_base` is the global row of the slab's first
 // row, `tmem_acc` the TMEM address (lane 0) of the accumulator's first column.
+// fp16 dequant of one row's 16 accumulators of a chunk, two columns per instruction: the reference arithmetic
+// (one rounding per fp16 operation, explicit .rn forms so that nothing is contracted into an fma), straight-line code
+// for the compiler to interleave -- an epilogue warp is alone on its scheduler, so instruction-level parallelism is all
+// the latency hiding it gets. ASYM / BIAS are compile-time so that no per-element branch splits the block.
+// FASTCVT: |accumulator| <= 2^22, so int -> float is an integer add and a float subtract (exact) instead of the
+// quarter-rate conversion instruction; float -> fp16 then rounds once, as the direct int -> fp16 conversion does.
+template <bool ASYM, bool BIAS, bool FASTCVT>
+__device__ __forceinline__ void dequant16(const uint32_t (&v)[16], __half sr, __half zr, const __half *cs, const __half *cz,
+                                          const __half *cb, __half2 (&o)[8]) {
+    const __half2 sr2 = __half2half2(sr), zr2 = __half2half2(zr);
+    const uint4 s4a = *reinterpret_cast<const uint4 *>(cs), s4b = *reinterpret_cast<const uint4 *>(cs + 8);
+    const __half2 *s2a = reinterpret_cast<const __half2 *>(&s4a), *s2b = reinterpret_cast<const __half2 *>(&s4b);
+    uint4 z4a = make_uint4(0, 0, 0, 0), z4b = z4a, b4a = z4a, b4b = z4a;
+    if (ASYM) { z4a = *reinterpret_cast<const uint4 *>(cz); z4b = *reinterpret_cast<const uint4 *>(cz + 8); }
+    if (BIAS) { b4a = *reinterpret_cast<const uint4 *>(cb); b4b = *reinterpret_cast<const uint4 *>(cb + 8); }
+    const __half2 *z2a = reinterpret_cast<const __half2 *>(&z4a), *z2b = reinterpret_cast<const __half2 *>(&z4b);
+    const __half2 *b2a = reinterpret_cast<const __half2 *>(&b4a), *b2b = reinterpret_cast<const __half2 *>(&b4b);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        __half2 e;
+        if (FASTCVT) {
+            const float f0 = __int_as_float(0x4B400000 + (int)v[2 * p]) - 12582912.0f;
+            const float f1 = __int_as_float(0x4B400000 + (int)v[2 * p + 1]) - 12582912.0f;
+            e = __floats2half2_rn(f0, f1);
+        } else {
+            e = __halves2half2(__int2half_rn((int)v[2 * p]), __int2half_rn((int)v[2 * p + 1]));
+        }
+        const __half2 sc = p < 4 ? s2a[p] : s2b[p - 4];
+        const __half2 ss = __hmul2_rn(sr2, sc);
+        __half2 val;
+        if (ASYM) {
+            const __half2 zc = p < 4 ? z2a[p] : z2b[p - 4];
+            val = __hmul2_rn(ss, __hsub2_rn(__hsub2_rn(e, zr2), zc));
+        } else {
+            val = __hmul2_rn(ss, e);
+        }
+        if (BIAS) val = __hadd2_rn(val, p < 4 ? b2a[p] : b2b[p - 4]);
+        o[p] = val;
+    }
+}
+
 // K-split of a tile over a group of CTA pairs (see the pair kernel): what one call of epi_store_tile does with the
 // partial-sum slabs. A slab (128 x BN int32) is private to the warps that exchange it -- the same lane quadrant of
 // the same CTA of each pair of the group -- so it is laid out for their access pattern: element (chunk ch, group of
@@ -293,15 +335,19 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
             }
         }
         if (mode == DUQ4_MODE_NONE) continue;
-        __align__(16) __half o[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            __half e = __int2half_rn((int)v[j]);
-            __half ss = __hmul_rn(sr, cs[c0 + j]);
-            __half val = asym ? __hmul_rn(ss, __hsub_rn(__hsub_rn(e, zr), cz[c0 + j])) : __hmul_rn(ss, e);
-            if (has_bias) val = __hadd_rn(val, cb[c0 + j]);
-            o[j] = val;
+        __align__(16) __half2 o2[8];
+        {
+            const __half *csp = cs + c0, *czp = cz + c0, *cbp = cb + c0;
+            const bool fast = a.acc_fits_22 != 0;
+            if (asym) {
+                if (has_bias) { if (fast) dequant16<true, true, true>(v, sr, zr, csp, czp, cbp, o2); else dequant16<true, true, false>(v, sr, zr, csp, czp, cbp, o2); }
+                else          { if (fast) dequant16<true, false, true>(v, sr, zr, csp, czp, cbp, o2); else dequant16<true, false, false>(v, sr, zr, csp, czp, cbp, o2); }
+            } else {
+                if (has_bias) { if (fast) dequant16<false, true, true>(v, sr, zr, csp, czp, cbp, o2); else dequant16<false, true, false>(v, sr, zr, csp, czp, cbp, o2); }
+                else          { if (fast) dequant16<false, false, true>(v, sr, zr, csp, czp, cbp, o2); else dequant16<false, false, false>(v, sr, zr, csp, czp, cbp, o2); }
+            }
         }
+        const __half *o = reinterpret_cast<const __half *>(o2);
         if (!STAGED) {
             if (!row_ok || !col_any) continue;
 #pragma unroll
@@ -327,6 +373,20 @@ __device__ __forceinline__ void epi_store_tile(const Args &a, const EpiParams &p
         __syncwarp();
         const uint32_t g0 = (uint32_t)(ch >> 2) * 64 + (lane & 7) * 8;   // first column of this lane's 8 (tile-relative)
         const bool seg_full = n0 + g0 + 8 <= n_end;
+        if (ob.n == 1 && !mc && vec_ok && pb.out_rows_per_owner == 0 && m_base + quad * 32 + 32 <= a.M && n0 + (uint32_t)(ch >> 2) * 64 + 64 <= n_end &&
+            (ch & 3) == 3) {
+            // the common case -- one destination, a whole 32 x 64 block inside the matrix: all eight reads, then all eight
+            // stores, no per-segment decisions
+            uint4 seg[8];
+#pragma unroll
+            for (int it = 0; it < 8; ++it) seg[it] = *reinterpret_cast<const uint4 *>(stg + (it * 4 + (lane >> 3)) * 144 + (lane & 7) * 16);
+            __half *dst = ob.base[0] + ((size_t)b * a.M + m_base + quad * 32 + (lane >> 3)) * pb.ldo + n0 + g0;
+            const size_t step = (size_t)4 * pb.ldo;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) *reinterpret_cast<uint4 *>(dst + it * step) = seg[it];
+            __syncwarp();   // the block is free for the next 64 columns
+            continue;
+        }
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const uint32_t r = it * 4 + (lane >> 3);
