@@ -178,15 +178,20 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
         if (pi < ob.n) obits |= reinterpret_cast<uintptr_t>(ob.base[pi]);
     const bool vec_ok = ((pb.ldo & 7u) == 0) && ((obits & 15u) == 0);
     const uint32_t taddr = tmem_acc + ((uint32_t)(quad * 32) << 16);
-    // Dequant of two neighbouring columns at a time with the packed fp16 instructions: every lane of
-    // hmul2 / hsub2 / hadd2 rounds like the scalar _rn form, so the values equal the plain epilogue's.
-    const __half2 sr2 = __half2half2(sr), zr2 = __half2half2(zr);
-    auto deq2 = [&](uint32_t raw0, uint32_t raw1, int c) {   // c even
-        const __half2 e = __halves2half2(__int2half_rn(((int)raw0) >> 8), __int2half_rn(((int)raw1) >> 8));   // accumulators are 256 x the true sums
-        const __half2 ss = __hmul2_rn(sr2, *reinterpret_cast<const __half2 *>(cs + c));
-        __half2 val = asym ? __hmul2_rn(ss, __hsub2_rn(__hsub2_rn(e, zr2), *reinterpret_cast<const __half2 *>(cz + c))) : __hmul2_rn(ss, e);
-        if (has_bias) val = __hadd2_rn(val, *reinterpret_cast<const __half2 *>(cb + c));
-        return val;
+    // Dequant with the plain epilogue's routine (two columns per instruction, every lane of hmul2 / hsub2 / hadd2 rounds
+    // like the scalar _rn form, so the values equal the plain epilogue's), one call for the chunk's 16 gate columns and
+    // one for its 16 up columns.
+    auto deq16 = [&](uint32_t (&v)[16], int c, __half2 (&o2)[8]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = (uint32_t)(((int)v[j]) >> 8);   // accumulators are 256 x the true sums
+        const bool fast = a.acc_fits_22 != 0;
+        if (asym) {
+            if (has_bias) { if (fast) tc::dequant16<true, true, true>(v, sr, zr, cs + c, cz + c, cb + c, o2); else tc::dequant16<true, true, false>(v, sr, zr, cs + c, cz + c, cb + c, o2); }
+            else          { if (fast) tc::dequant16<true, false, true>(v, sr, zr, cs + c, cz + c, cb + c, o2); else tc::dequant16<true, false, false>(v, sr, zr, cs + c, cz + c, cb + c, o2); }
+        } else {
+            if (has_bias) { if (fast) tc::dequant16<false, true, true>(v, sr, zr, cs + c, cz + c, cb + c, o2); else tc::dequant16<false, true, false>(v, sr, zr, cs + c, cz + c, cb + c, o2); }
+            else          { if (fast) tc::dequant16<false, false, true>(v, sr, zr, cs + c, cz + c, cb + c, o2); else tc::dequant16<false, false, false>(v, sr, zr, cs + c, cz + c, cb + c, o2); }
+        }
     };
 #pragma unroll 1
     for (int ch = ch_begin; ch < ch_end; ++ch) {   // 16-channel chunks of the tile's 128 hidden channels (a multiple of 4 of them)
@@ -197,11 +202,24 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
         tmem_ld_wait();
         const int c0 = ch * 16;
         __align__(16) __half o[16];
+        __half2 g2[8], u2[8];
+        deq16(vg, c0, g2);
+        deq16(vu, 128 + c0, u2);
+        // h = half(half(silu(g)) * u) as silu_mul_one forms it, in stages over the 16 elements so that the sixteen
+        // exponentials (branch-free) can be interleaved by the compiler before the divides (one block each)
+        float xs[16], ds[16];
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-            const __half2 g = deq2(vg[j], vg[j + 1], c0 + j), u = deq2(vu[j], vu[j + 1], 128 + c0 + j);
-            o[j] = silu_mul_one(__low2half(g), __low2half(u));
-            o[j + 1] = silu_mul_one(__high2half(g), __high2half(u));
+        for (int p = 0; p < 8; ++p) {
+            const float2 x2 = __half22float2(g2[p]);
+            xs[2 * p] = x2.x;
+            xs[2 * p + 1] = x2.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) ds[j] = 1.0f + expf(-xs[j]);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const __half2 s2 = __floats2half2_rn(__fdiv_rn(xs[2 * p], ds[2 * p]), __fdiv_rn(xs[2 * p + 1], ds[2 * p + 1]));
+            *reinterpret_cast<__half2 *>(&o[2 * p]) = __hmul2_rn(s2, u2[p]);
         }
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32) = *reinterpret_cast<const uint4 *>(&o[0]);
         *reinterpret_cast<uint4 *>(stg + lane * 144 + (ch & 3) * 32 + 16) = *reinterpret_cast<const uint4 *>(&o[8]);
@@ -436,16 +454,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // with eight epilogue warps the two warps of a lane quadrant take the chunks [0, 8) and [8, end) of the tile
             const int wch_lo = (EPI == 8 && warp >= 6) ? 8 : 0, wch_hi = (EPI == 8 && warp < 6) ? 8 : -1;
             if (GU) {
-                // per-channel terms of the tile's 128 gate columns, then of its 128 up columns
+                // per-channel terms of the tile's 128 gate columns, then of its 128 up columns; this warp's hidden
+                // channels only, all loads before the first store (see epi_stage_colterms)
                 __syncwarp();
-                for (int c = lane; c < BN; c += 32) {
+                const int hc_lo = ((warp - 2) >> 2) * 64, hc_hi = hc_lo + 64;
+                ColTerms t[BN / 32];
+#pragma unroll
+                for (int i = 0; i < BN / 32; ++i) {
+                    const int c = lane + 32 * i;
                     const uint32_t j = tn * 128u + (uint32_t)(c & 127);
-                    ColTerms t;
-                    t.s = t.z = t.b = __ushort_as_half(0);
-                    if (j < a.gate_up) t = load_col_terms(pb, (c < 128 ? 0u : a.gate_up) + j);
-                    cs[c] = t.s;
-                    cz[c] = t.z;
-                    cb[c] = t.b;
+                    t[i].s = t[i].z = t[i].b = __ushort_as_half(0);
+                    if ((c & 127) >= hc_lo && (c & 127) < hc_hi && j < a.gate_up) t[i] = load_col_terms(pb, (c < 128 ? 0u : a.gate_up) + j);
+                }
+#pragma unroll
+                for (int i = 0; i < BN / 32; ++i) {
+                    const int c = lane + 32 * i;
+                    if ((c & 127) >= hc_lo && (c & 127) < hc_hi) {
+                        cs[c] = t[i].s;
+                        cz[c] = t[i].z;
+                        cb[c] = t[i].b;
+                    }
                 }
                 __syncwarp();
             } else {
