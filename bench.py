@@ -861,7 +861,7 @@ def run_ours(args):
                          "achieved": round(gemm_tops, 2), "peak": round(int8_peak, 1), "unit": "TOP/s",
                          "frac": round(gemm_tops / int8_peak, 4),
                          # dram read+write bytes per launch: ncu capture of this kernel at the bench's own size
-                         # (profiles/bench_launch_list_M4096_K8192_N28672.md: 349.2 MB read + 218.7 MB written), scaled
+                         # (the capture summarised under profiles/: 349.2 MB read + 218.7 MB written), scaled
                          # by this rank's share of the columns when the layer is sharded
                          "traffic": round(567.9e6 * Ns / N),
                          "traffic_note": "ncu dram__bytes_read+write of one full-size launch (M=4096, K=8192, N=28672: 349.2 MB read + 218.7 MB "

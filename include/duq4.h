@@ -273,8 +273,8 @@ int duq4_linear_w4a4_preunpacked(const int8_t *A_i8, const uint8_t *W, uint32_t 
                                  uint32_t K, const duq4_epilogue *epi, void *out, int32_t *acc_out,
                                  void *stream);
 
-/* Weight pre-layout (optional, no reference counterpart; SURVEY of the design space: "one-off int8 pre-unpack of
- * W"): duq4_weight_prelayout_i8 turns packed weights W [N, K/2] into W_i8 [N, K] in the tensor-core-ready form of
+/* Weight pre-layout (optional, no reference counterpart: a one-off int8 pre-unpack of W):
+ * duq4_weight_prelayout_i8 turns packed weights W [N, K/2] into W_i8 [N, K] in the tensor-core-ready form of
  * duq4_quantize_fused_i8 (int8 = 16 * code, K permuted inside 128-blocks; K % 128 == 0; twice the bytes), once per
  * weight tensor. duq4_linear_w4a4_prelaid then runs the layer with BOTH operands in that form on the CTA-pair
  * tensor-core kernel with no in-kernel unpack (any M >= 1; DUQ4_ERR_DEVICE where CTA pairs cannot be scheduled).
