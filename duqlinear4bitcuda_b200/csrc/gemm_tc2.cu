@@ -337,12 +337,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         return false;
     };
+    // Tile order: row block fastest inside bands of a.band_rows row blocks, bands one after the other. Consecutive tiles
+    // -- the ones the pairs work on at the same time -- then share a few weight tiles and the activations of one band
+    // (16 row blocks of K = 8192: 33 MB), which stay in L2 beside the streaming weights and results; with all 32 row
+    // blocks of an 8192-token problem in one band the activations were evicted between column tiles.
+    const uint32_t kBandRows = a.band_rows;
     auto tile_coords = [&](uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
         const uint32_t per_b = a.tiles_m * a.tiles_n;
         b = tile / per_b;
         const uint32_t r = tile % per_b;
-        tn = r / a.tiles_m;
-        tm = r % a.tiles_m;
+        const uint32_t per_band = kBandRows * a.tiles_n;
+        const uint32_t band = r / per_band, rb = r % per_band;
+        const uint32_t rows_here = min(kBandRows, a.tiles_m - band * kBandRows);
+        tn = rb / rows_here;
+        tm = band * kBandRows + rb % rows_here;
     };
 
     if (warp == 0) {
@@ -664,6 +672,9 @@ static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_
     a.acc_out = acc_out;
     a.tiles_m = cdiv(M, 256);
     a.acc_fits_22 = (uint64_t)K * 64 <= (1u << 22) ? 1u : 0u;   // |int4 x int4| <= 64 per term
+    // row blocks per band of the tile order; measured on 8192 tokens: K = 8192 -> 3652 / 3806 / 3804 / 3616 TOPS with bands of
+    // 4 / 8 / 16 / 32, K = 28672 -> 3459 / 3552 / 3389 / 3301
+    a.band_rows = K > 16384 ? 8 : 16;
     a.gate_up = gate_up;   // N is then the width I of h; W has 2*I rows, tiles are 256 rows x 128 hidden channels
     // 256-wide tiles for peer output too: a 224-wide tile starts on a 448-byte boundary, so its 128-byte row
     // segments straddle 128-byte lines of the destination -- harmless in local HBM (whole 32-byte sectors),

@@ -88,6 +88,7 @@ struct Args {
     uint32_t tiles_m, tiles_n;
     uint32_t bn;              // CTA-pair kernel only: accumulator columns per tile (multiple of 32, <= 256)
     uint32_t a_rows;          // rows of the A buffer the tensor map may read (>= M; the extra rows are never stored)
+    uint32_t band_rows;       // CTA-pair kernel only: row blocks per band of the tile order (see the kernel)
     uint32_t acc_fits_22;     // 1 = every accumulator of this launch is at most 2^22 in magnitude (see dequant16)
     uint32_t gate_up;         // CTA-pair kernel only: 0, or I = width of a SiLU-gated gate/up projection (W has 2*I rows)
     // CTA-pair kernel only, K-split of the last, partly filled round of tiles: the last sk_tiles tiles are each
