@@ -382,6 +382,42 @@ def test_full_size_property_prefill(env):
     assert np.array_equal(C[idx].cpu().numpy(), sub)
 
 
+@pytest.mark.parametrize("M,N,K", [(8192, 512, 256), (4500, 520, 384), (2304, 256, 16512), (8192, 256, 128)])
+def test_banded_tile_order_covers_every_tile_once(env, M, N, K):
+    """Problems with more row blocks than one band of the CTA-pair kernel's tile order (16 row blocks; 8 when
+    K > 16384), ragged last bands included: the int32 accumulators of the packed route and of the pre-laid-out route
+    (with the K-split) must equal an fp32 matrix product of the unpacked codes (exact: every partial sum is an integer
+    below 2^24) in every element -- a tile computed twice or left out would show."""
+    torch, L, o = env
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    qa = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    qw = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    st = L.current_stream()
+
+    def unpack(q):
+        lo = (q & 0xF).to(torch.int16); hi = (q >> 4).to(torch.int16)
+        lo = torch.where(lo >= 8, lo - 16, lo); hi = torch.where(hi >= 8, hi - 16, hi)
+        return torch.stack([lo, hi], -1).reshape(q.shape[0], -1)
+
+    ai, wi = unpack(qa), unpack(qw)
+    want = (ai.float() @ wi.float().T).to(torch.int32)
+    C = torch.full((M, N), -7, dtype=torch.int32, device="cuda")
+    L.call("duq4_matmul_4bit", L.ptr(qa), L.ptr(qw), M, N, K, L.ptr(C), st)
+    torch.cuda.synchronize()
+    assert torch.equal(C, want)
+    # the pre-laid-out route: the same codes as tensor-core-ready int8 (16 * code, K permuted inside 128-blocks by the
+    # library's own re-layout of the packed tensor, which works on any packed [rows, K/2] tensor)
+    a8 = torch.empty((M, K), dtype=torch.int8, device="cuda"); w8 = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    L.call("duq4_weight_prelayout_i8", L.ptr(qa), M, K, L.ptr(a8), st)
+    L.call("duq4_weight_prelayout_i8", L.ptr(qw), N, K, L.ptr(w8), st)
+    sk = torch.empty(L.cdll.duq4_gemm_split_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    C2 = torch.full((M, N), -7, dtype=torch.int32, device="cuda")
+    L.call("duq4_linear_w4a4_prelaid", L.ptr(a8), L.ptr(w8), M, N, K, ctypes.byref(L.make_epilogue("none")), None, L.ptr(C2), L.ptr(sk), sk.numel(), st)
+    torch.cuda.synchronize()
+    assert tc_status(L) == 0
+    assert torch.equal(C2, want)
+
+
 @pytest.mark.parametrize("M", [4096, 512])
 def test_full_size_headline_route_equals_packed_route(env, M):
     """The route bench.py times at the benchmark size (K=8192, N=28672; 4096 tokens, and 512 where the last round of
