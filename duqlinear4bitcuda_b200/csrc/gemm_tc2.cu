@@ -55,8 +55,13 @@ constexpr int kStageOutWarp = 32 * 144;
 // the activations): both operands go straight from TMA into the MMA ring and the unpack warps have nothing to do.
 // Twice the weight bytes from HBM / L2, no shared-memory unpack traffic -- the measured alternative to the
 // in-kernel unpack.
-template <bool APK, bool GU = false, bool WI8 = false>
+// STG = the epilogue stages its fp16 rows through shared memory and stores 128-byte row segments (what crosses NVLink
+// well, and what the multicast and owner-routed stores need). A launch on pre-laid-out weights whose result stays on
+// this GPU runs without: each lane stores its own row's 32 bytes per chunk (whole sectors in local memory) and the
+// staging area pays for a sixth ring stage -- 98 vs 104 us at 512 tokens, 150 vs 155 at 1024, no difference from 2048 on.
+template <bool APK, bool GU = false, bool WI8 = false, bool STG = true>
 struct Cfg2 {
+    static_assert(STG || (WI8 && !GU), "only the plain kernel on pre-laid-out weights has an unstaged form");
     // Epilogue warps / unpack warps. A tile's epilogue on FOUR warps (one per TMEM lane quadrant, alone on its
     // scheduler, every TMEM load -> dequant -> store chain exposed) takes 13 us -- measured with one-k-step problems --
     // against 17.7 us of MMA work per tile at K = 8192 and 8.8 us at K = 4096: hidden at the first, the limit at the
@@ -70,9 +75,10 @@ struct Cfg2 {
     // cover ~3 k-steps of latency plus the stage being unpacked: with 3 stages the kernel ran at
     // (copy latency / 3) per k-step whatever the tile width.
     static constexpr int NPK = WI8 ? 1 : (GU ? (APK ? 3 : 5) : (APK ? 4 : 5));
-    static constexpr int NUP = WI8 ? 5 : ((APK || GU) ? 4 : 5);
+    static constexpr int NUP = WI8 ? (STG ? 5 : 6) : ((APK || GU) ? 4 : 5);
     static constexpr int kPackedStage = WI8 ? 0 : (APK ? BMH + BNH : BNH) * (BKE / 2);   // 16 / 8 KiB; none without an unpack
-    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + EPI * kStageOutWarp + 512;
+    static constexpr int kStageOut = STG ? EPI * kStageOutWarp : 0;
+    static constexpr int kSmem = 1024 + NUP * kUnpackedStage + NPK * kPackedStage + kColTerms + kStageOut + 512;
     static_assert(kSmem <= 232448, "exceeds the shared memory of a CTA");
 };
 
@@ -250,11 +256,11 @@ __device__ __forceinline__ void epi_store_tile_gate_up(const Args &a, const EpiP
     }
 }
 
-template <bool APK, bool GU, bool WI8>
+template <bool APK, bool GU, bool WI8, bool STG>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
     static_assert(!WI8 || !APK, "pre-laid-out weights go with int8 activations");
-    using C2 = Cfg2<APK, GU, WI8>;
+    using C2 = Cfg2<APK, GU, WI8, STG>;
     constexpr int NPK = C2::NPK, NUP = C2::NUP, kPackedStage = C2::kPackedStage;
     constexpr int EPI = C2::EPI, UW = C2::UWN, kColTerms = C2::kColTerms;
     extern __shared__ uint8_t smem_raw[];
@@ -269,7 +275,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t ct_off = NUP * kUnpackedStage + NPK * kPackedStage;
     __half *colterms = reinterpret_cast<__half *>(gbase + ct_off);
     uint8_t *stage_out = gbase + ct_off + kColTerms;
-    const uint32_t bar0 = base + ct_off + kColTerms + EPI * kStageOutWarp;
+    const uint32_t bar0 = base + ct_off + kColTerms + C2::kStageOut;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
     auto pk_empty = [&](int s) { return bar0 + 8u * (8 + s); };
     auto up_full = [&](int s) { return bar0 + 8u * (16 + s); };
@@ -493,7 +499,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 epi_store_tile_gate_up(a, pb, tm * 256 + rank * BMH, tn * 128u, tmem_base + buf * BN, quad, lane, cs, cz, cb,
                                        stage_out + (warp - 2) * kStageOutWarp, ((warp - 2) >> 2) * 4, ((warp - 2) >> 2) * 4 + 4);
             else if (w.sk_rank < 0)
-                epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                epi_store_tile<BN, STG>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                          stage_out + (warp - 2) * kStageOutWarp, (int)(bn >> 4), tc::SplitK(), wch_lo, wch_hi);
             else {
                 // K-split tile: the G pairs of the group hold partial sums over their K ranges. Reduce-scatter through
@@ -513,7 +519,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tc::SplitK p1;
                 p1.out = slot0 + ((size_t)r * 2 + rank) * slab;
                 p1.keep_b = own_b; p1.keep_e = own_e;
-                epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                epi_store_tile<BN, STG>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                          stage_out + (warp - 2) * kStageOutWarp, nch, p1, wch_lo, wch_hi);
                 __threadfence();   // this lane's partial sums are visible device-wide before the arrival below
                 __syncwarp();
@@ -543,7 +549,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     p2.add = slot0 + (size_t)rank * slab;
                     p2.n = G; p2.skip = r; p2.stride = 2 * slab;
                     p2.ch_b = own_b; p2.ch_e = own_e;
-                    epi_store_tile<BN, true>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
+                    epi_store_tile<BN, STG>(a, pb, b, tm * 256 + rank * BMH, n0, tmem_base + buf * BN, quad, lane, 8, cs, cz, cb,
                                              stage_out + (warp - 2) * kStageOutWarp, nch, p2, wch_lo, wch_hi);
                 }
             }
@@ -626,13 +632,13 @@ static uint32_t pick_tile_width(uint32_t tiles_m, uint32_t N, uint32_t batch, ui
 constexpr size_t kSkCounterBytes = 1024;
 size_t gemm_tc2_split_scratch_bytes() { return kSkCounterBytes + (size_t)148 / 2 * 256 * 256 * sizeof(int32_t); }
 
-template <bool APK, bool GU = false, bool WI8 = false>
+template <bool APK, bool GU = false, bool WI8 = false, bool STG = true>
 static int launch2(const void *A, const void *B, uint32_t M, uint32_t N, uint32_t K, uint32_t batch, const EpiParams &p,
                    void *out, int32_t *acc_out, cudaStream_t st, uint32_t gate_up = 0, bool cache_maps = true,
                    void *sk_scratch = nullptr, size_t sk_bytes = 0) {
     using namespace tc2;
-    constexpr int kSmem2 = Cfg2<APK, GU, WI8>::kSmem;
-    auto *kernel = gemm_tc2_kernel<APK, GU, WI8>;
+    constexpr int kSmem2 = Cfg2<APK, GU, WI8, STG>::kSmem;
+    auto *kernel = gemm_tc2_kernel<APK, GU, WI8, STG>;
     if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0) return DUQ4_ERR_ALIGN;
     if (K >= 131072u) return DUQ4_ERR_SHAPE;
     static DeviceOnce once;
@@ -748,6 +754,9 @@ int gemm_tc2_launch(bool a_packed, const void *A, const void *B, uint32_t M, uin
 // duq4_weight_prelayout_i8). DUQ4_ERR_DEVICE when the device cannot co-schedule CTA pairs.
 int gemm_tc2_launch_prelaid(const void *A, const void *W_i8, uint32_t M, uint32_t N, uint32_t K, const EpiParams &p, void *out,
                             int32_t *acc_out, cudaStream_t st, void *sk_scratch, size_t sk_bytes) {
+    // results that stay on this GPU need no staged row segments (see Cfg2)
+    if (p.n_peers == 0 && p.n_acc_owners == 0)
+        return launch2<false, false, true, false>(A, W_i8, M, N, K, 1, p, out, acc_out, st, 0, true, sk_scratch, sk_bytes);
     return launch2<false, false, true>(A, W_i8, M, N, K, 1, p, out, acc_out, st, 0, true, sk_scratch, sk_bytes);
 }
 
