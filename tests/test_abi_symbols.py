@@ -70,6 +70,27 @@ def test_arguments_are_rejected_before_any_launch():
     peers = L.Epilogue(); peers.mode = L.MODE_SYM; peers.scale_col_1 = 0x1000; peers.n_out_peers = 1; peers.out_peers[0] = 0x1000
     assert c.duq4_linear_w4a4_from_fp16_host(P, P, 300, 8, 64, L.MODE_SYM, 1.0, ctypes.byref(peers), P, 0, P, 1 << 30, NULL) == -3
     assert c.duq4_linear_w4a4_from_fp16_host(P, P, 300, 8, 64, L.MODE_SYM, 1.0, ep, P, 0, NULL, 1 << 30, NULL) == -4
+    # row routing of the fused gather: needs peers, no multicast, enough owners for the rows, an entry point that routes
+    routed = L.Epilogue(); routed.mode = L.MODE_SYM; routed.scale_row = 0x1000; routed.scale_col_1 = 0x1000; routed.out_rows_per_owner = 2
+    assert c.duq4_linear_w4a4(P, P, 4, 8, 64, ctypes.byref(routed), P, NULL, NULL) == -3            # no peers
+    routed.n_out_peers = 1; routed.out_peers[0] = 0x1000
+    assert c.duq4_linear_w4a4(P, P, 4, 8, 64, ctypes.byref(routed), NULL, NULL, NULL) == -2         # 1 owner x 2 rows < 4 rows
+    routed.out_multicast = 0x2000
+    assert c.duq4_linear_w4a4(P, P, 2, 8, 64, ctypes.byref(routed), NULL, NULL, NULL) == -3         # multicast and routing exclude each other
+    routed.out_multicast = None
+    assert c.duq4_linear_w4a4_batched(P, P, 2, 8, 64, 1, ctypes.byref(routed), NULL, NULL, NULL) == -3   # the batched entry point does not route
+    # host result by rows: flags, rank index, full width, routing chosen by the call itself
+    flags = (ctypes.c_void_p * 2)(0x3000, 0x4000)
+    epoch = ctypes.c_uint64(0)
+    two = L.Epilogue(); two.mode = L.MODE_SYM; two.scale_col_1 = 0x1000; two.ldo = 64; two.n_out_peers = 2; two.out_peers[0] = 0x1000; two.out_peers[1] = 0x2000
+    rows = lambda e_, col, self_, fl, ep_: c.duq4_linear_w4a4_from_fp16_to_host_rows(P, P, 0, 4, 8, 64, L.MODE_SYM, 1.0, ctypes.byref(e_), col, self_, fl,
+                                                                                   ep_, 0, P, 0, P, 1 << 20, NULL)
+    assert rows(two, 0, 0, None, ctypes.byref(epoch)) == -1          # no barrier flags
+    assert rows(two, 0, 2, flags, ctypes.byref(epoch)) == -2         # rank index outside the peer list
+    assert rows(two, 60, 0, flags, ctypes.byref(epoch)) == -2        # the block does not fit the result's width
+    two.out_rows_per_owner = 2
+    assert rows(two, 0, 0, flags, ctypes.byref(epoch)) == -3         # the routing is the call's own choice
+    assert epoch.value == 0
     # empty problems are fine and do nothing
     assert c.duq4_linear_w4a4_from_fp16(P, P, 0, 8, 64, L.MODE_SYM, 1.0, ep, P, P, 1 << 20, NULL) == 0
     # sizes of the host-buffer staging area: device copies of x and of the result + one chunk's quantizer scratch
